@@ -1,0 +1,298 @@
+// Fused expert-parallel combine for sm_100a: every source rank PULLS the
+// already-weighted partial rows of its tokens from the ranks that computed them
+// (peer loads over NVLink) and reduces them in one pass:
+//
+//   out[t] = bf16( float( bf16( sum_{r != self, ascending r} float(partial_r[t]) ) )
+//                  + float(partial_self[t]) )
+//
+// i.e. remote ranks are accumulated in FP32 in ascending rank order starting
+// from +0, rounded to BF16, then the local contribution is added and the sum is
+// rounded again - the arithmetic of the reference's finalize/reduce kernels
+// (ep_xpress/csrc/kernels.cu:27-36, ep_xpress/csrc/host_sm.cu:592-607 and
+// :1846-1895). RankCtx::single_round selects the multi-node variant instead:
+// one FP32 accumulation over all contributing ranks in rank order and a single
+// rounding (ep_xpress/csrc/gin.cu:226-246). Arrival order never changes the
+// arithmetic: loads of several peers are in flight together but are added in
+// program order.
+//
+// There is no receive staging plane [world, tokens, hidden] and no separate
+// reduce launch (reference: host_sm.cu:1212-1468 followed by :592-607).
+// Protocol: (A) if the expert output is a caller tensor it is copied into the
+// slot's peer-visible partial plane; the last CTA then publishes the monotone
+// combine epoch to every peer; (B) wait, bounded, for the epoch of exactly the
+// peers this rank sent rows to; (C) reduce; (D) the last CTA retires the epoch.
+// No trailing handshake is needed: a peer's partial plane is only rewritten
+// after a later dispatch on the same slot, which cannot complete before this
+// rank has entered that dispatch, i.e. finished this combine.
+#include "epx_device.cuh"
+#include "epx_launch.h"
+
+namespace epx {
+namespace {
+
+constexpr unsigned kPhaseCombine = 2;
+constexpr int kWarps = kThreads / 32;
+constexpr int kPeerBatch = 8;   // peer rows whose loads are in flight together
+
+template <int kWords>
+struct Chunk {
+  unsigned w[kWords];
+};
+
+template <int kWords>
+__device__ __forceinline__ Chunk<kWords> load_chunk(const char* p) {
+  Chunk<kWords> c;
+  if (kWords == 4) {
+    const uint4 v = ld_payload16(p);
+    c.w[0] = v.x; c.w[1 % kWords] = v.y; c.w[2 % kWords] = v.z; c.w[3 % kWords] = v.w;
+  } else {
+    c.w[0] = ld_payload4(p);
+  }
+  return c;
+}
+
+template <int kWords>
+__device__ __forceinline__ void store_chunk(char* p, const Chunk<kWords>& c) {
+  if (kWords == 4) st_payload16(p, make_uint4(c.w[0], c.w[1 % kWords], c.w[2 % kWords], c.w[3 % kWords]));
+  else st_payload4(p, c.w[0]);
+}
+
+template <int kWords>
+__device__ __forceinline__ void accumulate(float* acc, const Chunk<kWords>& c) {
+#pragma unroll
+  for (int i = 0; i < kWords; ++i) {
+    acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(c.w[i] << 16));
+    acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(c.w[i] & 0xffff0000u));
+  }
+}
+
+// Two-step rounding (default) or single rounding of the accumulated sum.
+template <int kWords>
+__device__ __forceinline__ Chunk<kWords> finish(const float* acc, const Chunk<kWords>& local, bool has_local,
+                                                bool single_round) {
+  Chunk<kWords> out;
+#pragma unroll
+  for (int i = 0; i < kWords; ++i) {
+    float lo = acc[2 * i], hi = acc[2 * i + 1];
+    if (!single_round) {
+      const float llo = has_local ? __uint_as_float(local.w[i] << 16) : 0.f;
+      const float lhi = has_local ? __uint_as_float(local.w[i] & 0xffff0000u) : 0.f;
+      lo = __fadd_rn(bf16_bits_to_float(float_to_bf16_bits(lo)), llo);
+      hi = __fadd_rn(bf16_bits_to_float(float_to_bf16_bits(hi)), lhi);
+    }
+    out.w[i] = static_cast<unsigned>(float_to_bf16_bits(lo)) |
+               (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+  }
+  return out;
+}
+
+__device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
+  for (int i = 0; i < n; ++i) mask &= mask - 1;
+  return __ffsll(static_cast<long long>(mask)) - 1;
+}
+
+template <bool kVec16>
+__device__ __forceinline__ void combine_body(const CombineOp& op) {
+  constexpr int kWords = kVec16 ? 4 : 1;
+  constexpr int kChunk = kWords * 4;
+  const RankCtx& c = *op.ctx;
+  const int W = c.world, self = c.rank, H = c.hidden, K = c.topk;
+  const bool single_round = c.single_round != 0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int T = op.tokens;
+  char* const my_heap = c.heap[self];
+  CtrlHeader* const hdr = header_of(my_heap);
+  const CtrlLayout cl = ctrl_layout(W);
+  const SlotLayout sl = slot_layout(op.slot_capacity, op.slot_tokens, H, K, W);
+  char* const slot = my_heap + op.slot_off;
+  const unsigned long long* const mask_arr = reinterpret_cast<const unsigned long long*>(slot + sl.mask);
+  const int* const dest_rows = reinterpret_cast<const int*>(slot + sl.dest_rows);
+  const int* const misc = reinterpret_cast<const int*>(slot + sl.misc);
+  const int fan = route_fanout(K, W);
+  const long long row_bytes = static_cast<long long>(H) * 2;
+
+  __shared__ const char* s_part[64];
+  __shared__ int s_need[64];
+  __shared__ int s_last;
+
+  const unsigned e = ld_volatile_u32(&hdr->comb_epoch) + 1;
+  if (tid < W) {
+    const unsigned long long off = reinterpret_cast<const unsigned long long*>(slot + sl.peer_off)[tid];
+    const int cap = reinterpret_cast<const int*>(slot + sl.peer_cap)[tid];
+    const SlotLayout pl = slot_layout(cap, 0, H, K, W);
+    s_part[tid] = c.heap[tid] + off + pl.partial;
+    s_need[tid] = (tid != self && reinterpret_cast<const int*>(slot + sl.send_cnt)[tid] > 0) ? 1 : 0;
+  }
+  const int valid = misc[kValidCount];
+
+  // ---- A. make my partial rows peer-visible -------------------------------------
+  if (op.partial != nullptr) {
+    const long long chunks = static_cast<long long>(valid) * row_bytes / kChunk;
+    const char* src = reinterpret_cast<const char*>(op.partial);
+    char* dst = slot + sl.partial;
+    const long long threads = static_cast<long long>(gridDim.x) * kThreads;
+    for (long long i = static_cast<long long>(blockIdx.x) * kThreads + tid; i < chunks; i += threads) {
+      if (kVec16) *reinterpret_cast<uint4*>(dst + i * 16) = *reinterpret_cast<const uint4*>(src + i * 16);
+      else *reinterpret_cast<unsigned*>(dst + i * 4) = *reinterpret_cast<const unsigned*>(src + i * 4);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(&hdr->cdone_count, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) __threadfence_system();
+  }
+  __syncthreads();
+  if (s_last && tid < W && tid != self) {
+    unsigned long long* flag = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.ready) + self;
+    st_release_sys(flag, static_cast<unsigned long long>(e));
+  }
+
+  // ---- B. wait for the peers I pull from --------------------------------------------
+  bool ok = true;
+  if (tid < W && s_need[tid]) {
+    const unsigned long long* flag = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready) + tid;
+    ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(flag) >= e; });
+  }
+  if (!__syncthreads_and(ok)) return;
+
+  // ---- C. pull + rank-order reduce ----------------------------------------------------
+  const int segs = op.segments;
+  const long long seg_bytes = align_up((row_bytes + segs - 1) / segs, 32 * kChunk);
+  const long long items = static_cast<long long>(T) * segs;
+  const long long total_warps = static_cast<long long>(gridDim.x) * kWarps;
+  for (long long item = static_cast<long long>(blockIdx.x) * kWarps + warp; item < items; item += total_warps) {
+    const int t = static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
+    const unsigned long long m = mask_arr[t];
+    const int n = __popcll(m);
+    const long long b0 = seg * seg_bytes;
+    const long long b1 = min(row_bytes, b0 + seg_bytes);
+    char* const outp = reinterpret_cast<char*>(op.out) + static_cast<long long>(t) * row_bytes;
+
+    // Lane j (and j + 32) resolves the j-th contributor in ascending rank order.
+    const char* ptr_a = nullptr;
+    const char* ptr_b = nullptr;
+    int self_index = -1;
+    {
+      bool is_self = false;
+      if (lane < n) {
+        const int d = nth_set_bit(m, lane);
+        const int row = dest_rows[static_cast<long long>(t) * fan + lane];
+        if (row >= 0) ptr_a = s_part[d] + static_cast<long long>(row) * row_bytes;
+        is_self = (d == self);
+      }
+      const unsigned vote_a = __ballot_sync(0xffffffffu, is_self);
+      is_self = false;
+      if (lane + 32 < n) {
+        const int d = nth_set_bit(m, lane + 32);
+        const int row = dest_rows[static_cast<long long>(t) * fan + lane + 32];
+        if (row >= 0) ptr_b = s_part[d] + static_cast<long long>(row) * row_bytes;
+        is_self = (d == self);
+      }
+      const unsigned vote_b = __ballot_sync(0xffffffffu, is_self);
+      if (vote_a) self_index = __ffs(vote_a) - 1;
+      else if (vote_b) self_index = 32 + __ffs(vote_b) - 1;
+    }
+    const int skip = single_round ? -1 : self_index;
+    const unsigned long long local_bits =
+        (self_index < 0 || single_round) ? 0ull
+        : __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(self_index < 32 ? ptr_a : ptr_b), self_index & 31);
+    const char* const local_ptr = reinterpret_cast<const char*>(local_bits);
+
+    if (n <= kPeerBatch) {
+      // Common case: every contributor's row pointer sits in a register.
+      const char* rp[kPeerBatch];
+#pragma unroll
+      for (int b = 0; b < kPeerBatch; ++b) {
+        const unsigned long long bits = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr_a), b);
+        rp[b] = (b < n && b != skip) ? reinterpret_cast<const char*>(bits) : nullptr;
+      }
+      for (long long off = b0 + static_cast<long long>(lane) * kChunk; off < b1; off += 32ll * kChunk) {
+        Chunk<kWords> v[kPeerBatch];
+#pragma unroll
+        for (int b = 0; b < kPeerBatch; ++b)
+          if (rp[b] != nullptr) v[b] = load_chunk<kWords>(rp[b] + off);
+        Chunk<kWords> local;
+        if (local_ptr != nullptr) local = load_chunk<kWords>(local_ptr + off);
+        float acc[kWords * 2];
+#pragma unroll
+        for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int b = 0; b < kPeerBatch; ++b)
+          if (rp[b] != nullptr) accumulate<kWords>(acc, v[b]);
+        store_chunk<kWords>(outp + off, finish<kWords>(acc, local, local_ptr != nullptr, single_round));
+      }
+    } else {
+      // More contributors than registers: batches of kPeerBatch, still ascending.
+      for (long long batch = b0; batch < b1; batch += 32ll * kChunk) {   // warp-uniform trip count
+        const long long off = batch + static_cast<long long>(lane) * kChunk;
+        const bool active = off < b1;
+        float acc[kWords * 2];
+#pragma unroll
+        for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
+        for (int j0 = 0; j0 < n; j0 += kPeerBatch) {
+          Chunk<kWords> v[kPeerBatch];
+          bool use[kPeerBatch];
+#pragma unroll
+          for (int b = 0; b < kPeerBatch; ++b) {
+            const int j = j0 + b;
+            const unsigned long long bits =
+                __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(j < 32 ? ptr_a : ptr_b), j & 31);
+            use[b] = active && j < n && j != skip && bits != 0ull;
+            if (use[b]) v[b] = load_chunk<kWords>(reinterpret_cast<const char*>(bits) + off);
+          }
+#pragma unroll
+          for (int b = 0; b < kPeerBatch; ++b)
+            if (use[b]) accumulate<kWords>(acc, v[b]);
+        }
+        if (active) {
+          Chunk<kWords> local;
+          if (local_ptr != nullptr) local = load_chunk<kWords>(local_ptr + off);
+          store_chunk<kWords>(outp + off, finish<kWords>(acc, local, local_ptr != nullptr, single_round));
+        }
+      }
+    }
+  }
+
+  // ---- D. retire the epoch ---------------------------------------------------------------
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(&hdr->cfin_count, 1u);
+    if (prev == gridDim.x - 1) {
+      hdr->cdone_count = 0;
+      hdr->cfin_count = 0;
+      hdr->comb_epoch = e;
+      __threadfence();
+    }
+  }
+}
+
+template <bool kVec16>
+__global__ void __launch_bounds__(kThreads, 1) combine_kernel(const __grid_constant__ CombineArgs args) {
+  combine_body<kVec16>(args.op[blockIdx.y]);
+}
+
+}  // namespace
+
+cudaError_t combine_max_ctas(bool vec16, int* ctas) {
+  int device = 0, sms = 0, per_sm = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (err != cudaSuccess) return err;
+  err = vec16 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<true>, kThreads, 0)
+              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<false>, kThreads, 0);
+  if (err != cudaSuccess) return err;
+  *ctas = per_sm * sms;
+  return cudaSuccess;
+}
+
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, cudaStream_t stream) {
+  void* params[] = {const_cast<CombineArgs*>(&args)};
+  const void* kernel = vec16 ? reinterpret_cast<const void*>(combine_kernel<true>)
+                             : reinterpret_cast<const void*>(combine_kernel<false>);
+  return cudaLaunchCooperativeKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, 0, stream);
+}
+
+}  // namespace epx

@@ -1,0 +1,404 @@
+// Fused expert-parallel dispatch for sm_100a: top-k routing, one-row-per-
+// destination-rank dedup, per-rank counts and offset prefix sums, and the BF16
+// payload pack, with the rows stored straight into the destination ranks'
+// receive tensors over NVLink (plain peer stores; local rows take the same
+// path into the rank's own heap). No staging buffer, no per-op host work, no
+// cross-GPU atomics.
+//
+// What the reference does with a persistent host-ring kernel plus init and
+// finalize launches (ep_xpress/csrc/host_sm.cu:559-607 and :613-1191) is one
+// launch here:
+//   1. route     every CTA maps a tile of tokens to a 64-bit destination mask
+//                (dedup), validates ids/weights, and counts rows per destination;
+//   2. publish   after one rank-local barrier the rank's count row goes to every
+//                peer as generation-tagged words (this message is also the
+//                credit "my receive slot of this generation is free");
+//   3. offsets   once all count rows are in, every rank knows
+//                offset[self->d] = sum_{s<self} count[s->d] and valid_count[d];
+//                rows therefore land in (source rank, token) order, the order of
+//                the reference's CPU planner (ep_xpress/routing.py:140-158);
+//   4. payload   one warp per (token, row segment) loads the row once and stores
+//                it to every destination together with translated local expert
+//                ids, weights and the (source, token) inverse entry;
+//   5. signal    the last CTA publishes "done" to every peer after a system fence;
+//   6. receive   padding rows are reset, valid_count is written, and the launch
+//                ends once every sender with rows for this rank has signalled.
+// Every wait is bounded by RankCtx::timeout_ns and ends in a status code.
+#include "epx_device.cuh"
+#include "epx_launch.h"
+
+namespace epx {
+namespace {
+
+constexpr unsigned kPhaseDispatch = 1;
+constexpr int kWarps = kThreads / 32;
+
+struct PeerPlanes {
+  char* hidden;
+  char* ids;
+  char* weights;
+  char* inverse;
+};
+
+template <typename IdT>
+__device__ __forceinline__ long long load_id(const void* ids, long long index) {
+  return static_cast<long long>(reinterpret_cast<const IdT*>(ids)[index]);
+}
+
+__device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
+  for (int i = 0; i < n; ++i) mask &= mask - 1;
+  return __ffsll(static_cast<long long>(mask)) - 1;
+}
+
+template <typename IdT, bool kVec16>
+__device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_base) {
+  const RankCtx& c = *op.ctx;
+  const int W = c.world, self = c.rank, H = c.hidden, K = c.topk, E = c.num_experts;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int T = op.tokens;
+  char* const my_heap = c.heap[self];
+  CtrlHeader* const hdr = header_of(my_heap);
+  const CtrlLayout cl = ctrl_layout(W);
+  const SlotLayout sl = slot_layout(op.slot_capacity, op.slot_tokens, H, K, W);
+  char* const slot = my_heap + op.slot_off;
+  unsigned long long* const mask_arr = reinterpret_cast<unsigned long long*>(slot + sl.mask);
+  int* const dest_rows = reinterpret_cast<int*>(slot + sl.dest_rows);
+  int* const tile_cnt = reinterpret_cast<int*>(slot + sl.tile_cnt);
+  int* const misc = reinterpret_cast<int*>(slot + sl.misc);
+  const int fan = route_fanout(K, W);
+  const int ntiles = route_tiles(T);
+
+  __shared__ int s_warp_cnt[kWarps][64];
+  __shared__ int s_send[64], s_off[64], s_total[64], s_ok[64];
+  __shared__ char* s_heap[64];
+  __shared__ PeerPlanes s_planes[64];
+  __shared__ int s_last;
+
+  const unsigned g = ld_volatile_u32(&hdr->disp_epoch) + 1;
+  const int par = static_cast<int>(g & 1u);
+  const int dirty_prev = misc[kDirtyRows];
+  unsigned long long* const my_cnt = reinterpret_cast<unsigned long long*>(my_heap + cl.cnt) +
+                                     static_cast<size_t>(par) * W * W;
+  unsigned long long* const my_addr = reinterpret_cast<unsigned long long*>(my_heap + cl.addr) +
+                                      static_cast<size_t>(par) * W * 4;
+  unsigned long long* const my_done = reinterpret_cast<unsigned long long*>(my_heap + cl.done) +
+                                      static_cast<size_t>(par) * W;
+  if (tid < W) s_heap[tid] = c.heap[tid];
+
+  // Credit + address: does not depend on routing, so it leaves first.
+  if (blockIdx.x == 0 && tid < W) {
+    unsigned long long* a = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.addr) +
+                            (static_cast<size_t>(par) * W + self) * 4;
+    st_relaxed_sys(a + 0, tagged(g, static_cast<unsigned>(op.slot_off >> 8)));
+    st_relaxed_sys(a + 1, tagged(g, static_cast<unsigned>(op.slot_capacity)));
+    st_relaxed_sys(a + 2, tagged(g, static_cast<unsigned>(op.capacity)));
+    st_relaxed_sys(a + 3, tagged(g, static_cast<unsigned>(op.identity)));
+  }
+
+  // ---- 1. route ------------------------------------------------------------
+  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int t = tile * kRouteTile + tid;
+    unsigned long long m = 0;
+    if (t < T) {
+      bool bad = false;
+      const long long row = static_cast<long long>(t) * K;
+      for (int k = 0; k < K; ++k) {
+        const long long id = load_id<IdT>(op.ids, row + k);
+        if (id == -1) continue;
+        if (id < 0 || id >= E) { bad = true; continue; }
+        const float w = op.weights[row + k];
+        if (!isfinite(w)) bad = true;
+        for (int j = 0; j < k; ++j)
+          if (load_id<IdT>(op.ids, row + j) == id) bad = true;
+        m |= 1ull << c.expert_rank[id];
+      }
+      if (bad) {
+        m = 0;
+        report_error(c, kInvalidRoute, kPhaseDispatch, 1, static_cast<unsigned>(t));
+      }
+      mask_arr[t] = m;
+    }
+    int j = 0;
+    for (int d = 0; d < W; ++d) {
+      const bool bit = (m >> d) & 1ull;
+      const unsigned ballot = __ballot_sync(0xffffffffu, bit);
+      if (bit) dest_rows[static_cast<long long>(t) * fan + j++] = __popc(ballot & ((1u << lane) - 1u));
+      if (lane == 0) s_warp_cnt[warp][d] = __popc(ballot);
+    }
+    __syncthreads();
+    if (tid < W) {
+      int run = 0;
+      for (int w = 0; w < kWarps; ++w) {
+        const int v = s_warp_cnt[w][tid];
+        s_warp_cnt[w][tid] = run;
+        run += v;
+      }
+      tile_cnt[static_cast<long long>(tile) * W + tid] = run;
+    }
+    __syncthreads();
+    if (m) {
+      int jj = 0;
+      for (unsigned long long mm = m; mm; mm &= mm - 1) {
+        const int d = __ffsll(static_cast<long long>(mm)) - 1;
+        dest_rows[static_cast<long long>(t) * fan + jj++] += s_warp_cnt[warp][d];
+      }
+    }
+    __syncthreads();
+  }
+
+  if (!rank_barrier(c, &hdr->bar_count, gridDim.x, kPhaseDispatch)) return;
+
+  // ---- 2. publish my count row ----------------------------------------------
+  if (tid < W) {
+    int run = 0;
+    for (int tile = 0; tile < ntiles; ++tile) {
+      const int v = tile_cnt[static_cast<long long>(tile) * W + tid];
+      tile_base[tile * W + tid] = run;
+      run += v;
+    }
+    s_send[tid] = run;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int i = tid; i < W * W; i += kThreads) {
+      const int p = i / W, d = i % W;
+      unsigned long long* dst = reinterpret_cast<unsigned long long*>(s_heap[p] + cl.cnt) +
+                                (static_cast<size_t>(par) * W + self) * W + d;
+      st_relaxed_sys(dst, tagged(g, static_cast<unsigned>(s_send[d])));
+    }
+  }
+
+  // ---- 3. wait for every rank's counts and addresses ---------------------------
+  bool ok = true;
+  for (int i = tid; i < W * W && ok; i += kThreads)
+    ok = bounded_wait(c, kPhaseDispatch, 3, [&] { return tag_of(ld_acquire_sys(my_cnt + i)) == g; });
+  for (int i = tid; i < W * 4 && ok; i += kThreads)
+    ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(my_addr + i)) == g; });
+  if (!__syncthreads_and(ok)) return;
+
+  if (tid < W) {
+    const int d = tid;
+    int off = 0, total = 0;
+    for (int s = 0; s < W; ++s) {
+      const int v = static_cast<int>(value_of(ld_relaxed_sys(my_cnt + s * W + d)));
+      if (s < self) off += v;
+      total += v;
+    }
+    const unsigned long long base = static_cast<unsigned long long>(value_of(ld_relaxed_sys(my_addr + d * 4 + 0))) << 8;
+    const int layout_cap = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * 4 + 1)));
+    const int bound = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * 4 + 2)));
+    const unsigned ident = value_of(ld_relaxed_sys(my_addr + d * 4 + 3));
+    const SlotLayout pl = slot_layout(layout_cap, 0, H, K, W);
+    char* peer_slot = s_heap[d] + base;
+    s_planes[d].hidden = peer_slot + pl.hidden;
+    s_planes[d].ids = peer_slot + pl.ids;
+    s_planes[d].weights = peer_slot + pl.weights;
+    s_planes[d].inverse = peer_slot + pl.inverse;
+    s_off[d] = off;
+    s_total[d] = total;
+    s_ok[d] = (total <= bound && bound <= layout_cap) ? 1 : 0;
+    if (blockIdx.x == 0) {
+      reinterpret_cast<unsigned long long*>(slot + sl.peer_off)[d] = base;
+      reinterpret_cast<int*>(slot + sl.peer_cap)[d] = layout_cap;
+      reinterpret_cast<int*>(slot + sl.send_cnt)[d] = s_ok[d] ? s_send[d] : 0;
+      reinterpret_cast<int*>(slot + sl.recv_cnt)[d] = static_cast<int>(value_of(ld_relaxed_sys(my_cnt + d * W + self)));
+      if (!s_ok[d] && (d == self || s_send[d] > 0))
+        report_error(c, kCapacityExceeded, kPhaseDispatch, static_cast<unsigned>(d), static_cast<unsigned>(total));
+      if (ident != static_cast<unsigned>(op.identity))
+        report_error(c, kIdentityMismatch, kPhaseDispatch, static_cast<unsigned>(d), ident);
+    }
+  }
+  __syncthreads();
+
+  // ---- 4. payload --------------------------------------------------------------
+  const long long row_bytes = static_cast<long long>(H) * 2;
+  constexpr int kChunk = kVec16 ? 16 : 4;
+  constexpr int kUnroll = 4;
+  const int segs = op.segments;
+  const long long seg_bytes = align_up((row_bytes + segs - 1) / segs, 32 * kChunk);
+  const long long items = static_cast<long long>(T) * segs;
+  const long long total_warps = static_cast<long long>(gridDim.x) * kWarps;
+  for (long long item = static_cast<long long>(blockIdx.x) * kWarps + warp; item < items; item += total_warps) {
+    const int t = static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
+    const unsigned long long m = mask_arr[t];
+    if (!m) continue;
+    const int n = __popcll(m);
+    const int tile = t / kRouteTile;
+    for (int j0 = 0; j0 < n; j0 += 32) {   // n <= 63: at most two rounds
+      const int j = j0 + lane;
+      int d = 0;
+      long long row = -1;
+      if (j < n) {
+        d = nth_set_bit(m, j);
+        if (s_ok[d]) row = static_cast<long long>(s_off[d]) + tile_base[tile * W + d] + dest_rows[static_cast<long long>(t) * fan + j];
+      }
+      // Payload of this round of destinations.
+      const int round = min(32, n - j0);
+      const long long b0 = seg * seg_bytes;
+      const long long b1 = min(row_bytes, b0 + seg_bytes);
+      const char* src = reinterpret_cast<const char*>(op.x) + static_cast<long long>(t) * row_bytes;
+      for (long long batch = b0; batch < b1; batch += 32ll * kChunk * kUnroll) {   // warp-uniform trip count
+        const long long off = batch + static_cast<long long>(lane) * kChunk;
+        uint4 v16[kUnroll];
+        unsigned v4[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const long long o = off + static_cast<long long>(u) * 32 * kChunk;
+          if (o < b1) {
+            if (kVec16) v16[u] = *reinterpret_cast<const uint4*>(src + o);
+            else v4[u] = *reinterpret_cast<const unsigned*>(src + o);
+          }
+        }
+        for (int jj = 0; jj < round; ++jj) {
+          const int d2 = __shfl_sync(0xffffffffu, d, jj);
+          const long long r2 = __shfl_sync(0xffffffffu, row, jj);
+          if (r2 < 0) continue;
+          char* dst = s_planes[d2].hidden + r2 * row_bytes;
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const long long o = off + static_cast<long long>(u) * 32 * kChunk;
+            if (o < b1) {
+              if (kVec16) st_payload16(dst + o, v16[u]);
+              else st_payload4(dst + o, v4[u]);
+            }
+          }
+        }
+      }
+      // Row metadata rides with segment 0.
+      if (seg == 0) {
+        for (int jj = 0; jj < round; ++jj) {
+          const int d2 = __shfl_sync(0xffffffffu, d, jj);
+          const long long r2 = __shfl_sync(0xffffffffu, row, jj);
+          if (r2 < 0) continue;
+          long long* out_ids = reinterpret_cast<long long*>(s_planes[d2].ids) + r2 * K;
+          float* out_w = reinterpret_cast<float*>(s_planes[d2].weights) + r2 * K;
+          for (int k = lane; k < K; k += 32) {
+            const long long id = load_id<IdT>(op.ids, static_cast<long long>(t) * K + k);
+            long long local = -1;
+            float w = 0.f;
+            if (id >= 0) {
+              w = op.weights[static_cast<long long>(t) * K + k];
+              if (c.expert_rank[id] == d2) local = c.expert_local[id];
+            }
+            out_ids[k] = local;
+            out_w[k] = w;
+          }
+          if (lane == 0) {
+            long long* inv = reinterpret_cast<long long*>(s_planes[d2].inverse) + r2 * 2;
+            inv[0] = self;
+            inv[1] = t;
+          }
+        }
+        if (j < n) dest_rows[static_cast<long long>(t) * fan + j] = static_cast<int>(row);
+      }
+    }
+  }
+
+  // ---- 5. signal -----------------------------------------------------------------
+  const int valid = s_ok[self] ? s_total[self] : 0;
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    const unsigned prev = atomicAdd(&hdr->done_count, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) __threadfence_system();
+  }
+  __syncthreads();
+  if (s_last) {
+    if (tid < W) {
+      unsigned long long* flag = reinterpret_cast<unsigned long long*>(s_heap[tid] + cl.done) +
+                                 static_cast<size_t>(par) * W + self;
+      st_release_sys(flag, tagged(g, 1u));
+    }
+    if (tid == 0) {
+      misc[kValidCount] = valid;
+      misc[kDirtyRows] = valid;
+      hdr->bar_count = 0;
+      hdr->done_count = 0;
+      hdr->disp_epoch = g;
+      __threadfence();
+    }
+  }
+
+  // ---- 6. receive side -------------------------------------------------------------
+  // Rows in [valid, previous valid) held data of the slot's previous operation.
+  if (dirty_prev > valid) {
+    const long long pad_rows = dirty_prev - valid;
+    char* hid = slot + sl.hidden;
+    long long* ids_out = reinterpret_cast<long long*>(slot + sl.ids);
+    float* w_out = reinterpret_cast<float*>(slot + sl.weights);
+    long long* inv_out = reinterpret_cast<long long*>(slot + sl.inverse);
+    const long long threads = static_cast<long long>(gridDim.x) * kThreads;
+    const long long me = static_cast<long long>(blockIdx.x) * kThreads + tid;
+    for (long long i = me; i < pad_rows * K; i += threads) {
+      ids_out[static_cast<long long>(valid) * K + i] = -1;
+      w_out[static_cast<long long>(valid) * K + i] = 0.f;
+    }
+    for (long long i = me; i < pad_rows * 2; i += threads) inv_out[static_cast<long long>(valid) * 2 + i] = -1;
+    if (op.zero_padding) {
+      const long long words = pad_rows * row_bytes / 4;
+      unsigned* base = reinterpret_cast<unsigned*>(hid + static_cast<long long>(valid) * row_bytes);
+      if (kVec16) {
+        const long long vecs = words / 4;
+        for (long long i = me; i < vecs; i += threads) st_payload16(base + i * 4, make_uint4(0, 0, 0, 0));
+      } else {
+        for (long long i = me; i < words; i += threads) base[i] = 0u;
+      }
+    }
+  }
+  ok = true;
+  if (tid < W && s_ok[self] && value_of(ld_relaxed_sys(my_cnt + tid * W + self)) > 0)
+    ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return tag_of(ld_acquire_sys(my_done + tid)) == g; });
+  __syncthreads_and(ok);
+}
+
+template <typename IdT, bool kVec16>
+__global__ void __launch_bounds__(kThreads, 1) dispatch_kernel(const __grid_constant__ DispatchArgs args) {
+  extern __shared__ int tile_base[];
+  dispatch_body<IdT, kVec16>(args.op[blockIdx.y], tile_base);
+}
+
+using DispatchKernel = void (*)(const DispatchArgs);
+
+DispatchKernel pick_kernel(bool ids64, bool vec16) {
+  if (ids64) return vec16 ? dispatch_kernel<long long, true> : dispatch_kernel<long long, false>;
+  return vec16 ? dispatch_kernel<int, true> : dispatch_kernel<int, false>;
+}
+
+}  // namespace
+
+size_t dispatch_dynamic_smem(int max_tokens, int world) {
+  return static_cast<size_t>(route_tiles(max_tokens) + 1) * world * sizeof(int);
+}
+
+cudaError_t dispatch_max_ctas(bool ids64, bool vec16, size_t dynamic_smem, int* ctas) {
+  int device = 0, sms = 0, per_sm = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  if (err != cudaSuccess) return err;
+  DispatchKernel kernel = pick_kernel(ids64, vec16);
+  if (dynamic_smem > 48 * 1024) {
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dynamic_smem));
+    if (err != cudaSuccess) return err;
+  }
+  err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, dynamic_smem);
+  if (err != cudaSuccess) return err;
+  *ctas = per_sm * sms;
+  return cudaSuccess;
+}
+
+cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
+                            size_t dynamic_smem, cudaStream_t stream) {
+  DispatchKernel kernel = pick_kernel(ids64, vec16);
+  if (dynamic_smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(dynamic_smem));
+    if (err != cudaSuccess) return err;
+  }
+  void* params[] = {const_cast<DispatchArgs*>(&args)};
+  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(ctas_per_rank, ranks, 1),
+                                     dim3(kThreads, 1, 1), params, dynamic_smem, stream);
+}
+
+}  // namespace epx

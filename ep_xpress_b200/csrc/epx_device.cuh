@@ -1,0 +1,161 @@
+// Device-side primitives shared by the transport kernels: system-scope flag
+// words, bounded waits, sticky error reporting and a bounded grid barrier.
+//
+// The reference's equivalents are system-scope loads/stores on mapped host
+// pages (ep_xpress/csrc/host_sm.cu:98-124) and a sticky status word
+// (host_sm.cu:523-532). Here the words live in the RECEIVER's HBM: writers
+// store across NVLink, readers poll local memory.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include "epx_layout.h"
+
+namespace epx {
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_volatile_i32(const int* p) {
+  int v;
+  asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_volatile_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// 16-byte payload accesses. Peer rows are rewritten every generation, so they
+// must not be served from a stale L1 line: no-allocate loads after the acquire.
+__device__ __forceinline__ uint4 ld_payload16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_payload4(const void* p) {
+  unsigned v;
+  asm volatile("ld.global.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_payload16(void* p, uint4 v) {
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void st_payload4(void* p, unsigned v) {
+  asm volatile("st.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long tagged(unsigned generation, unsigned value) {
+  return (static_cast<unsigned long long>(generation) << 32) | value;
+}
+__device__ __forceinline__ unsigned tag_of(unsigned long long word) { return static_cast<unsigned>(word >> 32); }
+__device__ __forceinline__ unsigned value_of(unsigned long long word) { return static_cast<unsigned>(word); }
+
+__device__ __forceinline__ CtrlHeader* header_of(char* heap) { return reinterpret_cast<CtrlHeader*>(heap); }
+
+// Record the first error, raise the local bail-out flag and tell every peer,
+// so that their bounded waits end early with kPeerAbort instead of a timeout.
+// (Behaviour of the arena header error word, ep_xpress/csrc/host_sm.cu:1184-1190,
+// without the trap.)
+static __device__ __noinline__ void report_error(const RankCtx& c, int code, unsigned phase, unsigned where,
+                                          unsigned value) {
+  CtrlHeader* h = header_of(c.heap[c.rank]);
+  if (atomicCAS(&h->status, 0, code) == 0) {
+    h->error_detail = (static_cast<unsigned long long>(phase) << 56) |
+                      (static_cast<unsigned long long>(where & 0xffffffu) << 32) | value;
+    const CtrlLayout l = ctrl_layout(c.world);
+    for (int p = 0; p < c.world; ++p) {
+      if (p == c.rank) continue;
+      unsigned* slot = reinterpret_cast<unsigned*>(c.heap[p] + l.perr) + c.rank;
+      st_relaxed_sys_u32(slot, static_cast<unsigned>(code));
+    }
+  }
+  atomicExch(&h->abort_flag, 1);
+  __threadfence();
+}
+
+// Poll `ready()` until it holds, the timeout passes, the local bail-out flag is
+// raised or a peer published an error. Returns true only when `ready()` held.
+// Never traps, never spins forever: on failure the caller unwinds and returns.
+template <typename Ready>
+__device__ __forceinline__ bool bounded_wait(const RankCtx& c, unsigned phase, unsigned where, Ready ready) {
+  if (ready()) return true;
+  CtrlHeader* h = header_of(c.heap[c.rank]);
+  const CtrlLayout l = ctrl_layout(c.world);
+  const unsigned* perr = reinterpret_cast<const unsigned*>(c.heap[c.rank] + l.perr);
+  const unsigned long long start = global_timer_ns();
+  unsigned spins = 0;
+  while (true) {
+    if (ready()) return true;
+    if ((++spins & 63u) == 0) {
+      if (ld_volatile_i32(&h->abort_flag) != 0) return false;
+      for (int p = 0; p < c.world; ++p) {
+        if (p != c.rank && ld_volatile_u32(perr + p) != 0) {
+          report_error(c, kPeerAbort, phase, where, static_cast<unsigned>(p));
+          return false;
+        }
+      }
+      if (global_timer_ns() - start > c.timeout_ns) {
+        report_error(c, kTimeout, phase, where, spins);
+        return false;
+      }
+      __nanosleep(32);
+    }
+  }
+}
+
+// Barrier over the CTAs of ONE rank (blockIdx.x dimension). `target` is the
+// arrival count that completes it: k * gridDim.x for the k-th barrier of the
+// launch; the last CTA of the launch puts the counter back to zero. Requires a
+// cooperative launch (all CTAs resident). Returns false when the rank is
+// bailing out; the caller must then skip to its exit path.
+__device__ __forceinline__ bool rank_barrier(const RankCtx& c, unsigned* counter, unsigned target,
+                                             unsigned phase) {
+  __shared__ int barrier_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const bool ok = bounded_wait(c, phase, 0xB0u, [&] { return ld_acquire_gpu_u32(counter) >= target; });
+    __threadfence();
+    barrier_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  return barrier_ok != 0;
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(unsigned short bits) {
+  return __uint_as_float(static_cast<unsigned>(bits) << 16);
+}
+__device__ __forceinline__ unsigned short float_to_bf16_bits(float v) {
+  return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+}  // namespace epx

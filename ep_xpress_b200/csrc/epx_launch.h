@@ -1,0 +1,36 @@
+// Host-callable launchers of the transport kernels (plain C++, no torch types).
+#pragma once
+#include <cuda_runtime.h>
+#include "epx_layout.h"
+
+namespace epx {
+
+// Dynamic shared memory of the dispatch kernel for a slot laid out for
+// `max_tokens` local tokens.
+size_t dispatch_dynamic_smem(int max_tokens, int world);
+
+// Largest number of CTAs of each kernel that can be resident at once on the
+// current device; a cooperative launch may not exceed it. (The reference
+// negotiates the same bound through an occupancy query,
+// ep_xpress/csrc/host_sm.cu:2516-2564.)
+cudaError_t dispatch_max_ctas(bool ids64, bool vec16, size_t dynamic_smem, int* ctas);
+cudaError_t combine_max_ctas(bool vec16, int* ctas);
+
+cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
+                            size_t dynamic_smem, cudaStream_t stream);
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16,
+                           cudaStream_t stream);
+
+// Synthetic expert used by the validation harness and the communication
+// benchmark: partial[row] = bf16(hidden[row] * sum_k weights[row,k] * factor[local_ids[row,k]])
+// over slots with local_ids >= 0, for rows below *valid_count.
+cudaError_t launch_scale_rows(const void* hidden, const long long* local_ids, const float* weights,
+                              const int* valid_count, const float* factors, int num_factors, void* partial,
+                              int capacity, int hidden_size, int topk, cudaStream_t stream);
+
+// Resets the rows of a fresh slot to the padding state (ids -1, weights 0,
+// inverse -1, zero activations) and clears its bookkeeping words.
+cudaError_t launch_slot_reset(char* slot, SlotLayout layout, long long capacity, int hidden, int topk,
+                              cudaStream_t stream);
+
+}  // namespace epx

@@ -1,0 +1,73 @@
+import dataclasses
+
+import pytest
+
+from ep_xpress_b200 import Config
+
+
+def test_defaults_and_layout_helpers():
+    cfg = Config(hidden_size=2048, topk=8, max_tokens_per_rank=4096)
+    assert cfg.transport == "nvlink" and cfg.device_transport
+    assert cfg.chunk_rows == (2 << 20) // 4096
+    assert cfg.slot_bytes % 4096 == 0
+    assert cfg.channel_chunk_rows(4) == 128
+    assert cfg.combine_chunk_rows(4, 8) == 16
+    assert cfg.heap_bytes(8) % (2 << 20) == 0
+    assert cfg.heap_bytes(8) >= 2 * cfg.nvlink_slot_bytes(8)
+    with pytest.raises(dataclasses.FrozenInstanceError):
+        cfg.topk = 4
+
+
+def test_slot_bytes_accounts_for_every_plane():
+    cfg = Config(hidden_size=256, topk=2, max_tokens_per_rank=64)
+    cap, tok = 128, 64
+    minimum = cap * 256 * 2 * 2 + cap * 2 * 12 + cap * 16 + tok * 256 * 2
+    assert cfg.nvlink_slot_bytes(2) >= minimum
+    assert cfg.nvlink_slot_bytes(2, 10, 3) < cfg.nvlink_slot_bytes(2)
+
+
+@pytest.mark.parametrize("kwargs,fragment", [
+    (dict(diagnostics=1), "diagnostics must be a bool"),
+    (dict(transport="host_ce", diagnostics=True), "only supported by host_sm"),
+    (dict(transport="host_ce", decode_max_tokens=8), "only supported by host_sm"),
+    (dict(decode_single_frame=True), "decode_single_frame"),
+    (dict(channels=33), "channels must be at most 32"),
+    (dict(hidden_size=0), "hidden_size must be a positive integer"),
+    (dict(hidden_size=True), "hidden_size must be a positive integer"),
+    (dict(hidden_size=7), "even hidden size"),
+    (dict(topk=257), "topk <= 256"),
+    (dict(timeout_seconds=float("inf")), "timeout_seconds"),
+    (dict(timeout_seconds=4000.0), "3600"),
+    (dict(workload="train"), "workload"),
+    (dict(chunk_bytes=16), "chunk_bytes"),
+    (dict(decode_max_tokens=257), "decode_max_tokens"),
+    (dict(internode_transport="ib"), "internode_transport"),
+    (dict(internode_transport="gin", transport="nvlink"), "GIN requires host_sm"),
+    (dict(gin_contexts=0), "gin_contexts"),
+    (dict(combine_rounding="banker"), "combine_rounding"),
+])
+def test_validation(kwargs, fragment):
+    base = dict(hidden_size=64, topk=2, max_tokens_per_rank=8)
+    base.update(kwargs)
+    with pytest.raises(ValueError, match=fragment):
+        Config(**base)
+
+
+@pytest.mark.parametrize("kwargs", [dict(transport="rdma"), dict(combine_backend="cpu"), dict(graph_mode="capture")])
+def test_not_implemented(kwargs):
+    with pytest.raises(NotImplementedError):
+        Config(hidden_size=64, topk=2, max_tokens_per_rank=8, **kwargs)
+
+
+def test_host_ce_allows_odd_hidden_and_reports_host_pool():
+    cfg = Config(hidden_size=7, topk=2, max_tokens_per_rank=8, transport="host_ce")
+    assert cfg.pool_bytes(4) > 0
+    assert cfg.pinned_working_set_bytes(4) > cfg.pool_bytes(4)
+    assert Config(hidden_size=64, topk=2, max_tokens_per_rank=8).pool_bytes(4) == 0
+
+
+def test_gin_is_gated_at_context_creation():
+    from ep_xpress_b200 import Context
+    cfg = Config(hidden_size=64, topk=2, max_tokens_per_rank=8, transport="host_sm", internode_transport="gin")
+    with pytest.raises(NotImplementedError, match="second node"):
+        Context(None, [0], cfg)
