@@ -1,0 +1,313 @@
+"""Headline benchmark: one MoE layer's expert-parallel communication step.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+
+A step is dispatch -> identity-times-routing-weight expert -> combine of the
+DeepSeek-V3-shaped prefill configuration (hidden 7168 BF16, 256 experts in equal
+contiguous blocks per rank, top-8, 4096 tokens per rank, ids uniform without
+replacement, weights = normalised sigmoid scores), through the public API
+(``Context.dispatch_on_stream`` / ``combine_on_stream`` with a retained workspace).
+Per-GPU work is fixed as N grows (weak scaling); ``value`` is tokens/s of the
+whole job. ``--config decode`` runs the 128-tokens-per-rank shape instead, and
+``--config qwen3`` the hidden-2048 / 128-expert shape the reference publishes
+numbers for.
+
+``--impl reference`` runs the UNMODIFIED reference library installed in
+``baseline/_ref`` through its own public API (``host_sm`` transport) on the same
+shapes with a plain-PyTorch expert, and prints the same JSON line.
+
+Timing: device time by CUDA events around exactly K steps, bracketed by a
+barrier and a device synchronisation on both sides, maximum over ranks. Inputs
+rotate over four pre-staged batches and one step touches several hundred MB, far
+more than the 126 MB L2. The ``e2e`` block repeats the measurement with the
+step's inputs copied from pinned host memory every step (prefetched on a copy
+stream) and a checksum plus ``valid_count`` read back to the host every step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "dispatch+combine µs/MoE layer (p50, max over ranks) and tokens/s, 1/2/4/8 B200"
+SHAPES = {
+    "prefill": dict(model="DeepSeek-V3-shaped MoE layer (communication only)", hidden=7168, experts=256, topk=8,
+                    tokens=4096, weights="sigmoid"),
+    "decode": dict(model="DeepSeek-V3-shaped MoE layer (communication only)", hidden=7168, experts=256, topk=8,
+                   tokens=128, weights="sigmoid"),
+    "qwen3": dict(model="Qwen3-30B-A3B-shaped MoE layer (communication only)", hidden=2048, experts=128, topk=8,
+                  tokens=4096, weights="softmax"),
+}
+# Reference's published dispatch + combine medians at 4096 tokens/rank, hidden 2048, 8 ranks
+# (8x H20D, host-staged PCIe): 3270.70 + 4474.98 us  ->  8 * 4096 tokens per 7745.68 us.
+PUBLISHED_TOKENS_PER_S = {("qwen3", 8): 8 * 4096 / 7745.68e-6}
+
+
+def parse_args():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--config", choices=sorted(SHAPES), default="prefill")
+    parser.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
+    parser.add_argument("--routing", choices=("uniform", "zipf"), default="uniform")
+    parser.add_argument("--no-e2e", action="store_true")
+    return parser.parse_args()
+
+
+def init_distributed(gpus):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != gpus:
+        raise SystemExit(f"--gpus {gpus} does not match WORLD_SIZE {world}; launch with torch.distributed.run")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if "MASTER_PORT" not in os.environ:
+        import socket
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            os.environ["MASTER_PORT"] = str(s.getsockname()[1])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def make_inputs(shape, tokens, world, rank, routing, sets):
+    """Pinned host batches (x, ids, weights) of this rank."""
+    import torch
+    from ep_xpress_b200.utils import workloads
+    batches = []
+    for index in range(sets):
+        if routing == "zipf":
+            ids, w = workloads.zipf_routing(tokens, shape["experts"], shape["topk"], seed=index, rank=rank)
+        else:
+            ids, w = workloads.uniform_routing(tokens, shape["experts"], shape["topk"], seed=index, rank=rank,
+                                               weights=shape["weights"])
+        x = workloads.gaussian_payload(tokens, shape["hidden"], seed=index, rank=rank)
+        batches.append(tuple(t.contiguous().pin_memory() for t in (x, ids, w)))
+    return batches
+
+
+class OursArm:
+    name = "ours"
+
+    def __init__(self, shape, tokens, world, rank, local):
+        import torch.distributed as dist
+        from ep_xpress_b200 import Config, Context, get_nccl_comm_handle
+        from ep_xpress_b200.models import IdentityMoELayer
+        from ep_xpress_b200.utils import workloads
+        self.comm = get_nccl_comm_handle(dist.group.WORLD)
+        cfg = Config(hidden_size=shape["hidden"], topk=shape["topk"], max_tokens_per_rank=tokens,
+                     timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30)
+        self.context = Context(self.comm, workloads.contiguous_expert_map(shape["experts"], world), cfg)
+        self.layer = IdentityMoELayer(self.context)
+
+    def step(self, x, ids, weights, timing=None):
+        return self.layer.forward(x, ids, weights, timing=timing)
+
+    def launches_per_step(self):
+        return 3
+
+    def close(self):
+        self.context.close()
+
+
+class ReferenceArm:
+    """The reference's own library and stock code path; nothing of this repository's runtime."""
+    name = "reference"
+
+    def __init__(self, shape, tokens, world, rank, local):
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+        os.environ.setdefault("MAX_JOBS", "4")
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import ep_xpress
+        per_rank = shape["experts"] // world
+        owners = [e // per_rank for e in range(shape["experts"])]
+        self.comm = ep_xpress.get_nccl_comm_handle(dist.group.WORLD)
+        cfg = ep_xpress.Config(hidden_size=shape["hidden"], topk=shape["topk"], max_tokens_per_rank=tokens,
+                               transport="host_sm", channels=8, timeout_seconds=120.0,
+                               host_pool_budget_bytes=8 << 30)
+        self.context = ep_xpress.Context(nccl_comm=self.comm, expert_to_rank=owners, config=cfg)
+        self.workspace = self.context.create_workspace(world * tokens, tokens)
+        self.torch = torch
+
+    def step(self, x, ids, weights, timing=None):
+        torch = self.torch
+        ep = self.context
+        stream = torch.cuda.current_stream()
+        marks = [mark(stream)] if timing is not None else None
+        batch = ep.dispatch_on_stream(x, ids, weights, workspace=self.workspace)
+        if timing is not None:
+            marks.append(mark(stream))
+        scale = (batch.weights * (batch.local_ids >= 0)).sum(dim=1, keepdim=True)
+        partial = (batch.hidden.float() * scale).to(torch.bfloat16)
+        if timing is not None:
+            marks.append(mark(stream))
+        out = ep.combine_on_stream(partial, batch.handle)
+        if timing is not None:
+            marks.append(mark(stream))
+            timing.append(marks)
+        return out, batch.valid_count
+
+    def launches_per_step(self):
+        return 0
+
+    def close(self):
+        self.context.close()
+
+
+def mark(stream):
+    import torch
+    event = torch.cuda.Event(enable_timing=True)
+    event.record(stream)
+    return event
+
+
+def gather_max(values, world):
+    """Element-wise maximum over ranks of a list of floats."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(values, dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.cpu().tolist()
+
+
+def fenced(world):
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def run(args):
+    import torch
+    from ep_xpress_b200.utils.clocks import ClockSampler
+    rank, world, local = init_distributed(args.gpus)
+    shape = SHAPES[args.config]
+    tokens = shape["tokens"] if args.tokens is None else args.tokens
+    sets = 4
+    host = make_inputs(shape, tokens, world, rank, args.routing, sets)
+    device = [tuple(t.cuda(non_blocking=True) for t in batch) for batch in host]
+    arm = (OursArm if args.impl == "ours" else ReferenceArm)(shape, tokens, world, rank, local)
+    stream = torch.cuda.current_stream()
+
+    # ---- device-timed: inputs resident, rotated ---------------------------------
+    for i in range(args.warmup):
+        arm.step(*device[i % sets])
+    fenced(world)
+    timing = []
+    with ClockSampler(local) as clocks:
+        begin = mark(stream)
+        for i in range(args.steps):
+            arm.step(*device[i % sets], timing=timing)
+        end = mark(stream)
+        fenced(world)
+    total_ms = gather_max([begin.elapsed_time(end)], world)[0]
+    dispatch_us = gather_max([m[0].elapsed_time(m[1]) * 1e3 for m in timing], world)
+    combine_us = gather_max([m[2].elapsed_time(m[3]) * 1e3 for m in timing], world)
+    both_us = [d + c for d, c in zip(dispatch_us, combine_us)]
+    ms_per_step = total_ms / args.steps
+    value = world * tokens / (ms_per_step * 1e-3)
+
+    # ---- end to end: H2D of every step's inputs, D2H of its result -----------------
+    e2e = None
+    if not args.no_e2e:
+        copy_stream = torch.cuda.Stream()
+        staging = [tuple(torch.empty_like(t, device="cuda") for t in host[0]) for _ in range(2)]
+        ready = [torch.cuda.Event() for _ in range(2)]
+        consumed = [torch.cuda.Event() for _ in range(2)]
+        result_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+        h2d_bytes = sum(t.numel() * t.element_size() for t in host[0])
+
+        def prefetch(step):
+            slot = step % 2
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(consumed[slot])
+                for dst, src in zip(staging[slot], host[step % sets]):
+                    dst.copy_(src, non_blocking=True)
+                ready[slot].record(copy_stream)
+
+        def e2e_loop(steps):
+            for slot in range(2):
+                consumed[slot].record(stream)
+            prefetch(0)
+            checksum = 0.0
+            for step in range(steps):
+                slot = step % 2
+                if step + 1 < steps:
+                    prefetch(step + 1)
+                stream.wait_event(ready[slot])
+                out, valid = arm.step(*staging[slot])
+                consumed[slot].record(stream)
+                result = torch.stack([out.float().sum(), valid.float().sum()])
+                result_host.copy_(result, non_blocking=True)
+                stream.synchronize()                     # the host reads this step's result
+                checksum += float(result_host[0])
+            return checksum
+
+        e2e_loop(max(3, args.warmup))
+        fenced(world)
+        begin = mark(stream)
+        e2e_loop(args.steps)
+        end = mark(stream)
+        fenced(world)
+        e2e_ms = gather_max([begin.elapsed_time(end)], world)[0] / args.steps
+        e2e = {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 8}
+
+    published = PUBLISHED_TOKENS_PER_S.get((args.config, world)) if args.tokens is None else None
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / published) if published else None, "dtype": "bf16", "data": "synthetic",
+        "impl": arm.name,
+        "config": {"model": shape["model"], "global_batch": world * tokens, "seq_len": tokens,
+                   "tokens_per_rank": tokens, "hidden": shape["hidden"], "experts": shape["experts"],
+                   "topk": shape["topk"], "routing": args.routing, "parallelism": f"ep{world}",
+                   "l2": "inputs rotate over 4 batches; a step touches far more than the 126 MB L2"},
+        "dispatch_us_p50": statistics.median(dispatch_us), "combine_us_p50": statistics.median(combine_us),
+        "dispatch_combine_us_p50": statistics.median(both_us),
+        "clocks": clocks.summary(), "e2e": e2e,
+        "gpu_launches": arm.launches_per_step() * args.steps,
+    }
+    arm.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    import torch.distributed as dist
+    dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference" and not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "ep_xpress")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"}))
+        return
+    try:
+        run(args)
+    except Exception as error:
+        if args.impl != "reference":
+            raise
+        if int(os.environ.get("RANK", "0")) == 0:
+            reason = f"{type(error).__name__}: {error}".replace("\n", " ")[:300]
+            print(json.dumps({"impl": "reference", "unavailable": reason}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,3 @@
+"""Model-level building blocks driven through the public context API."""
+
+from .synthetic import IdentityMoELayer  # noqa: F401

@@ -1,0 +1,3 @@
+"""Hand-written device operators exposed to users of a context."""
+
+from .expert import scale_rows  # noqa: F401

@@ -64,7 +64,7 @@ class HeapAllocator:
         return sum(end - begin for begin, end in self._free)
 
 
-@dataclass
+@dataclass(repr=False)
 class SlotViews:
     """Tensor views of one rank's slot (no copies; storage is the heap)."""
     hidden: torch.Tensor       # bf16  [capacity, hidden]
@@ -80,7 +80,7 @@ class SlotViews:
     output: torch.Tensor       # bf16  [tokens, hidden]
 
 
-@dataclass
+@dataclass(repr=False)
 class Slot:
     capacity: int
     tokens: int

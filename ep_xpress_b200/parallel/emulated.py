@@ -22,7 +22,7 @@ from ..config import Config
 from .core import Slot, TransportCore
 
 
-@dataclass
+@dataclass(repr=False)
 class EmulatedBatch:
     hidden: torch.Tensor
     local_ids: torch.Tensor
@@ -102,6 +102,9 @@ class EmulatedGroup:
     def __enter__(self):
         return self
 
-    def __exit__(self, *exc):
-        self.close()
+    def __exit__(self, exc_type, exc_value, traceback):
+        # On an exception the heaps stay mapped until the process ends: whoever formats
+        # the error may still print tensors that are views of them.
+        if exc_type is None:
+            self.close()
         return False

@@ -523,17 +523,16 @@ class NVLinkContext(Context):
         return report
 
     # ------------------------------------------------------------------ teardown
-    def _release_resources(self):
+    def _release_resources(self, *, keep_own_heap=False):
         from .. import native as native_loader
         native = native_loader.load()
-        self._core = None if not hasattr(self, "_core") else self._core
         for base in self._peer_bases:
             try:
                 native.heap_release(base)
             except Exception:
                 pass
         self._peer_bases = []
-        if self._heap_base is not None:
+        if self._heap_base is not None and not keep_own_heap:
             try:
                 native.heap_release(self._heap_base)
             except Exception:
@@ -541,16 +540,22 @@ class NVLinkContext(Context):
             self._heap_base = None
 
     def close(self):
-        """Collective on healthy contexts: drain, rendezvous, unmap, free."""
+        """Collective on healthy contexts: drain, rendezvous, unmap, free.
+
+        After a failure there is no rendezvous (a peer may be gone): peer mappings
+        are dropped, but this rank's own heap stays allocated until the process
+        exits, because surviving peers may still store flag words into it.
+        """
         with self._lock:
             if self._closed:
                 return
             self._closed = True
             with torch.cuda.device(self.device):
                 torch.cuda.synchronize(self.device)
-                if self._failed is None:
+                healthy = self._failed is None
+                if healthy:
                     self._comm.barrier()
                 self._pool = []
                 self._workspaces = []
                 self._core = None
-                self._release_resources()
+                self._release_resources(keep_own_heap=not healthy)

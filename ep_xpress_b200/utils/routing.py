@@ -118,8 +118,8 @@ def plan_routes(ids_by_rank, weights_by_rank, expert_to_rank, world_size: int, t
     for ids, _ in cleaned:
         active = ids >= 0
         dest = owner_t[ids.clamp(min=0)]
-        hit = torch.zeros((ids.shape[0], world_size), dtype=torch.bool)
-        hit.scatter_(1, dest, active)       # duplicates collapse: one row per (token, rank)
+        # Duplicates collapse (one row per (token, rank)); a dropped slot never hides an active one.
+        hit = torch.zeros((ids.shape[0], world_size), dtype=torch.int64).scatter_add_(1, dest, active.to(torch.int64)) > 0
         per_source_hits.append(hit)
         masks.append((hit.to(torch.int64) << torch.arange(world_size)).sum(dim=1))
 

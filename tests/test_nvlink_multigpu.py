@@ -1,0 +1,51 @@
+"""End-to-end tests of the NVLink context on real GPUs, one process per GPU over NCCL
+(the reference's tier of spawned multi-GPU tests, e.g. tests/test_host_sm_graph_cuda.py)."""
+
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+from conftest import gpu_count
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu,
+              pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")]
+
+WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "nvlink_worker.py")
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def launch(case, ranks, *extra, timeout=420):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()), WORKER, "--case", case, *extra]
+    result = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert result.returncode == 0, result.stdout[-3000:] + "\n" + result.stderr[-3000:]
+
+
+def ranks_available():
+    return [n for n in (2, 4, 8) if n <= gpu_count()]
+
+
+@pytest.mark.parametrize("ranks", ranks_available())
+def test_replay_cases(ranks):
+    launch("replay", ranks)
+
+
+def test_reverse_order_handles():
+    launch("reverse", min(gpu_count(), 4))
+
+
+def test_cuda_graph_replay_with_changing_routes():
+    launch("graph", min(gpu_count(), 4))
+
+
+def test_undersized_capacity_poisons_the_group_without_hanging():
+    launch("errors", 2)

@@ -68,6 +68,13 @@ def test_dedup_and_order():
     assert plan.dest_rows[0].tolist() == [[0, -1], [1, 0], [-1, -1]]
 
 
+def test_dropped_slot_does_not_hide_an_active_slot_of_the_same_rank():
+    plan = routing.plan_routes([[[0, 1, 2, -1]], []], [[[0.5, 0.25, 0.25, float("nan")]], []], [0, 0, 1, 1], 2, 4)
+    assert plan.dest_masks[0].tolist() == [3]
+    assert plan.received[1].local_ids.tolist() == [[-1, -1, 0, -1]]
+    assert plan.received[1].weights.tolist() == [[0.5, 0.25, 0.25, 0.0]]
+
+
 def test_local_ids_follow_order_of_appearance():
     assert routing.expert_local_ids([1, 0, 1, 1, 0], 2) == [0, 0, 1, 2, 1]
 
