@@ -213,12 +213,14 @@ def run(args):
         arm.step(*device[i % sets])
     fenced(world)
     timing = []
-    with ClockSampler(local) as clocks:
-        begin = mark(stream)
-        for i in range(args.steps):
-            arm.step(*device[i % sets], timing=timing)
-        end = mark(stream)
-        fenced(world)
+    clocks = ClockSampler(local, interval_s=0.002)
+    clocks.__enter__()
+    begin = mark(stream)
+    for i in range(args.steps):
+        arm.step(*device[i % sets], timing=timing)
+    end = mark(stream)
+    fenced(world)
+    clocks.pause()
     total_ms = gather_max([begin.elapsed_time(end)], world)[0]
     dispatch_us = gather_max([m[0].elapsed_time(m[1]) * 1e3 for m in timing], world)
     combine_us = gather_max([m[2].elapsed_time(m[3]) * 1e3 for m in timing], world)
@@ -264,14 +266,17 @@ def run(args):
 
         e2e_loop(max(3, args.warmup))
         fenced(world)
+        clocks.resume()
         begin = mark(stream)
         e2e_loop(args.steps)
         end = mark(stream)
         fenced(world)
+        clocks.pause()
         e2e_ms = gather_max([begin.elapsed_time(end)], world)[0] / args.steps
         e2e = {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 8}
 
+    clocks.__exit__(None, None, None)
     published = PUBLISHED_TOKENS_PER_S.get((args.config, world)) if args.tokens is None else None
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

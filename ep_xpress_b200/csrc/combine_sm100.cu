@@ -86,6 +86,79 @@ __device__ __forceinline__ Chunk<kWords> finish(const float* acc, const Chunk<kW
   return out;
 }
 
+// Reduce one row segment whose contributors' row pointers sit in registers:
+// kPeers rows x kUnroll chunks of loads are issued before the first add; adds
+// then run in ascending rank order per chunk.
+template <int kWords, int kPeers, int kUnroll>
+__device__ __forceinline__ void reduce_rows(const char* const* rp, const char* local_ptr, char* outp, long long b0,
+                                            long long b1, int lane, bool single_round) {
+  constexpr int kChunk = kWords * 4;
+  for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
+    Chunk<kWords> v[kPeers][kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long off = base + static_cast<long long>(u) * 32 * kChunk;
+      if (off < b1) {
+#pragma unroll
+        for (int b = 0; b < kPeers; ++b)
+          if (rp[b] != nullptr) v[b][u] = load_chunk<kWords>(rp[b] + off);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long off = base + static_cast<long long>(u) * 32 * kChunk;
+      if (off < b1) {
+        Chunk<kWords> local;
+        if (local_ptr != nullptr) local = load_chunk<kWords>(local_ptr + off);   // own HBM: short latency
+        float acc[kWords * 2];
+#pragma unroll
+        for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int b = 0; b < kPeers; ++b)
+          if (rp[b] != nullptr) accumulate<kWords>(acc, v[b][u]);
+        store_chunk<kWords>(outp + off, finish<kWords>(acc, local, local_ptr != nullptr, single_round));
+      }
+    }
+  }
+}
+
+// More contributors than registers (groups wider than kPeerBatch ranks): batches of
+// kPeerBatch loads, still added in ascending rank order. Lane j holds the pointer of
+// contributor j (ptr_a) and j + 32 (ptr_b).
+template <int kWords>
+__device__ __noinline__ void reduce_rows_generic(const char* ptr_a, const char* ptr_b, int n, int skip,
+                                                 const char* local_ptr, char* outp, long long b0, long long b1,
+                                                 int lane, bool single_round) {
+  constexpr int kChunk = kWords * 4;
+  for (long long batch = b0; batch < b1; batch += 32ll * kChunk) {   // warp-uniform trip count
+    const long long off = batch + static_cast<long long>(lane) * kChunk;
+    const bool active = off < b1;
+    float acc[kWords * 2];
+#pragma unroll
+    for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
+    for (int j0 = 0; j0 < n; j0 += kPeerBatch) {
+      Chunk<kWords> v[kPeerBatch];
+      bool use[kPeerBatch];
+#pragma unroll
+      for (int b = 0; b < kPeerBatch; ++b) {
+        const int j = j0 + b;
+        const unsigned long long bits =
+            __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(j < 32 ? ptr_a : ptr_b), j & 31);
+        use[b] = active && j < n && j != skip && bits != 0ull;
+        if (use[b]) v[b] = load_chunk<kWords>(reinterpret_cast<const char*>(bits) + off);
+      }
+#pragma unroll
+      for (int b = 0; b < kPeerBatch; ++b)
+        if (use[b]) accumulate<kWords>(acc, v[b]);
+    }
+    if (active) {
+      Chunk<kWords> local;
+      if (local_ptr != nullptr) local = load_chunk<kWords>(local_ptr + off);
+      store_chunk<kWords>(outp + off, finish<kWords>(acc, local, local_ptr != nullptr, single_round));
+    }
+  }
+}
+
 __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
   for (int i = 0; i < n; ++i) mask &= mask - 1;
   return __ffsll(static_cast<long long>(mask)) - 1;
@@ -201,57 +274,20 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
     const char* const local_ptr = reinterpret_cast<const char*>(local_bits);
 
     if (n <= kPeerBatch) {
-      // Common case: every contributor's row pointer sits in a register.
+      // Common case: every contributor's row pointer sits in a register. Few contributors
+      // leave registers free, so more chunks of each row are kept in flight instead: the
+      // pull is bound by NVLink round trips, i.e. by bytes in flight per SM.
       const char* rp[kPeerBatch];
 #pragma unroll
       for (int b = 0; b < kPeerBatch; ++b) {
         const unsigned long long bits = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr_a), b);
         rp[b] = (b < n && b != skip) ? reinterpret_cast<const char*>(bits) : nullptr;
       }
-      for (long long off = b0 + static_cast<long long>(lane) * kChunk; off < b1; off += 32ll * kChunk) {
-        Chunk<kWords> v[kPeerBatch];
-#pragma unroll
-        for (int b = 0; b < kPeerBatch; ++b)
-          if (rp[b] != nullptr) v[b] = load_chunk<kWords>(rp[b] + off);
-        Chunk<kWords> local;
-        if (local_ptr != nullptr) local = load_chunk<kWords>(local_ptr + off);
-        float acc[kWords * 2];
-#pragma unroll
-        for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
-#pragma unroll
-        for (int b = 0; b < kPeerBatch; ++b)
-          if (rp[b] != nullptr) accumulate<kWords>(acc, v[b]);
-        store_chunk<kWords>(outp + off, finish<kWords>(acc, local, local_ptr != nullptr, single_round));
-      }
+      if (n <= 2) reduce_rows<kWords, 2, 4>(rp, local_ptr, outp, b0, b1, lane, single_round);
+      else if (n <= 4) reduce_rows<kWords, 4, 2>(rp, local_ptr, outp, b0, b1, lane, single_round);
+      else reduce_rows<kWords, kPeerBatch, 1>(rp, local_ptr, outp, b0, b1, lane, single_round);
     } else {
-      // More contributors than registers: batches of kPeerBatch, still ascending.
-      for (long long batch = b0; batch < b1; batch += 32ll * kChunk) {   // warp-uniform trip count
-        const long long off = batch + static_cast<long long>(lane) * kChunk;
-        const bool active = off < b1;
-        float acc[kWords * 2];
-#pragma unroll
-        for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
-        for (int j0 = 0; j0 < n; j0 += kPeerBatch) {
-          Chunk<kWords> v[kPeerBatch];
-          bool use[kPeerBatch];
-#pragma unroll
-          for (int b = 0; b < kPeerBatch; ++b) {
-            const int j = j0 + b;
-            const unsigned long long bits =
-                __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(j < 32 ? ptr_a : ptr_b), j & 31);
-            use[b] = active && j < n && j != skip && bits != 0ull;
-            if (use[b]) v[b] = load_chunk<kWords>(reinterpret_cast<const char*>(bits) + off);
-          }
-#pragma unroll
-          for (int b = 0; b < kPeerBatch; ++b)
-            if (use[b]) accumulate<kWords>(acc, v[b]);
-        }
-        if (active) {
-          Chunk<kWords> local;
-          if (local_ptr != nullptr) local = load_chunk<kWords>(local_ptr + off);
-          store_chunk<kWords>(outp + off, finish<kWords>(acc, local, local_ptr != nullptr, single_round));
-        }
-      }
+      reduce_rows_generic<kWords>(ptr_a, ptr_b, n, skip, local_ptr, outp, b0, b1, lane, single_round);
     }
   }
 

@@ -258,22 +258,25 @@ class NVLinkContext(Context):
                 stream.wait_stream(self._last_stream)
             self._last_stream = stream
 
-    def _begin(self, execution, *, same_stream):
-        """Serialise this operation after the context's previous one; returns the capture flag."""
+    def _check_capture(self, *, same_stream):
+        """Lifecycle misuse is a caller error: it is raised before anything is enqueued and
+        does not poison the context."""
+        if not torch.cuda.is_current_stream_capturing():
+            return False
+        if not (self._graph_enabled and self._capture_ready):
+            raise RuntimeError("prepare_graph_capture is required before capturing EP operations")
+        if not same_stream:
+            raise RuntimeError("CUDA Graph capture requires direct-stream operations")
+        return True
+
+    def _begin(self, execution, *, capturing):
+        """Serialise this operation after the context's previous one."""
         self._counter += 1
         if self._counter >= _MAX_EPOCHS:
             raise RuntimeError("operation epochs are exhausted; recreate the context")
-        if torch.cuda.is_current_stream_capturing():
-            if not (self._graph_enabled and self._capture_ready):
-                raise RuntimeError("prepare_graph_capture is required before capturing EP operations")
-            if not same_stream:
-                raise RuntimeError("CUDA Graph capture requires direct-stream operations")
-            self._last_stream = execution
-            return True
-        if self._last_stream is not None and self._last_stream != execution:
+        if not capturing and self._last_stream is not None and self._last_stream != execution:
             execution.wait_stream(self._last_stream)
         self._last_stream = execution
-        return False
 
     # ------------------------------------------------------------------ workspaces
     def create_workspace(self, recv_capacity, local_tokens, *, fused_combine=False):
@@ -368,12 +371,12 @@ class NVLinkContext(Context):
             identity = operation_identity("dispatch", tag) if self.config.diagnostics else 0
             producer = stream or torch.cuda.current_stream(self.device)
             execution = producer if same_stream else self._work_stream
-            capturing_now = torch.cuda.is_current_stream_capturing()
-            if capturing_now and (workspace is None or workspace._generation == 0):
+            capturing = self._check_capture(same_stream=same_stream)
+            if capturing and (workspace is None or workspace._generation == 0):
                 raise RuntimeError("CUDA Graph capture requires a warmed, retained workspace")
             slot = workspace._slot if workspace is not None else self._acquire_pool_slot()
             try:
-                capturing = self._begin(execution, same_stream=same_stream)
+                self._begin(execution, capturing=capturing)
                 if not same_stream:
                     execution.wait_stream(producer)
                 if workspace is not None:
@@ -464,8 +467,9 @@ class NVLinkContext(Context):
             identity = operation_identity("combine", tag, handle.operation) if self.config.diagnostics else 0
             producer = stream or torch.cuda.current_stream(self.device)
             execution = producer if same_stream else self._work_stream
+            capturing = self._check_capture(same_stream=same_stream)
             try:
-                capturing = self._begin(execution, same_stream=same_stream)
+                self._begin(execution, capturing=capturing)
                 if not same_stream:
                     execution.wait_stream(producer)
                 with torch.cuda.stream(execution), torch.no_grad():

@@ -26,6 +26,7 @@ class ClockSampler:
         self.max_mhz = None
         self._interval = interval_s
         self._stop = threading.Event()
+        self._paused = threading.Event()
         self._thread = None
         self._handle = None
         try:
@@ -40,6 +41,9 @@ class ClockSampler:
     def _loop(self):
         nvml = self._nvml
         while not self._stop.is_set():
+            if self._paused.is_set():
+                self._stop.wait(self._interval)
+                continue
             try:
                 self.samples.append(nvml.nvmlDeviceGetClockInfo(self._handle, nvml.NVML_CLOCK_SM))
                 getter = getattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
@@ -57,6 +61,12 @@ class ClockSampler:
             self._thread = threading.Thread(target=self._loop, daemon=True)
             self._thread.start()
         return self
+
+    def pause(self):
+        self._paused.set()
+
+    def resume(self):
+        self._paused.clear()
 
     def __exit__(self, *exc):
         self._stop.set()
