@@ -62,6 +62,8 @@ def parse_args():
     parser.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     parser.add_argument("--routing", choices=("uniform", "zipf"), default="uniform")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--profile-out", default=None,
+                        help="after timing, run 4 profiled steps and write per-CTA phase stamps to PATH.rankR.json")
     return parser.parse_args()
 
 
@@ -277,6 +279,14 @@ def run(args):
                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 8}
 
     clocks.__exit__(None, None, None)
+    if args.profile_out and args.impl == "ours":
+        arm.context.start_combine_profile(16)
+        for i in range(4):
+            arm.step(*device[i % sets])
+        report = arm.context.stop_combine_profile()
+        with open(f"{args.profile_out}.rank{rank}.json", "w") as handle:
+            json.dump(report, handle)
+        fenced(world)
     published = PUBLISHED_TOKENS_PER_S.get((args.config, world)) if args.tokens is None else None
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

@@ -178,7 +178,7 @@ class Config:
         fanout = min(k, w)
         tiles = -(-tokens // _ROUTE_TILE)
         parts = (capacity * h * 2, capacity * k * 8, capacity * k * 4, capacity * 16, capacity * h * 2,
-                 tokens * 8, tokens * fanout * 4, (tiles + 1) * w * 4, w * 8, w * 4, w * 4, w * 4, 64 * 4,
+                 tokens * 8, tokens * fanout * 4, tokens * fanout * 4, (tiles + 1) * w * 4, w * 8, w * 4, w * 4, w * 4, 64 * 4,
                  tokens * h * 2)
         return _round_up(sum(_round_up(p, _SLOT_ALIGN) for p in parts), 4096)
 

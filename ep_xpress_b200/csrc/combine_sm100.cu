@@ -179,7 +179,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
   const SlotLayout sl = slot_layout(op.slot_capacity, op.slot_tokens, H, K, W);
   char* const slot = my_heap + op.slot_off;
   const unsigned long long* const mask_arr = reinterpret_cast<const unsigned long long*>(slot + sl.mask);
-  const int* const dest_rows = reinterpret_cast<const int*>(slot + sl.dest_rows);
+  const int* const dest_rows = reinterpret_cast<const int*>(slot + sl.send_rows);
   const int* const misc = reinterpret_cast<const int*>(slot + sl.misc);
   const int fan = route_fanout(K, W);
   const long long row_bytes = static_cast<long long>(H) * 2;
@@ -188,6 +188,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
   __shared__ int s_need[64];
   __shared__ int s_last;
 
+  profile_stamp(op.profile, 0);
   const unsigned e = ld_volatile_u32(&hdr->comb_epoch) + 1;
   if (tid < W) {
     const unsigned long long off = reinterpret_cast<const unsigned long long*>(slot + sl.peer_off)[tid];
@@ -210,6 +211,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
     }
   }
   __syncthreads();
+  profile_stamp(op.profile, 1);
   if (tid == 0) {
     __threadfence_system();
     const unsigned prev = atomicAdd(&hdr->cdone_count, 1u);
@@ -229,6 +231,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
     ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(flag) >= e; });
   }
   if (!__syncthreads_and(ok)) return;
+  profile_stamp(op.profile, 2);
 
   // ---- C. pull + rank-order reduce ----------------------------------------------------
   const int segs = op.segments;
@@ -293,6 +296,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
 
   // ---- D. retire the epoch ---------------------------------------------------------------
   __syncthreads();
+  profile_stamp(op.profile, 3);
   if (tid == 0) {
     const unsigned prev = atomicAdd(&hdr->cfin_count, 1u);
     if (prev == gridDim.x - 1) {

@@ -63,6 +63,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   char* const slot = my_heap + op.slot_off;
   unsigned long long* const mask_arr = reinterpret_cast<unsigned long long*>(slot + sl.mask);
   int* const dest_rows = reinterpret_cast<int*>(slot + sl.dest_rows);
+  int* const send_rows = reinterpret_cast<int*>(slot + sl.send_rows);
   int* const tile_cnt = reinterpret_cast<int*>(slot + sl.tile_cnt);
   int* const misc = reinterpret_cast<int*>(slot + sl.misc);
   const int fan = route_fanout(K, W);
@@ -74,6 +75,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   __shared__ PeerPlanes s_planes[64];
   __shared__ int s_last;
 
+  profile_stamp(op.profile, 0);
   const unsigned g = ld_volatile_u32(&hdr->disp_epoch) + 1;
   const int par = static_cast<int>(g & 1u);
   const int dirty_prev = misc[kDirtyRows];
@@ -146,7 +148,9 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     __syncthreads();
   }
 
+  profile_stamp(op.profile, 1);
   if (!rank_barrier(c, &hdr->bar_count, gridDim.x, kPhaseDispatch)) return;
+  profile_stamp(op.profile, 2);
 
   // ---- 2. publish my count row ----------------------------------------------
   if (tid < W) {
@@ -175,6 +179,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   for (int i = tid; i < W * 4 && ok; i += kThreads)
     ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(my_addr + i)) == g; });
   if (!__syncthreads_and(ok)) return;
+  profile_stamp(op.profile, 3);
 
   if (tid < W) {
     const int d = tid;
@@ -289,7 +294,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
             inv[1] = t;
           }
         }
-        if (j < n) dest_rows[static_cast<long long>(t) * fan + j] = static_cast<int>(row);
+        if (j < n) send_rows[static_cast<long long>(t) * fan + j] = static_cast<int>(row);
       }
     }
   }
@@ -297,6 +302,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   // ---- 5. signal -----------------------------------------------------------------
   const int valid = s_ok[self] ? s_total[self] : 0;
   __syncthreads();
+  profile_stamp(op.profile, 4);
   if (tid == 0) {
     __threadfence_system();
     const unsigned prev = atomicAdd(&hdr->done_count, 1u);
@@ -320,6 +326,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     }
   }
 
+  profile_stamp(op.profile, 5);
   // ---- 6. receive side -------------------------------------------------------------
   // Rows in [valid, previous valid) held data of the slot's previous operation.
   if (dirty_prev > valid) {
@@ -346,10 +353,12 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       }
     }
   }
+  profile_stamp(op.profile, 6);
   ok = true;
   if (tid < W && s_ok[self] && value_of(ld_relaxed_sys(my_cnt + tid * W + self)) > 0)
     ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return tag_of(ld_acquire_sys(my_done + tid)) == g; });
   __syncthreads_and(ok);
+  profile_stamp(op.profile, 7);
 }
 
 template <typename IdT, bool kVec16>

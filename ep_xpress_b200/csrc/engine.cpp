@@ -101,7 +101,7 @@ class Engine {
     const SlotLayout l = slot_layout(capacity, tokens, hidden_, topk_, world_);
     py::dict d;
     d["hidden"] = l.hidden; d["ids"] = l.ids; d["weights"] = l.weights; d["inverse"] = l.inverse;
-    d["partial"] = l.partial; d["mask"] = l.mask; d["dest_rows"] = l.dest_rows; d["tile_cnt"] = l.tile_cnt;
+    d["partial"] = l.partial; d["mask"] = l.mask; d["dest_rows"] = l.dest_rows; d["send_rows"] = l.send_rows; d["tile_cnt"] = l.tile_cnt;
     d["peer_off"] = l.peer_off; d["peer_cap"] = l.peer_cap; d["send_cnt"] = l.send_cnt; d["recv_cnt"] = l.recv_cnt;
     d["misc"] = l.misc; d["output"] = l.output; d["bytes"] = l.bytes;
     return d;
@@ -150,7 +150,7 @@ class Engine {
                 const std::vector<at::Tensor>& weights, const std::vector<int64_t>& slot_off,
                 const std::vector<int64_t>& capacity, const std::vector<int64_t>& slot_capacity,
                 const std::vector<int64_t>& slot_tokens, uint64_t identity, int ctas, bool zero_padding,
-                int64_t stream) const {
+                int64_t stream, const std::optional<at::Tensor>& profile) const {
     const size_t n = local_ranks_.size();
     TORCH_CHECK(x.size() == n && ids.size() == n && weights.size() == n && slot_off.size() == n &&
                 capacity.size() == n && slot_capacity.size() == n && slot_tokens.size() == n,
@@ -206,13 +206,15 @@ class Engine {
       args.op[i].segments = segments;
       args.op[i].vec16 = vec16 ? 1 : 0;
     }
+    attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
     cuda_check(launch_dispatch(args, static_cast<int>(n), ctas, ids64, vec16, smem, stream_of(stream)),
                "dispatch launch");
   }
 
   void combine(const std::vector<std::optional<at::Tensor>>& partial, const std::vector<at::Tensor>& out,
                const std::vector<int64_t>& slot_off, const std::vector<int64_t>& slot_capacity,
-               const std::vector<int64_t>& slot_tokens, uint64_t identity, int ctas, int64_t stream) const {
+               const std::vector<int64_t>& slot_tokens, uint64_t identity, int ctas, int64_t stream,
+               const std::optional<at::Tensor>& profile) const {
     const size_t n = local_ranks_.size();
     TORCH_CHECK(partial.size() == n && out.size() == n && slot_off.size() == n && slot_capacity.size() == n &&
                 slot_tokens.size() == n, "combine needs one entry per local rank");
@@ -259,6 +261,7 @@ class Engine {
       args.op[i].segments = segments;
       args.op[i].vec16 = vec16 ? 1 : 0;
     }
+    attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
     cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, stream_of(stream)), "combine launch");
   }
 
@@ -330,13 +333,26 @@ class Engine {
   void check_local(int local) const {
     TORCH_CHECK(local >= 0 && static_cast<size_t>(local) < local_ranks_.size(), "local rank index out of range");
   }
-  // Rows are split into segments so that small batches still occupy every warp.
+  // Rows are split into segments of at least 2 KiB (one fully unrolled warp iteration) so
+  // that there are several work items per warp: small batches still occupy every warp and
+  // large ones do not end with a half-empty last round.
   int pick_segments(int64_t tokens, int ctas) const {
     const int64_t warps = static_cast<int64_t>(ctas) * (kThreads / 32);
     const int64_t row_bytes = static_cast<int64_t>(hidden_) * 2;
-    const int64_t max_segments = std::max<int64_t>(1, row_bytes / 1024);
-    const int64_t wanted = (warps + std::max<int64_t>(tokens, 1) - 1) / std::max<int64_t>(tokens, 1);
+    const int64_t max_segments = std::max<int64_t>(1, row_bytes / 2048);
+    const int64_t wanted = (8 * warps + std::max<int64_t>(tokens, 1) - 1) / std::max<int64_t>(tokens, 1);
     return static_cast<int>(std::max<int64_t>(1, std::min(wanted, max_segments)));
+  }
+  // profile: int64 [ranks, ctas, kProfileStamps] on the context device, or nothing.
+  template <typename Assign>
+  void attach_profile(const std::optional<at::Tensor>& profile, int ctas, size_t ranks, Assign assign) const {
+    if (!profile.has_value()) return;
+    const at::Tensor& p = *profile;
+    TORCH_CHECK(p.is_cuda() && p.get_device() == device_ && p.scalar_type() == at::kLong && p.is_contiguous() &&
+                p.numel() >= static_cast<int64_t>(ranks) * ctas * kProfileStamps,
+                "profile must be a contiguous int64 CUDA tensor of at least ranks * ctas * 8 elements");
+    for (size_t i = 0; i < ranks; ++i)
+      assign(i, reinterpret_cast<unsigned long long*>(p.data_ptr<int64_t>()) + i * ctas * kProfileStamps);
   }
 
   int world_;
@@ -358,6 +374,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("MAX_WORLD") = kMaxWorld;
   m.attr("MAX_EMULATED_RANKS") = kMaxEmulatedRanks;
   m.attr("THREADS") = kThreads;
+  m.attr("PROFILE_STAMPS") = kProfileStamps;
   m.def("heap_allocate", [](size_t bytes) { return reinterpret_cast<int64_t>(HeapRegistry::instance().allocate(bytes)); });
   m.def("heap_export", [](int64_t base) { return py::bytes(HeapRegistry::instance().export_handle(reinterpret_cast<void*>(base))); });
   m.def("heap_open", [](const std::string& handle, size_t bytes) {
@@ -383,9 +400,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("slot_reset", &Engine::slot_reset)
       .def("dispatch", &Engine::dispatch, py::arg("x"), py::arg("ids"), py::arg("weights"), py::arg("slot_off"),
            py::arg("capacity"), py::arg("slot_capacity"), py::arg("slot_tokens"), py::arg("identity"),
-           py::arg("ctas"), py::arg("zero_padding"), py::arg("stream"))
+           py::arg("ctas"), py::arg("zero_padding"), py::arg("stream"), py::arg("profile") = py::none())
       .def("combine", &Engine::combine, py::arg("partial"), py::arg("out"), py::arg("slot_off"),
-           py::arg("slot_capacity"), py::arg("slot_tokens"), py::arg("identity"), py::arg("ctas"), py::arg("stream"))
+           py::arg("slot_capacity"), py::arg("slot_tokens"), py::arg("identity"), py::arg("ctas"), py::arg("stream"),
+           py::arg("profile") = py::none())
       .def("scale_rows", &Engine::scale_rows)
       .def("status", &Engine::status)
       .def("poke_u64", &Engine::poke_u64)

@@ -151,6 +151,12 @@ __device__ __forceinline__ bool rank_barrier(const RankCtx& c, unsigned* counter
   return barrier_ok != 0;
 }
 
+// Opt-in phase timestamp of one CTA (thread 0 only); a null buffer costs one predicate.
+__device__ __forceinline__ void profile_stamp(unsigned long long* profile, int index) {
+  if (profile != nullptr && threadIdx.x == 0)
+    profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + index] = global_timer_ns();
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(unsigned short bits) {
   return __uint_as_float(static_cast<unsigned>(bits) << 16);
 }

@@ -29,6 +29,7 @@ constexpr int kThreads = 512;        // threads per CTA of the transport kernels
 constexpr int kRouteTile = kThreads; // tokens routed per CTA iteration
 constexpr int kSlotAlign = 256;      // every sub-buffer starts on a 256-byte boundary
 constexpr int kMaxRouteTiles = 8192; // bound of the per-CTA prefix table
+constexpr int kProfileStamps = 8;    // phase timestamps one CTA records when profiling
 
 // Sticky status codes (same meaning as ep_xpress/host_sm.py:32-38).
 enum Status : int {
@@ -99,7 +100,8 @@ struct SlotLayout {
   size_t partial;    // bf16  [capacity, hidden]
   // rank-local
   size_t mask;       // u64   [tokens]             destination-rank set per token
-  size_t dest_rows;  // i32   [tokens, fanout]     row index at the j-th destination
+  size_t dest_rows;  // i32   [tokens, fanout]     position among this rank's rows for the j-th destination
+  size_t send_rows;  // i32   [tokens, fanout]     final row index at the j-th destination (-1: not sent)
   size_t tile_cnt;   // i32   [tiles, world]       per route tile, rows per destination
   size_t peer_off;   // u64   [world]              slot offset inside each peer's heap
   size_t peer_cap;   // i32   [world]              capacity of each peer's slot
@@ -129,6 +131,7 @@ EPX_HD SlotLayout slot_layout(long long capacity, long long tokens, int hidden, 
   l.partial = take(c * h * 2);
   l.mask = take(t * 8);
   l.dest_rows = take(t * static_cast<size_t>(route_fanout(topk, world)) * 4);
+  l.send_rows = take(t * static_cast<size_t>(route_fanout(topk, world)) * 4);
   l.tile_cnt = take(static_cast<size_t>(route_tiles(static_cast<int>(tokens)) + 1) * w * 4);
   l.peer_off = take(w * 8);
   l.peer_cap = take(w * 4);
@@ -163,6 +166,7 @@ struct DispatchOp {
   const float* weights;   // f32 [tokens, topk]
   unsigned long long slot_off;
   unsigned long long identity;  // diagnostics: hash of (phase, tag); 0 when off
+  unsigned long long* profile;  // null, or [ctas, kProfileStamps] globaltimer stamps of this launch
   int tokens;
   int capacity;           // row bound of this operation (<= slot_capacity)
   int slot_capacity;      // capacity the slot was laid out for
@@ -180,6 +184,7 @@ struct CombineOp {
   void* out;              // bf16 [tokens, hidden]
   unsigned long long slot_off;
   unsigned long long identity;
+  unsigned long long* profile;  // null, or [ctas, kProfileStamps] globaltimer stamps of this launch
   int tokens;
   int slot_capacity;
   int slot_tokens;

@@ -38,16 +38,27 @@ __global__ void __launch_bounds__(256) scale_rows_kernel(const unsigned short* _
     const unsigned short* src = hidden + row * hidden_size;
     unsigned short* dst = partial + row * hidden_size;
     if (vec) {
-      for (int i = lane * 8; i < hidden_size; i += 32 * 8) {
-        uint4 v = *reinterpret_cast<const uint4*>(src + i);
-        unsigned* w = reinterpret_cast<unsigned*>(&v);
+      constexpr int kUnroll = 4;   // 64 bytes per lane in flight: the kernel is a pure HBM stream
+      for (int base = lane * 8; base < hidden_size; base += 32 * 8 * kUnroll) {
+        uint4 v[kUnroll];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float lo = __fmul_rn(__uint_as_float(w[q] << 16), scale);
-          const float hi = __fmul_rn(__uint_as_float(w[q] & 0xffff0000u), scale);
-          w[q] = static_cast<unsigned>(float_to_bf16_bits(lo)) | (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+        for (int u = 0; u < kUnroll; ++u) {
+          const int i = base + u * 256;
+          if (i < hidden_size) v[u] = *reinterpret_cast<const uint4*>(src + i);
         }
-        *reinterpret_cast<uint4*>(dst + i) = v;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int i = base + u * 256;
+          if (i >= hidden_size) continue;
+          unsigned* w = reinterpret_cast<unsigned*>(&v[u]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float lo = __fmul_rn(__uint_as_float(w[q] << 16), scale);
+            const float hi = __fmul_rn(__uint_as_float(w[q] & 0xffff0000u), scale);
+            w[q] = static_cast<unsigned>(float_to_bf16_bits(lo)) | (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+          }
+          *reinterpret_cast<uint4*>(dst + i) = v[u];
+        }
       }
     } else {
       for (int i = lane; i < hidden_size; i += 32)
@@ -80,7 +91,7 @@ cudaError_t launch_scale_rows(const void* hidden, const long long* local_ids, co
                               const int* valid_count, const float* factors, int num_factors, void* partial,
                               int capacity, int hidden_size, int topk, cudaStream_t stream) {
   if (capacity <= 0) return cudaSuccess;
-  const int ctas = capacity < 8 * 148 * 4 ? (capacity + 7) / 8 : 148 * 4;
+  const int ctas = capacity < 8 * 148 * 8 ? (capacity + 7) / 8 : 148 * 8;
   scale_rows_kernel<<<ctas, 256, 0, stream>>>(static_cast<const unsigned short*>(hidden), local_ids, weights,
                                               valid_count, factors, num_factors,
                                               static_cast<unsigned short*>(partial), capacity, hidden_size, topk);

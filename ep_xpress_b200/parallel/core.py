@@ -74,7 +74,7 @@ class SlotViews:
     partial: torch.Tensor      # bf16  [capacity, hidden]
     count: torch.Tensor        # int32 [1]  valid_count
     mask: torch.Tensor         # int64 [tokens]  destination-rank set per local token
-    dest_rows: torch.Tensor    # int32 [tokens, fanout]
+    dest_rows: torch.Tensor    # int32 [tokens, fanout]  row index at the j-th destination rank
     send_counts: torch.Tensor  # int32 [world]
     recv_counts: torch.Tensor  # int32 [world]
     output: torch.Tensor       # bf16  [tokens, hidden]
@@ -130,7 +130,7 @@ class TransportCore:
                 partial=view("partial", (capacity, self.hidden), torch.bfloat16),
                 count=view("misc", (1,), torch.int32),
                 mask=view("mask", (tokens,), torch.int64),
-                dest_rows=view("dest_rows", (tokens, fanout), torch.int32),
+                dest_rows=view("send_rows", (tokens, fanout), torch.int32),
                 send_counts=view("send_cnt", (self.world,), torch.int32),
                 recv_counts=view("recv_cnt", (self.world,), torch.int32),
                 output=view("output", (tokens, self.hidden), torch.bfloat16),
@@ -146,29 +146,30 @@ class TransportCore:
 
     # ---- launches --------------------------------------------------------------
     def pick_ctas(self, tokens: int, budget: Optional[int] = None) -> int:
-        """CTAs per rank: enough warps for every (token, 1 KiB row segment), within the budget."""
+        """CTAs per rank: enough warps for every (token, 2 KiB row segment), within the budget."""
         budget = self.max_ctas if budget is None else max(1, min(budget, self.max_ctas))
-        segments = max(1, self.hidden * 2 // 1024)
+        segments = max(1, self.hidden * 2 // 2048)
         wanted = -(-max(tokens, 1) * segments // (self.native.THREADS // 32))
         return max(1, min(budget, wanted))
 
-    def dispatch(self, slot: Slot, xs, ids, weights, capacities, *, identity=0, ctas=None, stream=None):
+    def dispatch(self, slot: Slot, xs, ids, weights, capacities, *, identity=0, ctas=None, stream=None,
+                 profile=None):
         stream = stream or torch.cuda.current_stream(self.device)
         tokens = max(x.shape[0] for x in xs)
         ctas = self.pick_ctas(tokens) if ctas is None else ctas
         n = len(self.local_ranks)
         self.engine.dispatch(list(xs), list(ids), list(weights), slot.offsets, list(capacities),
                              [slot.capacity] * n, [slot.tokens] * n, identity, ctas,
-                             bool(self.config.zero_padding), stream.cuda_stream)
+                             bool(self.config.zero_padding), stream.cuda_stream, profile)
         self.launches += 1
 
-    def combine(self, slot: Slot, partials, outs, *, identity=0, ctas=None, stream=None):
+    def combine(self, slot: Slot, partials, outs, *, identity=0, ctas=None, stream=None, profile=None):
         stream = stream or torch.cuda.current_stream(self.device)
         tokens = max(out.shape[0] for out in outs)
         ctas = self.pick_ctas(tokens) if ctas is None else ctas
         n = len(self.local_ranks)
         self.engine.combine(list(partials), list(outs), slot.offsets, [slot.capacity] * n, [slot.tokens] * n,
-                            identity, ctas, stream.cuda_stream)
+                            identity, ctas, stream.cuda_stream, profile)
         self.launches += 1
 
     def scale_rows(self, hidden, local_ids, weights, valid_count, factors, partial, stream=None):

@@ -389,12 +389,14 @@ class NVLinkContext(Context):
                     x = x.clone()
                 budget = max(1, self._core.max_ctas * channels // self.effective_channels)
                 ctas = self._core.pick_ctas(x.shape[0], budget)
+                profile = None if self._profile is None else self._profile.slice_for(
+                    "dispatch", self._counter, tag, x.shape[0], capacity, ctas)
                 with torch.cuda.stream(execution), torch.no_grad():
                     if not same_stream:
                         for tensor in (x, ids, weights):
                             tensor.record_stream(execution)
                     self._core.dispatch(slot, [x], [ids], [weights], [capacity], identity=identity, ctas=ctas,
-                                        stream=execution)
+                                        stream=execution, profile=profile)
             except BaseException as error:
                 self._abort(error)
                 raise
@@ -407,8 +409,6 @@ class NVLinkContext(Context):
             handle = RouteHandle(self._id, self._counter, route, x.shape[0], capacity, tag)
             batch = DispatchBatch(views.hidden[:capacity], views.local_ids[:capacity], views.weights[:capacity],
                                   handle, views.count)
-            if self._profile is not None:
-                self._profile.record("dispatch", handle, tag, execution)
             if same_stream:
                 return batch
             return self._finish(batch, workspace)
@@ -481,14 +481,15 @@ class NVLinkContext(Context):
                                              dtype=torch.bfloat16, device=self.device)
                     else:
                         output = workspace.output
+                    profile = None if self._profile is None else self._profile.slice_for(
+                        "combine", handle.operation, tag, handle.local_token_count, handle.received_count,
+                        route.ctas)
                     self._core.combine(route.slot, [source], [output], identity=identity, ctas=route.ctas,
-                                       stream=execution)
+                                       stream=execution, profile=profile)
             except BaseException as error:
                 self._abort(error)
                 raise
             handle._consumed = True
-            if self._profile is not None:
-                self._profile.record("combine", handle, tag, execution)
             if workspace is None:
                 route.slot.busy = False
             if same_stream:
@@ -517,7 +518,11 @@ class NVLinkContext(Context):
             if self._profile is None:
                 raise RuntimeError("no profile is running")
             profile, self._profile = self._profile, None
-            self._last_profile = profile.finish()
+            with torch.cuda.device(self.device):
+                self._work_stream.synchronize()
+                if self._last_stream is not None:
+                    self._last_stream.synchronize()
+                self._last_profile = profile.finish()
             return self._last_profile
 
     def read_combine_profile(self):
