@@ -177,7 +177,8 @@ class Config:
         h, k, w = self.hidden_size, self.topk, world_size
         fanout = min(k, w)
         tiles = -(-tokens // _ROUTE_TILE)
-        parts = (capacity * h * 2, capacity * k * 8, capacity * k * 4, capacity * 16, capacity * h * 2,
+        parts = (capacity * h * 2, capacity * k * 8, capacity * k * 4, capacity * 16, capacity * 4,
+                 tokens * fanout * h * 2, capacity * h * 2,
                  tokens * 8, tokens * fanout * 4, tokens * fanout * 4, (tiles + 1) * w * 4, w * 8, w * 4, w * 4, w * 4, 64 * 4,
                  tokens * h * 2)
         return _round_up(sum(_round_up(p, _SLOT_ALIGN) for p in parts), 4096)

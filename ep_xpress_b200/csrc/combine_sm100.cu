@@ -1,6 +1,8 @@
-// Fused expert-parallel combine for sm_100a: every source rank PULLS the
-// already-weighted partial rows of its tokens from the ranks that computed them
-// (peer loads over NVLink) and reduces them in one pass:
+// Fused expert-parallel combine for sm_100a. Every expert rank PUSHES its
+// already-weighted partial rows straight into the staging plane of the rank that
+// owns the token (peer stores over NVLink, the direction that runs at link
+// speed; peer loads do not), signals, and every source rank then reduces its
+// tokens in one pass:
 //
 //   out[t] = bf16( float( bf16( sum_{r != self, ascending r} float(partial_r[t]) ) )
 //                  + float(partial_self[t]) )
@@ -12,18 +14,23 @@
 // :1846-1895). RankCtx::single_round selects the multi-node variant instead:
 // one FP32 accumulation over all contributing ranks in rank order and a single
 // rounding (ep_xpress/csrc/gin.cu:226-246). Arrival order never changes the
-// arithmetic: loads of several peers are in flight together but are added in
-// program order.
+// arithmetic: a token's contributions sit at fixed staging rows (token * fanout
+// + j, j-th destination rank ascending) and are added in that order.
 //
-// There is no receive staging plane [world, tokens, hidden] and no separate
-// reduce launch (reference: host_sm.cu:1212-1468 followed by :592-607).
-// Protocol: (A) if the expert output is a caller tensor it is copied into the
-// slot's peer-visible partial plane; the last CTA then publishes the monotone
-// combine epoch to every peer; (B) wait, bounded, for the epoch of exactly the
-// peers this rank sent rows to; (C) reduce; (D) the last CTA retires the epoch.
-// No trailing handshake is needed: a peer's partial plane is only rewritten
-// after a later dispatch on the same slot, which cannot complete before this
-// rank has entered that dispatch, i.e. finished this combine.
+// One launch replaces the reference's zero-fill, pair transport and reduce
+// launches (host_sm.cu:559-590, :1212-1468, :592-607). Protocol:
+//   A. push    work items (received row, row segment) claimed from a local counter:
+//              rows whose source is a peer are stored to that peer's staging plane
+//              at the return slot the dispatch recorded next to the row;
+//   B. signal  the last CTA publishes the monotone combine epoch to every peer
+//              after a system fence;
+//   C. wait    bounded, for the epoch of exactly the peers this rank sent rows to;
+//   D. reduce  work items (token, segment): staging rows and the local partial row
+//              are read from this GPU's own memory and reduced in rank order;
+//   E. retire  the last CTA advances the device epoch.
+// No trailing handshake is needed: a staging plane is only rewritten by the combine
+// of a later dispatch on the same slot, which cannot complete before this rank has
+// entered that dispatch, i.e. finished this reduce.
 #include "epx_device.cuh"
 #include "epx_launch.h"
 
@@ -31,7 +38,6 @@ namespace epx {
 namespace {
 
 constexpr unsigned kPhaseCombine = 2;
-constexpr int kWarps = kThreads / 32;
 constexpr int kPeerBatch = 8;   // peer rows whose loads are in flight together
 
 template <int kWords>
@@ -47,6 +53,18 @@ __device__ __forceinline__ Chunk<kWords> load_chunk(const char* p) {
     c.w[0] = v.x; c.w[1 % kWords] = v.y; c.w[2 % kWords] = v.z; c.w[3 % kWords] = v.w;
   } else {
     c.w[0] = ld_payload4(p);
+  }
+  return c;
+}
+
+template <int kWords>
+__device__ __forceinline__ Chunk<kWords> load_local_chunk(const char* p) {
+  Chunk<kWords> c;
+  if (kWords == 4) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    c.w[0] = v.x; c.w[1 % kWords] = v.y; c.w[2 % kWords] = v.z; c.w[3 % kWords] = v.w;
+  } else {
+    c.w[0] = *reinterpret_cast<const unsigned*>(p);
   }
   return c;
 }
@@ -168,10 +186,11 @@ template <bool kVec16>
 __device__ __forceinline__ void combine_body(const CombineOp& op) {
   constexpr int kWords = kVec16 ? 4 : 1;
   constexpr int kChunk = kWords * 4;
+  constexpr int kUnroll = 4;
   const RankCtx& c = *op.ctx;
   const int W = c.world, self = c.rank, H = c.hidden, K = c.topk;
   const bool single_round = c.single_round != 0;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31;
   const int T = op.tokens;
   char* const my_heap = c.heap[self];
   CtrlHeader* const hdr = header_of(my_heap);
@@ -179,12 +198,16 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
   const SlotLayout sl = slot_layout(op.slot_capacity, op.slot_tokens, H, K, W);
   char* const slot = my_heap + op.slot_off;
   const unsigned long long* const mask_arr = reinterpret_cast<const unsigned long long*>(slot + sl.mask);
-  const int* const dest_rows = reinterpret_cast<const int*>(slot + sl.send_rows);
+  const int* const send_rows = reinterpret_cast<const int*>(slot + sl.send_rows);
+  const long long* const inverse = reinterpret_cast<const long long*>(slot + sl.inverse);
+  const int* const ret = reinterpret_cast<const int*>(slot + sl.ret);
   const int* const misc = reinterpret_cast<const int*>(slot + sl.misc);
+  const char* const partial = reinterpret_cast<const char*>(op.partial);
+  const char* const staging = slot + sl.staging;
   const int fan = route_fanout(K, W);
   const long long row_bytes = static_cast<long long>(H) * 2;
 
-  __shared__ const char* s_part[64];
+  __shared__ char* s_stage[64];
   __shared__ int s_need[64];
   __shared__ int s_last;
 
@@ -194,24 +217,50 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
     const unsigned long long off = reinterpret_cast<const unsigned long long*>(slot + sl.peer_off)[tid];
     const int cap = reinterpret_cast<const int*>(slot + sl.peer_cap)[tid];
     const SlotLayout pl = slot_layout(cap, 0, H, K, W);
-    s_part[tid] = c.heap[tid] + off + pl.partial;
+    s_stage[tid] = c.heap[tid] + off + pl.staging;
     s_need[tid] = (tid != self && reinterpret_cast<const int*>(slot + sl.send_cnt)[tid] > 0) ? 1 : 0;
   }
-  const int valid = misc[kValidCount];
+  const int valid = min(misc[kValidCount], op.partial_rows);
+  const int segs = op.segments;
+  const long long seg_bytes = align_up((row_bytes + segs - 1) / segs, 32 * kChunk * kUnroll);
+  __syncthreads();
 
-  // ---- A. make my partial rows peer-visible -------------------------------------
-  if (op.partial != nullptr) {
-    const long long chunks = static_cast<long long>(valid) * row_bytes / kChunk;
-    const char* src = reinterpret_cast<const char*>(op.partial);
-    char* dst = slot + sl.partial;
-    const long long threads = static_cast<long long>(gridDim.x) * kThreads;
-    for (long long i = static_cast<long long>(blockIdx.x) * kThreads + tid; i < chunks; i += threads) {
-      if (kVec16) *reinterpret_cast<uint4*>(dst + i * 16) = *reinterpret_cast<const uint4*>(src + i * 16);
-      else *reinterpret_cast<unsigned*>(dst + i * 4) = *reinterpret_cast<const unsigned*>(src + i * 4);
+  // ---- A. push my rows to the ranks that own the tokens ---------------------------
+  {
+    const long long items = static_cast<long long>(valid) * segs;
+    while (true) {
+      unsigned claimed = 0;
+      if (lane == 0) claimed = atomicAdd(&hdr->cwork_push, 1u);
+      const long long item = __shfl_sync(0xffffffffu, claimed, 0);
+      if (item >= items) break;
+      const long long row = item / segs;
+      const int seg = static_cast<int>(item % segs);
+      const int source = static_cast<int>(inverse[row * 2]);
+      if (source == self || source < 0 || source >= W) continue;
+      const long long back = ret[row];
+      const char* src = partial + row * row_bytes;
+      char* dst = s_stage[source] + back * row_bytes;
+      const long long b0 = seg * seg_bytes;
+      const long long b1 = min(row_bytes, b0 + seg_bytes);
+      for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
+        Chunk<kWords> v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const long long off = base + static_cast<long long>(u) * 32 * kChunk;
+          if (off < b1) v[u] = load_local_chunk<kWords>(src + off);
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const long long off = base + static_cast<long long>(u) * 32 * kChunk;
+          if (off < b1) store_chunk<kWords>(dst + off, v[u]);
+        }
+      }
     }
   }
   __syncthreads();
   profile_stamp(op.profile, 1);
+
+  // ---- B. signal ------------------------------------------------------------------------
   if (tid == 0) {
     __threadfence_system();
     const unsigned prev = atomicAdd(&hdr->cdone_count, 1u);
@@ -224,7 +273,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
     st_release_sys(flag, static_cast<unsigned long long>(e));
   }
 
-  // ---- B. wait for the peers I pull from --------------------------------------------
+  // ---- C. wait for the peers that push to me ----------------------------------------------
   bool ok = true;
   if (tid < W && s_need[tid]) {
     const unsigned long long* flag = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready) + tid;
@@ -233,68 +282,72 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
   if (!__syncthreads_and(ok)) return;
   profile_stamp(op.profile, 2);
 
-  // ---- C. pull + rank-order reduce ----------------------------------------------------
-  const int segs = op.segments;
-  const long long seg_bytes = align_up((row_bytes + segs - 1) / segs, 32 * kChunk);
-  const long long items = static_cast<long long>(T) * segs;
-  const long long total_warps = static_cast<long long>(gridDim.x) * kWarps;
-  for (long long item = static_cast<long long>(blockIdx.x) * kWarps + warp; item < items; item += total_warps) {
-    const int t = static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
-    const unsigned long long m = mask_arr[t];
-    const int n = __popcll(m);
-    const long long b0 = seg * seg_bytes;
-    const long long b1 = min(row_bytes, b0 + seg_bytes);
-    char* const outp = reinterpret_cast<char*>(op.out) + static_cast<long long>(t) * row_bytes;
+  // ---- D. rank-order reduce from local memory -----------------------------------------------
+  {
+    const long long items = static_cast<long long>(T) * segs;
+    while (true) {
+      unsigned claimed = 0;
+      if (lane == 0) claimed = atomicAdd(&hdr->cwork_reduce, 1u);
+      const long long item = __shfl_sync(0xffffffffu, claimed, 0);
+      if (item >= items) break;
+      const int t = static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
+      const unsigned long long m = mask_arr[t];
+      const int n = __popcll(m);
+      const long long b0 = seg * seg_bytes;
+      const long long b1 = min(row_bytes, b0 + seg_bytes);
+      char* const outp = reinterpret_cast<char*>(op.out) + static_cast<long long>(t) * row_bytes;
 
-    // Lane j (and j + 32) resolves the j-th contributor in ascending rank order.
-    const char* ptr_a = nullptr;
-    const char* ptr_b = nullptr;
-    int self_index = -1;
-    {
-      bool is_self = false;
-      if (lane < n) {
-        const int d = nth_set_bit(m, lane);
-        const int row = dest_rows[static_cast<long long>(t) * fan + lane];
-        if (row >= 0) ptr_a = s_part[d] + static_cast<long long>(row) * row_bytes;
-        is_self = (d == self);
+      // Lane j (and j + 32) resolves the j-th contributor in ascending rank order.
+      const char* ptr_a = nullptr;
+      const char* ptr_b = nullptr;
+      int self_index = -1;
+      {
+        bool is_self = false;
+        if (lane < n) {
+          const int d = nth_set_bit(m, lane);
+          const int row = send_rows[static_cast<long long>(t) * fan + lane];
+          is_self = (d == self);
+          if (row >= 0)
+            ptr_a = is_self ? partial + static_cast<long long>(row) * row_bytes
+                            : staging + (static_cast<long long>(t) * fan + lane) * row_bytes;
+        }
+        const unsigned vote_a = __ballot_sync(0xffffffffu, is_self);
+        is_self = false;
+        if (lane + 32 < n) {
+          const int d = nth_set_bit(m, lane + 32);
+          const int row = send_rows[static_cast<long long>(t) * fan + lane + 32];
+          is_self = (d == self);
+          if (row >= 0)
+            ptr_b = is_self ? partial + static_cast<long long>(row) * row_bytes
+                            : staging + (static_cast<long long>(t) * fan + lane + 32) * row_bytes;
+        }
+        const unsigned vote_b = __ballot_sync(0xffffffffu, is_self);
+        if (vote_a) self_index = __ffs(vote_a) - 1;
+        else if (vote_b) self_index = 32 + __ffs(vote_b) - 1;
       }
-      const unsigned vote_a = __ballot_sync(0xffffffffu, is_self);
-      is_self = false;
-      if (lane + 32 < n) {
-        const int d = nth_set_bit(m, lane + 32);
-        const int row = dest_rows[static_cast<long long>(t) * fan + lane + 32];
-        if (row >= 0) ptr_b = s_part[d] + static_cast<long long>(row) * row_bytes;
-        is_self = (d == self);
-      }
-      const unsigned vote_b = __ballot_sync(0xffffffffu, is_self);
-      if (vote_a) self_index = __ffs(vote_a) - 1;
-      else if (vote_b) self_index = 32 + __ffs(vote_b) - 1;
-    }
-    const int skip = single_round ? -1 : self_index;
-    const unsigned long long local_bits =
-        (self_index < 0 || single_round) ? 0ull
-        : __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(self_index < 32 ? ptr_a : ptr_b), self_index & 31);
-    const char* const local_ptr = reinterpret_cast<const char*>(local_bits);
+      const int skip = single_round ? -1 : self_index;
+      const unsigned long long local_bits =
+          (self_index < 0 || single_round) ? 0ull
+          : __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(self_index < 32 ? ptr_a : ptr_b), self_index & 31);
+      const char* const local_ptr = reinterpret_cast<const char*>(local_bits);
 
-    if (n <= kPeerBatch) {
-      // Common case: every contributor's row pointer sits in a register. Few contributors
-      // leave registers free, so more chunks of each row are kept in flight instead: the
-      // pull is bound by NVLink round trips, i.e. by bytes in flight per SM.
-      const char* rp[kPeerBatch];
+      if (n <= kPeerBatch) {
+        // Common case: every contributor's row pointer sits in a register.
+        const char* rp[kPeerBatch];
 #pragma unroll
-      for (int b = 0; b < kPeerBatch; ++b) {
-        const unsigned long long bits = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr_a), b);
-        rp[b] = (b < n && b != skip) ? reinterpret_cast<const char*>(bits) : nullptr;
+        for (int b = 0; b < kPeerBatch; ++b) {
+          const unsigned long long bits = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr_a), b);
+          rp[b] = (b < n && b != skip) ? reinterpret_cast<const char*>(bits) : nullptr;
+        }
+        if (n <= 2) reduce_rows<kWords, 2, 4>(rp, local_ptr, outp, b0, b1, lane, single_round);
+        else reduce_rows<kWords, kPeerBatch, 1>(rp, local_ptr, outp, b0, b1, lane, single_round);
+      } else {
+        reduce_rows_generic<kWords>(ptr_a, ptr_b, n, skip, local_ptr, outp, b0, b1, lane, single_round);
       }
-      if (n <= 2) reduce_rows<kWords, 2, 4>(rp, local_ptr, outp, b0, b1, lane, single_round);
-      else if (n <= 4) reduce_rows<kWords, 4, 2>(rp, local_ptr, outp, b0, b1, lane, single_round);
-      else reduce_rows<kWords, kPeerBatch, 1>(rp, local_ptr, outp, b0, b1, lane, single_round);
-    } else {
-      reduce_rows_generic<kWords>(ptr_a, ptr_b, n, skip, local_ptr, outp, b0, b1, lane, single_round);
     }
   }
 
-  // ---- D. retire the epoch ---------------------------------------------------------------
+  // ---- E. retire the epoch ---------------------------------------------------------------
   __syncthreads();
   profile_stamp(op.profile, 3);
   if (tid == 0) {
@@ -302,6 +355,8 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
     if (prev == gridDim.x - 1) {
       hdr->cdone_count = 0;
       hdr->cfin_count = 0;
+      hdr->cwork_push = 0;
+      hdr->cwork_reduce = 0;
       hdr->comb_epoch = e;
       __threadfence();
     }

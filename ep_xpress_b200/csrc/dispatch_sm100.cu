@@ -38,6 +38,7 @@ struct PeerPlanes {
   char* ids;
   char* weights;
   char* inverse;
+  char* ret;
 };
 
 template <typename IdT>
@@ -199,6 +200,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     s_planes[d].ids = peer_slot + pl.ids;
     s_planes[d].weights = peer_slot + pl.weights;
     s_planes[d].inverse = peer_slot + pl.inverse;
+    s_planes[d].ret = peer_slot + pl.ret;
     s_off[d] = off;
     s_total[d] = total;
     s_ok[d] = (total <= bound && bound <= layout_cap) ? 1 : 0;
@@ -222,8 +224,13 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   const int segs = op.segments;
   const long long seg_bytes = align_up((row_bytes + segs - 1) / segs, 32 * kChunk);
   const long long items = static_cast<long long>(T) * segs;
-  const long long total_warps = static_cast<long long>(gridDim.x) * kWarps;
-  for (long long item = static_cast<long long>(blockIdx.x) * kWarps + warp; item < items; item += total_warps) {
+  // Work items are claimed from a rank-local counter: SMs differ in how fast their
+  // stores drain towards NVLink, and a static split leaves the fast ones idle.
+  while (true) {
+    unsigned claimed = 0;
+    if (lane == 0) claimed = atomicAdd(&hdr->work_next, 1u);
+    const long long item = __shfl_sync(0xffffffffu, claimed, 0);
+    if (item >= items) break;
     const int t = static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
     const unsigned long long m = mask_arr[t];
     if (!m) continue;
@@ -292,6 +299,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
             long long* inv = reinterpret_cast<long long*>(s_planes[d2].inverse) + r2 * 2;
             inv[0] = self;
             inv[1] = t;
+            reinterpret_cast<int*>(s_planes[d2].ret)[r2] = t * fan + j0 + jj;
           }
         }
         if (j < n) send_rows[static_cast<long long>(t) * fan + j] = static_cast<int>(row);
@@ -321,6 +329,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       misc[kDirtyRows] = valid;
       hdr->bar_count = 0;
       hdr->done_count = 0;
+      hdr->work_next = 0;
       hdr->disp_epoch = g;
       __threadfence();
     }

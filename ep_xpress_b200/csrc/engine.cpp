@@ -101,7 +101,7 @@ class Engine {
     const SlotLayout l = slot_layout(capacity, tokens, hidden_, topk_, world_);
     py::dict d;
     d["hidden"] = l.hidden; d["ids"] = l.ids; d["weights"] = l.weights; d["inverse"] = l.inverse;
-    d["partial"] = l.partial; d["mask"] = l.mask; d["dest_rows"] = l.dest_rows; d["send_rows"] = l.send_rows; d["tile_cnt"] = l.tile_cnt;
+    d["partial"] = l.partial; d["ret"] = l.ret; d["staging"] = l.staging; d["mask"] = l.mask; d["dest_rows"] = l.dest_rows; d["send_rows"] = l.send_rows; d["tile_cnt"] = l.tile_cnt;
     d["peer_off"] = l.peer_off; d["peer_cap"] = l.peer_cap; d["send_cnt"] = l.send_cnt; d["recv_cnt"] = l.recv_cnt;
     d["misc"] = l.misc; d["output"] = l.output; d["bytes"] = l.bytes;
     return d;
@@ -222,7 +222,7 @@ class Engine {
     CombineArgs args;
     std::memset(&args, 0, sizeof(args));
     bool vec16 = hidden_ % 8 == 0;
-    int64_t max_tokens = 1;
+    int64_t max_tokens = 1, max_rows = 1;
     for (size_t i = 0; i < n; ++i) {
       TORCH_CHECK(out[i].is_cuda() && out[i].get_device() == device_ && out[i].scalar_type() == at::kBFloat16 &&
                   out[i].dim() == 2 && out[i].size(1) == hidden_ && out[i].is_contiguous(),
@@ -240,21 +240,22 @@ class Engine {
       op.slot_tokens = static_cast<int>(slot_tokens[i]);
       if (reinterpret_cast<uintptr_t>(op.out) % 16 != 0) vec16 = false;
       TORCH_CHECK(reinterpret_cast<uintptr_t>(op.out) % 4 == 0, "combine output must be 4-byte aligned");
-      if (partial[i].has_value()) {
+      TORCH_CHECK(partial[i].has_value(), "combine needs this rank's partial tensor");
+      {
         const at::Tensor& p = *partial[i];
         TORCH_CHECK(p.is_cuda() && p.get_device() == device_ && p.scalar_type() == at::kBFloat16 && p.dim() == 2 &&
                     p.size(1) == hidden_ && p.is_contiguous(),
                     "partial must be contiguous BF16 [rows, hidden] on the context device");
         TORCH_CHECK(p.size(0) <= slot_capacity[i], "partial has more rows than the dispatch capacity");
-        char* plane = own_heap_[i] + slot_off[i] + l.partial;
-        if (p.data_ptr() != static_cast<void*>(plane)) {
-          op.partial = p.data_ptr();
-          TORCH_CHECK(reinterpret_cast<uintptr_t>(op.partial) % 4 == 0, "partial must be 4-byte aligned");
-          if (reinterpret_cast<uintptr_t>(op.partial) % 16 != 0) vec16 = false;
-        }
+        op.partial = p.data_ptr();
+        op.partial_rows = static_cast<int>(p.size(0));
+        TORCH_CHECK(reinterpret_cast<uintptr_t>(op.partial) % 4 == 0, "partial must be 4-byte aligned");
+        if (reinterpret_cast<uintptr_t>(op.partial) % 16 != 0) vec16 = false;
       }
       max_tokens = std::max<int64_t>(max_tokens, out[i].size(0));
+      max_rows = std::max<int64_t>(max_rows, args.op[i].partial_rows);
     }
+    (void)max_rows;
     ctas = std::max(1, ctas);
     const int segments = pick_segments(max_tokens, ctas);
     for (size_t i = 0; i < n; ++i) {

@@ -58,9 +58,11 @@ struct CtrlHeader {
   unsigned cdone_count;     // combine CTAs whose partial rows are in the heap
   unsigned cfin_count;      // combine CTAs that finished reducing
   unsigned long long error_detail;  // (phase << 56 | where << 32 | value) of the first error
-  unsigned long long wait_polls;    // diagnostic: total flag polls of the last launch
-  unsigned long long identity[2];   // diagnostics mode: (dispatch, combine) operation identity
-  unsigned long long reserved[24];
+  unsigned work_next;       // dispatch: next unclaimed (token, segment) work item
+  unsigned cwork_push;      // combine: next unclaimed (row, segment) item of the push phase
+  unsigned cwork_reduce;    // combine: next unclaimed (token, segment) item of the reduce phase
+  unsigned reserved0;
+  unsigned long long reserved[25];
 };
 static_assert(sizeof(CtrlHeader) == 256, "control header is one 256-byte block");
 
@@ -88,17 +90,20 @@ EPX_HD CtrlLayout ctrl_layout(int world) {
 }
 
 // ---- slot -----------------------------------------------------------------
-// The peer-visible part comes first and depends only on (capacity, hidden,
-// topk), so a peer that knows my slot offset and capacity can address every
-// plane. The rank-local part also depends on this rank's token bound.
+// The peer-visible part comes first and every plane OFFSET in it depends only on
+// (capacity, hidden, topk), so a peer that knows my slot offset and capacity can
+// address every plane (the last one, staging, is sized by this rank's token bound,
+// but nothing peer-visible follows it). The rank-local part comes after.
 struct SlotLayout {
   // peer-visible
   size_t hidden;     // bf16  [capacity, hidden]
   size_t ids;        // int64 [capacity, topk]
   size_t weights;    // f32   [capacity, topk]
   size_t inverse;    // int64 [capacity, 2]
-  size_t partial;    // bf16  [capacity, hidden]
+  size_t ret;        // i32   [capacity]           where the row's result goes back: token * fanout + j
+  size_t staging;    // bf16  [tokens * fanout, hidden]  partial rows pushed back by the expert ranks
   // rank-local
+  size_t partial;    // bf16  [capacity, hidden]   default output plane of the expert runner
   size_t mask;       // u64   [tokens]             destination-rank set per token
   size_t dest_rows;  // i32   [tokens, fanout]     position among this rank's rows for the j-th destination
   size_t send_rows;  // i32   [tokens, fanout]     final row index at the j-th destination (-1: not sent)
@@ -128,6 +133,8 @@ EPX_HD SlotLayout slot_layout(long long capacity, long long tokens, int hidden, 
   l.ids = take(c * k * 8);
   l.weights = take(c * k * 4);
   l.inverse = take(c * 16);
+  l.ret = take(c * 4);
+  l.staging = take(t * static_cast<size_t>(route_fanout(topk, world)) * h * 2);
   l.partial = take(c * h * 2);
   l.mask = take(t * 8);
   l.dest_rows = take(t * static_cast<size_t>(route_fanout(topk, world)) * 4);
@@ -179,8 +186,7 @@ struct DispatchOp {
 
 struct CombineOp {
   const RankCtx* ctx;
-  const void* partial;    // bf16 [capacity, hidden] outside the heap, or null when the
-                          // runner wrote the slot's partial plane directly
+  const void* partial;    // bf16 [rows, hidden]: this rank's weighted expert output (any device tensor)
   void* out;              // bf16 [tokens, hidden]
   unsigned long long slot_off;
   unsigned long long identity;
@@ -190,7 +196,7 @@ struct CombineOp {
   int slot_tokens;
   int segments;
   int vec16;
-  int reserved;
+  int partial_rows;       // rows of `partial`; rows at or above it are not pushed
 };
 
 struct DispatchArgs { DispatchOp op[kMaxEmulatedRanks]; };
