@@ -113,6 +113,7 @@ __device__ __forceinline__ void reduce_rows(const char* const* rp, const char* l
   constexpr int kChunk = kWords * 4;
   for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
     Chunk<kWords> v[kPeers][kUnroll];
+    Chunk<kWords> local[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const long long off = base + static_cast<long long>(u) * 32 * kChunk;
@@ -120,21 +121,20 @@ __device__ __forceinline__ void reduce_rows(const char* const* rp, const char* l
 #pragma unroll
         for (int b = 0; b < kPeers; ++b)
           if (rp[b] != nullptr) v[b][u] = load_chunk<kWords>(rp[b] + off);
+        if (local_ptr != nullptr) local[u] = load_local_chunk<kWords>(local_ptr + off);
       }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const long long off = base + static_cast<long long>(u) * 32 * kChunk;
       if (off < b1) {
-        Chunk<kWords> local;
-        if (local_ptr != nullptr) local = load_chunk<kWords>(local_ptr + off);   // own HBM: short latency
         float acc[kWords * 2];
 #pragma unroll
         for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
 #pragma unroll
         for (int b = 0; b < kPeers; ++b)
           if (rp[b] != nullptr) accumulate<kWords>(acc, v[b][u]);
-        store_chunk<kWords>(outp + off, finish<kWords>(acc, local, local_ptr != nullptr, single_round));
+        store_chunk<kWords>(outp + off, finish<kWords>(acc, local[u], local_ptr != nullptr, single_round));
       }
     }
   }
@@ -340,6 +340,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
           rp[b] = (b < n && b != skip) ? reinterpret_cast<const char*>(bits) : nullptr;
         }
         if (n <= 2) reduce_rows<kWords, 2, 4>(rp, local_ptr, outp, b0, b1, lane, single_round);
+        else if (n <= 4) reduce_rows<kWords, 4, 2>(rp, local_ptr, outp, b0, b1, lane, single_round);
         else reduce_rows<kWords, kPeerBatch, 1>(rp, local_ptr, outp, b0, b1, lane, single_round);
       } else {
         reduce_rows_generic<kWords>(ptr_a, ptr_b, n, skip, local_ptr, outp, b0, b1, lane, single_round);

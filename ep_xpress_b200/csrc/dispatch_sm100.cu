@@ -32,6 +32,7 @@ namespace {
 
 constexpr unsigned kPhaseDispatch = 1;
 constexpr int kWarps = kThreads / 32;
+constexpr int kRegK = 8;   // top-k up to which a token's ids and weights are routed from registers
 
 struct PeerPlanes {
   char* hidden;
@@ -105,15 +106,41 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     if (t < T) {
       bool bad = false;
       const long long row = static_cast<long long>(t) * K;
-      for (int k = 0; k < K; ++k) {
-        const long long id = load_id<IdT>(op.ids, row + k);
-        if (id == -1) continue;
-        if (id < 0 || id >= E) { bad = true; continue; }
-        const float w = op.weights[row + k];
-        if (!isfinite(w)) bad = true;
-        for (int j = 0; j < k; ++j)
-          if (load_id<IdT>(op.ids, row + j) == id) bad = true;
-        m |= 1ull << c.expert_rank[id];
+      if (K <= kRegK) {
+        // Independent loads first, lookups second, checks in registers: the route phase is a
+        // chain of dependent memory latencies, not bandwidth.
+        long long id[kRegK];
+        float w[kRegK];
+        int owner[kRegK];
+#pragma unroll
+        for (int k = 0; k < kRegK; ++k) {
+          id[k] = k < K ? load_id<IdT>(op.ids, row + k) : -1;
+          w[k] = k < K ? op.weights[row + k] : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < kRegK; ++k) {
+          const bool in_range = id[k] >= 0 && id[k] < E;
+          owner[k] = in_range ? c.expert_rank[id[k]] : -1;
+          if (id[k] != -1 && (!in_range || !isfinite(w[k]))) bad = true;
+        }
+#pragma unroll
+        for (int k = 0; k < kRegK; ++k) {
+          if (owner[k] >= 0) m |= 1ull << owner[k];
+#pragma unroll
+          for (int j = 0; j < k; ++j)
+            if (id[k] >= 0 && id[j] == id[k]) bad = true;
+        }
+      } else {
+        for (int k = 0; k < K; ++k) {
+          const long long id = load_id<IdT>(op.ids, row + k);
+          if (id == -1) continue;
+          if (id < 0 || id >= E) { bad = true; continue; }
+          const float w = op.weights[row + k];
+          if (!isfinite(w)) bad = true;
+          for (int j = 0; j < k; ++j)
+            if (load_id<IdT>(op.ids, row + j) == id) bad = true;
+          m |= 1ull << c.expert_rank[id];
+        }
       }
       if (bad) {
         m = 0;
@@ -121,11 +148,19 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       }
       mask_arr[t] = m;
     }
+    // Position of this token among the tile's rows for each destination: the first eight
+    // stay packed in registers (one byte each, < 32), wider fan-outs spill to the plane.
+    unsigned long long packed = 0;
     int j = 0;
     for (int d = 0; d < W; ++d) {
       const bool bit = (m >> d) & 1ull;
       const unsigned ballot = __ballot_sync(0xffffffffu, bit);
-      if (bit) dest_rows[static_cast<long long>(t) * fan + j++] = __popc(ballot & ((1u << lane) - 1u));
+      if (bit) {
+        const unsigned before = __popc(ballot & ((1u << lane) - 1u));
+        if (j < 8) packed |= static_cast<unsigned long long>(before) << (8 * j);
+        else dest_rows[static_cast<long long>(t) * fan + j] = static_cast<int>(before);
+        ++j;
+      }
       if (lane == 0) s_warp_cnt[warp][d] = __popc(ballot);
     }
     __syncthreads();
@@ -141,9 +176,11 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     __syncthreads();
     if (m) {
       int jj = 0;
-      for (unsigned long long mm = m; mm; mm &= mm - 1) {
+      for (unsigned long long mm = m; mm; mm &= mm - 1, ++jj) {
         const int d = __ffsll(static_cast<long long>(mm)) - 1;
-        dest_rows[static_cast<long long>(t) * fan + jj++] += s_warp_cnt[warp][d];
+        const long long at = static_cast<long long>(t) * fan + jj;
+        const int before = jj < 8 ? static_cast<int>((packed >> (8 * jj)) & 0xffu) : dest_rows[at];
+        dest_rows[at] = before + s_warp_cnt[warp][d];
       }
     }
     __syncthreads();

@@ -335,13 +335,13 @@ class Engine {
     TORCH_CHECK(local >= 0 && static_cast<size_t>(local) < local_ranks_.size(), "local rank index out of range");
   }
   // Rows are split into segments of at least 2 KiB (one fully unrolled warp iteration) so
-  // that there are several work items per warp: small batches still occupy every warp and
-  // large ones do not end with a half-empty last round.
+  // that small batches still occupy every warp. Work items are claimed dynamically, so two
+  // items per warp are enough for balance; more would only add per-item overhead.
   int pick_segments(int64_t tokens, int ctas) const {
     const int64_t warps = static_cast<int64_t>(ctas) * (kThreads / 32);
     const int64_t row_bytes = static_cast<int64_t>(hidden_) * 2;
     const int64_t max_segments = std::max<int64_t>(1, row_bytes / 2048);
-    const int64_t wanted = (8 * warps + std::max<int64_t>(tokens, 1) - 1) / std::max<int64_t>(tokens, 1);
+    const int64_t wanted = (2 * warps + std::max<int64_t>(tokens, 1) - 1) / std::max<int64_t>(tokens, 1);
     return static_cast<int>(std::max<int64_t>(1, std::min(wanted, max_segments)));
   }
   // profile: int64 [ranks, ctas, kProfileStamps] on the context device, or nothing.
