@@ -62,6 +62,7 @@ def parse_args():
     parser.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     parser.add_argument("--routing", choices=("uniform", "zipf"), default="uniform")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--plain-launch", action="store_true", help="ordinary instead of cooperative launches")
     parser.add_argument("--profile-out", default=None,
                         help="after timing, run 4 profiled steps and write per-CTA phase stamps to PATH.rankR.json")
     return parser.parse_args()
@@ -105,14 +106,15 @@ def make_inputs(shape, tokens, world, rank, routing, sets):
 class OursArm:
     name = "ours"
 
-    def __init__(self, shape, tokens, world, rank, local):
+    def __init__(self, shape, tokens, world, rank, local, plain_launch=False):
         import torch.distributed as dist
         from ep_xpress_b200 import Config, Context, get_nccl_comm_handle
         from ep_xpress_b200.models import IdentityMoELayer
         from ep_xpress_b200.utils import workloads
         self.comm = get_nccl_comm_handle(dist.group.WORLD)
         cfg = Config(hidden_size=shape["hidden"], topk=shape["topk"], max_tokens_per_rank=tokens,
-                     timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30)
+                     timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30,
+                     cooperative_launch=not plain_launch)
         self.context = Context(self.comm, workloads.contiguous_expert_map(shape["experts"], world), cfg)
         self.layer = IdentityMoELayer(self.context)
 
@@ -130,7 +132,7 @@ class ReferenceArm:
     """The reference's own library and stock code path; nothing of this repository's runtime."""
     name = "reference"
 
-    def __init__(self, shape, tokens, world, rank, local):
+    def __init__(self, shape, tokens, world, rank, local, plain_launch=False):
         import torch
         import torch.distributed as dist
         os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
@@ -207,7 +209,7 @@ def run(args):
     sets = 4
     host = make_inputs(shape, tokens, world, rank, args.routing, sets)
     device = [tuple(t.cuda(non_blocking=True) for t in batch) for batch in host]
-    arm = (OursArm if args.impl == "ours" else ReferenceArm)(shape, tokens, world, rank, local)
+    arm = (OursArm if args.impl == "ours" else ReferenceArm)(shape, tokens, world, rank, local, args.plain_launch)
     stream = torch.cuda.current_stream()
 
     # ---- device-timed: inputs resident, rotated ---------------------------------

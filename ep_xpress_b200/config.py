@@ -63,6 +63,7 @@ class Config:
     workspace_pool_bytes: int = 0             # heap reserve for create_workspace; 0 = two more slots
     combine_rounding: str = "two_step"        # "two_step" (single-node reference) or "single" (multi-node reference)
     zero_padding: bool = True                 # keep activation rows above valid_count at zero
+    cooperative_launch: bool = True           # driver-guaranteed co-residency of the transport CTAs
 
     @property
     def device_transport(self) -> bool:
@@ -79,7 +80,7 @@ class Config:
         if not _is_int(self.gin_gpu_budget_bytes) or self.gin_gpu_budget_bytes <= 0:
             raise ValueError("gin_gpu_budget_bytes must be positive")
         for name in ("decode_single_frame", "combine_warp_specialization", "fatal_errors", "diagnostics",
-                     "zero_padding"):
+                     "zero_padding", "cooperative_launch"):
             if not isinstance(getattr(self, name), bool):
                 raise ValueError(f"{name} must be a bool")
         if self.decode_single_frame and (not device or not self.decode_max_tokens):

@@ -384,10 +384,13 @@ cudaError_t combine_max_ctas(bool vec16, int* ctas) {
   return cudaSuccess;
 }
 
-cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, cudaStream_t stream) {
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, bool cooperative,
+                           cudaStream_t stream) {
   void* params[] = {const_cast<CombineArgs*>(&args)};
   const void* kernel = vec16 ? reinterpret_cast<const void*>(combine_kernel<true>)
                              : reinterpret_cast<const void*>(combine_kernel<false>);
+  if (!cooperative)
+    return cudaLaunchKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, 0, stream);
   return cudaLaunchCooperativeKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, 0, stream);
 }
 

@@ -444,7 +444,7 @@ cudaError_t dispatch_max_ctas(bool ids64, bool vec16, size_t dynamic_smem, int* 
 }
 
 cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
-                            size_t dynamic_smem, cudaStream_t stream) {
+                            size_t dynamic_smem, bool cooperative, cudaStream_t stream) {
   DispatchKernel kernel = pick_kernel(ids64, vec16);
   if (dynamic_smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -452,6 +452,9 @@ cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_ra
     if (err != cudaSuccess) return err;
   }
   void* params[] = {const_cast<DispatchArgs*>(&args)};
+  if (!cooperative)
+    return cudaLaunchKernel(reinterpret_cast<const void*>(kernel), dim3(ctas_per_rank, ranks, 1),
+                            dim3(kThreads, 1, 1), params, dynamic_smem, stream);
   return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3(ctas_per_rank, ranks, 1),
                                      dim3(kThreads, 1, 1), params, dynamic_smem, stream);
 }

@@ -36,8 +36,10 @@ cudaStream_t stream_of(int64_t handle) { return reinterpret_cast<cudaStream_t>(h
 class Engine {
  public:
   Engine(int world, std::vector<int> local_ranks, int hidden, int topk, std::vector<int> expert_to_rank,
-         std::vector<std::vector<int64_t>> heaps, double timeout_seconds, bool single_round, int device)
-      : world_(world), local_ranks_(std::move(local_ranks)), hidden_(hidden), topk_(topk), device_(device) {
+         std::vector<std::vector<int64_t>> heaps, double timeout_seconds, bool single_round, int device,
+         bool cooperative)
+      : world_(world), local_ranks_(std::move(local_ranks)), hidden_(hidden), topk_(topk), device_(device),
+        cooperative_(cooperative) {
     TORCH_CHECK(world >= 1 && world <= kMaxWorld, "world size must be in [1, 63]");
     TORCH_CHECK(!local_ranks_.empty() && local_ranks_.size() <= static_cast<size_t>(kMaxEmulatedRanks),
                 "an engine drives between 1 and ", kMaxEmulatedRanks, " ranks");
@@ -83,9 +85,9 @@ class Engine {
     cuda_check(cudaMalloc(&ctx_, sizeof(RankCtx) * host.size()), "cudaMalloc rank contexts");
     cuda_check(cudaMemcpy(ctx_, host.data(), sizeof(RankCtx) * host.size(), cudaMemcpyHostToDevice), "upload");
     cuda_check(cudaDeviceGetAttribute(&sms_, cudaDevAttrMultiProcessorCount, device_), "query SM count");
-    int cooperative = 0;
-    cuda_check(cudaDeviceGetAttribute(&cooperative, cudaDevAttrCooperativeLaunch, device_), "query cooperative launch");
-    TORCH_CHECK(cooperative, "the transport kernels need cooperative all-resident launches");
+    int supported = 0;
+    cuda_check(cudaDeviceGetAttribute(&supported, cudaDevAttrCooperativeLaunch, device_), "query cooperative launch");
+    TORCH_CHECK(supported || !cooperative_, "the transport kernels need cooperative all-resident launches");
   }
 
   ~Engine() {
@@ -207,7 +209,7 @@ class Engine {
       args.op[i].vec16 = vec16 ? 1 : 0;
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
-    cuda_check(launch_dispatch(args, static_cast<int>(n), ctas, ids64, vec16, smem, stream_of(stream)),
+    cuda_check(launch_dispatch(args, static_cast<int>(n), ctas, ids64, vec16, smem, cooperative_, stream_of(stream)),
                "dispatch launch");
   }
 
@@ -263,7 +265,7 @@ class Engine {
       args.op[i].vec16 = vec16 ? 1 : 0;
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
-    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, stream_of(stream)), "combine launch");
+    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, cooperative_, stream_of(stream)), "combine launch");
   }
 
   void scale_rows(const at::Tensor& hidden, const at::Tensor& local_ids, const at::Tensor& weights,
@@ -359,6 +361,7 @@ class Engine {
   int world_;
   std::vector<int> local_ranks_;
   int hidden_, topk_, device_;
+  bool cooperative_ = true;
   int sms_ = 0;
   std::vector<int> experts_per_rank_;
   std::vector<char*> own_heap_;
@@ -388,9 +391,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return slot_layout(capacity, tokens, hidden, topk, world).bytes;
   });
   py::class_<Engine>(m, "Engine")
-      .def(py::init<int, std::vector<int>, int, int, std::vector<int>, std::vector<std::vector<int64_t>>, double, bool, int>(),
+      .def(py::init<int, std::vector<int>, int, int, std::vector<int>, std::vector<std::vector<int64_t>>, double, bool, int, bool>(),
            py::arg("world"), py::arg("local_ranks"), py::arg("hidden"), py::arg("topk"), py::arg("expert_to_rank"),
-           py::arg("heaps"), py::arg("timeout_seconds"), py::arg("single_round"), py::arg("device"))
+           py::arg("heaps"), py::arg("timeout_seconds"), py::arg("single_round"), py::arg("device"),
+           py::arg("cooperative") = true)
       .def("sm_count", &Engine::sm_count)
       .def("experts_per_rank", &Engine::experts_per_rank)
       .def("ctrl_bytes", &Engine::ctrl_bytes)

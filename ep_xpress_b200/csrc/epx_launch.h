@@ -16,9 +16,13 @@ size_t dispatch_dynamic_smem(int max_tokens, int world);
 cudaError_t dispatch_max_ctas(bool ids64, bool vec16, size_t dynamic_smem, int* ctas);
 cudaError_t combine_max_ctas(bool vec16, int* ctas);
 
+// `cooperative` selects cudaLaunchCooperativeKernel (the driver guarantees that all CTAs are
+// resident together) over a plain launch (cheaper to enqueue; co-residency then rests on the
+// grid fitting the device, which the caller bounds with the *_max_ctas queries, and on no
+// other kernel holding the SMs forever).
 cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
-                            size_t dynamic_smem, cudaStream_t stream);
-cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16,
+                            size_t dynamic_smem, bool cooperative, cudaStream_t stream);
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, bool cooperative,
                            cudaStream_t stream);
 
 // Synthetic expert used by the validation harness and the communication

@@ -102,7 +102,8 @@ class TransportCore:
         self.hidden, self.topk = config.hidden_size, config.topk
         self.engine = native.Engine(world, self.local_ranks, self.hidden, self.topk, list(expert_to_rank),
                                     [list(map(int, row)) for row in heaps], float(config.timeout_seconds),
-                                    config.combine_rounding == "single", self.device.index)
+                                    config.combine_rounding == "single", self.device.index,
+                                    bool(config.cooperative_launch))
         ctrl = self.engine.ctrl_bytes()
         self._allocators = [HeapAllocator(ctrl, heap_bytes) for _ in self.local_ranks]
         self.max_ctas = max(1, min(self.engine.max_ctas(config.max_tokens_per_rank), self.engine.sm_count()))
