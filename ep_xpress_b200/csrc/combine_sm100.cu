@@ -107,10 +107,15 @@ __device__ __forceinline__ Chunk<kWords> finish(const float* acc, const Chunk<kW
 // Reduce one row segment whose contributors' row pointers sit in registers:
 // kPeers rows x kUnroll chunks of loads are issued before the first add; adds
 // then run in ascending rank order per chunk.
+struct RowPointers {
+  const char* row[kPeerBatch];
+};
+
 template <int kWords, int kPeers, int kUnroll>
-__device__ __forceinline__ void reduce_rows(const char* const* rp, const char* local_ptr, char* outp, long long b0,
-                                            long long b1, int lane, bool single_round) {
+__device__ __noinline__ void reduce_rows(RowPointers rows, const char* local_ptr, char* outp, long long b0,
+                                         long long b1, int lane, bool single_round) {
   constexpr int kChunk = kWords * 4;
+  const char* const* rp = rows.row;
   for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
     Chunk<kWords> v[kPeers][kUnroll];
     Chunk<kWords> local[kUnroll];
@@ -182,8 +187,120 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
   return __ffsll(static_cast<long long>(mask)) - 1;
 }
 
+// ---- reduce phase, bulk-copy variant (rows 16-byte aligned) -------------------------------
+// Each warp streams its work item through a ring of shared-memory stages: lanes that hold a
+// contributor's row pointer issue one bulk copy (TMA) of the next 512-byte step of that row,
+// all contributors of a step complete on one mbarrier, and the warp then adds the staged
+// chunks in ascending rank order. Data in flight lives in shared memory, not in registers,
+// so the phase runs at memory speed with a small register footprint.
+constexpr int kStepBytes = 512;                 // 32 lanes x 16 bytes
+constexpr int kStages = 3;
+constexpr int kStageBytes = kPeerBatch * kStepBytes;
+constexpr int kWarpRingBytes = kStages * kStageBytes;
+constexpr int kCombineWarps = kThreads / 32;
+constexpr size_t kCombineSmemBytes = static_cast<size_t>(kCombineWarps) * kWarpRingBytes;
+constexpr unsigned kMbarrierSpinLimit = 1u << 24;
+
+struct WarpRing {
+  char* buffer;                    // kStages x kPeerBatch x kStepBytes of this warp
+  unsigned long long* bars;        // kStages mbarriers of this warp
+  unsigned issued;                 // units issued so far (persist across work items)
+  unsigned consumed;               // units consumed so far
+};
+
+// A unit is (step of the row segment, batch of up to kPeerBatch contributors).
+__device__ __forceinline__ void ring_issue(WarpRing& ring, const char* ptr_a, const char* ptr_b, int n, int batch,
+                                           long long offset, unsigned bytes, int lane) {
+  const int stage = ring.issued % kStages;
+  const int first = batch * kPeerBatch;                 // first contributor of this batch
+  const int local = lane - (first & 31);                // this lane's position inside the batch
+  const bool mine = local >= 0 && local < kPeerBatch && first + local < n;
+  const char* src = (first < 32) ? ptr_a : ptr_b;
+  const bool valid = mine && src != nullptr;
+  const unsigned votes = __ballot_sync(0xffffffffu, valid);
+  __syncwarp();                                         // everyone finished reading this stage
+  if (lane == 0) {
+    fence_proxy_async();
+    mbarrier_arrive_expect_tx(ring.bars + stage, static_cast<unsigned>(__popc(votes)) * bytes);
+  }
+  __syncwarp();
+  if (valid) bulk_load_to_smem(ring.buffer + stage * kStageBytes + local * kStepBytes, src + offset, bytes,
+                               ring.bars + stage);
+  ++ring.issued;
+}
+
+__device__ __forceinline__ bool ring_wait(WarpRing& ring) {
+  const int stage = ring.consumed % kStages;
+  const unsigned parity = (ring.consumed / kStages) & 1u;
+  unsigned spins = 0;
+  while (!mbarrier_try_wait(ring.bars + stage, parity))
+    if (++spins > kMbarrierSpinLimit) return false;
+  return true;
+}
+
+// Reduce one row segment [b0, b1) of token t. Lane j holds contributor j (ptr_a) and j + 32
+// (ptr_b), ascending rank order; self_index is this rank's own position or -1.
+__device__ __forceinline__ bool reduce_segment_bulk(WarpRing& ring, const char* ptr_a, const char* ptr_b, int n,
+                                                    int self_index, bool single_round, char* outp, long long b0,
+                                                    long long b1, int lane) {
+  const int batches = n == 0 ? 0 : (n + kPeerBatch - 1) / kPeerBatch;
+  const int steps = static_cast<int>((b1 - b0 + kStepBytes - 1) / kStepBytes);
+  if (batches == 0) {                                   // padding token: zero row
+    for (long long off = b0 + lane * 16; off < b1; off += kStepBytes) st_payload16(outp + off, make_uint4(0, 0, 0, 0));
+    return true;
+  }
+  const unsigned valid_a = __ballot_sync(0xffffffffu, ptr_a != nullptr);
+  const unsigned valid_b = __ballot_sync(0xffffffffu, ptr_b != nullptr);
+  const int units = steps * batches;
+  int issued = 0;
+  auto issue_next = [&]() {
+    const int step = issued / batches, batch = issued % batches;
+    const long long offset = b0 + static_cast<long long>(step) * kStepBytes;
+    const unsigned bytes = static_cast<unsigned>(min(static_cast<long long>(kStepBytes), b1 - offset));
+    ring_issue(ring, ptr_a, ptr_b, n, batch, offset, bytes, lane);
+    ++issued;
+  };
+  for (int u = 0; u < kStages - 1 && issued < units; ++u) issue_next();
+  float acc[8];
+  Chunk<4> local;
+  bool has_local = false;
+  for (int unit = 0; unit < units; ++unit) {
+    const int step = unit / batches, batch = unit % batches;
+    if (issued < units) issue_next();
+    if (!ring_wait(ring)) return false;
+    const long long offset = b0 + static_cast<long long>(step) * kStepBytes;
+    const bool active = offset + lane * 16 < b1;
+    if (batch == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      has_local = false;
+    }
+    const char* stage = ring.buffer + (ring.consumed % kStages) * kStageBytes + lane * 16;
+    const int first = batch * kPeerBatch;
+    const unsigned valid = (first < 32 ? valid_a : valid_b) >> (first & 31);
+#pragma unroll
+    for (int i = 0; i < kPeerBatch; ++i) {
+      if (first + i < n && ((valid >> i) & 1u) && active) {
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + i * kStepBytes);
+        Chunk<4> c;
+        c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
+        if (!single_round && first + i == self_index) {
+          local = c;
+          has_local = true;
+        } else {
+          accumulate<4>(acc, c);
+        }
+      }
+    }
+    ++ring.consumed;
+    if (batch == batches - 1 && active)
+      store_chunk<4>(outp + offset + lane * 16, finish<4>(acc, local, has_local, single_round));
+  }
+  return true;
+}
+
 template <bool kVec16>
-__device__ __forceinline__ void combine_body(const CombineOp& op) {
+__device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_smem) {
   constexpr int kWords = kVec16 ? 4 : 1;
   constexpr int kChunk = kWords * 4;
   constexpr int kUnroll = 4;
@@ -284,8 +401,20 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
 
   // ---- D. rank-order reduce from local memory -----------------------------------------------
   {
+    __shared__ unsigned long long s_bars[kCombineWarps * kStages];
+    WarpRing ring;
+    ring.buffer = dynamic_smem + static_cast<size_t>(tid >> 5) * kWarpRingBytes;
+    ring.bars = s_bars + (tid >> 5) * kStages;
+    ring.issued = ring.consumed = 0;
+    if (kVec16) {
+      if (lane < kStages) mbarrier_init(ring.bars + lane, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      fence_proxy_async();
+      __syncwarp();
+    }
+    bool healthy = true;
     const long long items = static_cast<long long>(T) * segs;
-    while (true) {
+    while (healthy) {
       unsigned claimed = 0;
       if (lane == 0) claimed = atomicAdd(&hdr->cwork_reduce, 1u);
       const long long item = __shfl_sync(0xffffffffu, claimed, 0);
@@ -307,7 +436,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
           const int d = nth_set_bit(m, lane);
           const int row = send_rows[static_cast<long long>(t) * fan + lane];
           is_self = (d == self);
-          if (row >= 0)
+          if (row >= 0 && !(is_self && row >= op.partial_rows))
             ptr_a = is_self ? partial + static_cast<long long>(row) * row_bytes
                             : staging + (static_cast<long long>(t) * fan + lane) * row_bytes;
         }
@@ -317,7 +446,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
           const int d = nth_set_bit(m, lane + 32);
           const int row = send_rows[static_cast<long long>(t) * fan + lane + 32];
           is_self = (d == self);
-          if (row >= 0)
+          if (row >= 0 && !(is_self && row >= op.partial_rows))
             ptr_b = is_self ? partial + static_cast<long long>(row) * row_bytes
                             : staging + (static_cast<long long>(t) * fan + lane + 32) * row_bytes;
         }
@@ -331,13 +460,15 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
           : __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(self_index < 32 ? ptr_a : ptr_b), self_index & 31);
       const char* const local_ptr = reinterpret_cast<const char*>(local_bits);
 
-      if (n <= kPeerBatch) {
+      if (kVec16) {
+        healthy = reduce_segment_bulk(ring, ptr_a, ptr_b, n, self_index, single_round, outp, b0, b1, lane);
+      } else if (n <= kPeerBatch) {
         // Common case: every contributor's row pointer sits in a register.
-        const char* rp[kPeerBatch];
+        RowPointers rp;
 #pragma unroll
         for (int b = 0; b < kPeerBatch; ++b) {
           const unsigned long long bits = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(ptr_a), b);
-          rp[b] = (b < n && b != skip) ? reinterpret_cast<const char*>(bits) : nullptr;
+          rp.row[b] = (b < n && b != skip) ? reinterpret_cast<const char*>(bits) : nullptr;
         }
         if (n <= 2) reduce_rows<kWords, 2, 4>(rp, local_ptr, outp, b0, b1, lane, single_round);
         else if (n <= 4) reduce_rows<kWords, 4, 2>(rp, local_ptr, outp, b0, b1, lane, single_round);
@@ -346,6 +477,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
         reduce_rows_generic<kWords>(ptr_a, ptr_b, n, skip, local_ptr, outp, b0, b1, lane, single_round);
       }
     }
+    if (!healthy) report_error(c, kTimeout, kPhaseCombine, 4, 0);
   }
 
   // ---- E. retire the epoch ---------------------------------------------------------------
@@ -366,7 +498,16 @@ __device__ __forceinline__ void combine_body(const CombineOp& op) {
 
 template <bool kVec16>
 __global__ void __launch_bounds__(kThreads, 1) combine_kernel(const __grid_constant__ CombineArgs args) {
-  combine_body<kVec16>(args.op[blockIdx.y]);
+  extern __shared__ __align__(128) char combine_smem[];
+  combine_body<kVec16>(args.op[blockIdx.y], combine_smem);
+}
+
+template <bool kVec16>
+cudaError_t prepare_combine_kernel(size_t* dynamic_smem) {
+  *dynamic_smem = kVec16 ? kCombineSmemBytes : 0;
+  if (*dynamic_smem <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(combine_kernel<kVec16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(*dynamic_smem));
 }
 
 }  // namespace
@@ -377,8 +518,11 @@ cudaError_t combine_max_ctas(bool vec16, int* ctas) {
   if (err != cudaSuccess) return err;
   err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (err != cudaSuccess) return err;
-  err = vec16 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<true>, kThreads, 0)
-              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<false>, kThreads, 0);
+  size_t smem = 0;
+  err = vec16 ? prepare_combine_kernel<true>(&smem) : prepare_combine_kernel<false>(&smem);
+  if (err != cudaSuccess) return err;
+  err = vec16 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<true>, kThreads, smem)
+              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<false>, kThreads, smem);
   if (err != cudaSuccess) return err;
   *ctas = per_sm * sms;
   return cudaSuccess;
@@ -387,11 +531,14 @@ cudaError_t combine_max_ctas(bool vec16, int* ctas) {
 cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, bool cooperative,
                            cudaStream_t stream) {
   void* params[] = {const_cast<CombineArgs*>(&args)};
+  size_t smem = 0;
+  cudaError_t err = vec16 ? prepare_combine_kernel<true>(&smem) : prepare_combine_kernel<false>(&smem);
+  if (err != cudaSuccess) return err;
   const void* kernel = vec16 ? reinterpret_cast<const void*>(combine_kernel<true>)
                              : reinterpret_cast<const void*>(combine_kernel<false>);
   if (!cooperative)
-    return cudaLaunchKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, 0, stream);
-  return cudaLaunchCooperativeKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, 0, stream);
+    return cudaLaunchKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, smem, stream);
+  return cudaLaunchCooperativeKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, smem, stream);
 }
 
 }  // namespace epx

@@ -151,6 +151,34 @@ __device__ __forceinline__ bool rank_barrier(const RankCtx& c, unsigned* counter
   return barrier_ok != 0;
 }
 
+// ---- bulk asynchronous copies (TMA, no tensor map) into this CTA's shared memory -------
+__device__ __forceinline__ unsigned smem_address(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbarrier_init(unsigned long long* bar, unsigned arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbarrier_try_wait(unsigned long long* bar, unsigned parity) {
+  unsigned done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(smem_address(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// Global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) that
+// signals `bar` with its byte count when the data has landed. Destination is this CTA's own
+// shared memory; one copy per call, no fan-out.
+__device__ __forceinline__ void bulk_load_to_smem(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_address(dst)), "l"(src), "r"(bytes), "r"(smem_address(bar)) : "memory");
+}
+// Orders earlier generic-proxy accesses of this thread before later async-proxy (bulk copy) ones.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // Opt-in phase timestamp of one CTA (thread 0 only); a null buffer costs one predicate.
 __device__ __forceinline__ void profile_stamp(unsigned long long* profile, int index) {
   if (profile != nullptr && threadIdx.x == 0)
