@@ -187,119 +187,175 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
   return __ffsll(static_cast<long long>(mask)) - 1;
 }
 
-// ---- reduce phase, bulk-copy variant (rows 16-byte aligned) -------------------------------
-// Each warp streams its work item through a ring of shared-memory stages: lanes that hold a
-// contributor's row pointer issue one bulk copy (TMA) of the next 512-byte step of that row,
-// all contributors of a step complete on one mbarrier, and the warp then adds the staged
-// chunks in ascending rank order. Data in flight lives in shared memory, not in registers,
-// so the phase runs at memory speed with a small register footprint.
-constexpr int kStepBytes = 512;                 // 32 lanes x 16 bytes
+// ---- reduce phase, bulk-copy variant -------------------------------------------------------
+// (rows 16-byte aligned, at most kPeerBatch contributors per token)
+// One producer warp and sixteen consumer warps share a ring of shared-memory stages. The
+// producer claims (token, row segment) items, and lane j issues ONE bulk copy (TMA) of
+// contributor j's segment - up to 8 KiB each - into the stage; all copies of an item complete
+// on the stage's "full" mbarrier. Consumers add the staged chunks in ascending rank order,
+// store the result and release the stage through its "empty" mbarrier. Data in flight lives
+// in shared memory (up to two items, ~100 KiB per SM), so the phase runs at memory speed with
+// few registers, and the item look-ups (claim, mask, row indices) are prefetched two items
+// ahead by the producer instead of sitting on every warp's critical path.
+constexpr int kConsumerWarps = kThreads / 32;
+constexpr int kBulkThreads = kThreads + 32;       // + the producer warp
 constexpr int kStages = 3;
-constexpr int kStageBytes = kPeerBatch * kStepBytes;
-constexpr int kWarpRingBytes = kStages * kStageBytes;
-constexpr int kCombineWarps = kThreads / 32;
-constexpr size_t kCombineSmemBytes = static_cast<size_t>(kCombineWarps) * kWarpRingBytes;
-constexpr unsigned kMbarrierSpinLimit = 1u << 24;
+constexpr int kSegMaxBytes = 8192;                // largest row segment of one item
+constexpr int kStageBytes = kPeerBatch * kSegMaxBytes;
+constexpr size_t kBulkSmemBytes = static_cast<size_t>(kStages) * kStageBytes;
+constexpr unsigned kMbarrierSpinLimit = 1u << 22;
 
-struct WarpRing {
-  char* buffer;                    // kStages x kPeerBatch x kStepBytes of this warp
-  unsigned long long* bars;        // kStages mbarriers of this warp
-  unsigned issued;                 // units issued so far (persist across work items)
-  unsigned consumed;               // units consumed so far
+struct StageItem {
+  long long out_offset;   // byte offset of the segment inside the output tensor
+  int bytes;              // segment length, multiple of 16
+  int contributors;       // n
+  int self_index;         // position of this rank among the contributors, or -1
+  unsigned valid;         // bit j: contributor j was copied
+  int end;                // non-zero: no more items
+  int pad;
 };
 
-// A unit is (step of the row segment, batch of up to kPeerBatch contributors).
-__device__ __forceinline__ void ring_issue(WarpRing& ring, const char* ptr_a, const char* ptr_b, int n, int batch,
-                                           long long offset, unsigned bytes, int lane) {
-  const int stage = ring.issued % kStages;
-  const int first = batch * kPeerBatch;                 // first contributor of this batch
-  const int local = lane - (first & 31);                // this lane's position inside the batch
-  const bool mine = local >= 0 && local < kPeerBatch && first + local < n;
-  const char* src = (first < 32) ? ptr_a : ptr_b;
-  const bool valid = mine && src != nullptr;
-  const unsigned votes = __ballot_sync(0xffffffffu, valid);
-  __syncwarp();                                         // everyone finished reading this stage
-  if (lane == 0) {
-    fence_proxy_async();
-    mbarrier_arrive_expect_tx(ring.bars + stage, static_cast<unsigned>(__popc(votes)) * bytes);
-  }
-  __syncwarp();
-  if (valid) bulk_load_to_smem(ring.buffer + stage * kStageBytes + local * kStepBytes, src + offset, bytes,
-                               ring.bars + stage);
-  ++ring.issued;
+__device__ __forceinline__ void mbarrier_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar)) : "memory");
 }
 
-__device__ __forceinline__ bool ring_wait(WarpRing& ring) {
-  const int stage = ring.consumed % kStages;
-  const unsigned parity = (ring.consumed / kStages) & 1u;
+__device__ __forceinline__ bool mbarrier_wait(unsigned long long* bar, unsigned parity) {
   unsigned spins = 0;
-  while (!mbarrier_try_wait(ring.bars + stage, parity))
+  while (!mbarrier_try_wait(bar, parity))
     if (++spins > kMbarrierSpinLimit) return false;
   return true;
 }
 
-// Reduce one row segment [b0, b1) of token t. Lane j holds contributor j (ptr_a) and j + 32
-// (ptr_b), ascending rank order; self_index is this rank's own position or -1.
-__device__ __forceinline__ bool reduce_segment_bulk(WarpRing& ring, const char* ptr_a, const char* ptr_b, int n,
-                                                    int self_index, bool single_round, char* outp, long long b0,
-                                                    long long b1, int lane) {
-  const int batches = n == 0 ? 0 : (n + kPeerBatch - 1) / kPeerBatch;
-  const int steps = static_cast<int>((b1 - b0 + kStepBytes - 1) / kStepBytes);
-  if (batches == 0) {                                   // padding token: zero row
-    for (long long off = b0 + lane * 16; off < b1; off += kStepBytes) st_payload16(outp + off, make_uint4(0, 0, 0, 0));
-    return true;
-  }
-  const unsigned valid_a = __ballot_sync(0xffffffffu, ptr_a != nullptr);
-  const unsigned valid_b = __ballot_sync(0xffffffffu, ptr_b != nullptr);
-  const int units = steps * batches;
-  int issued = 0;
-  auto issue_next = [&]() {
-    const int step = issued / batches, batch = issued % batches;
-    const long long offset = b0 + static_cast<long long>(step) * kStepBytes;
-    const unsigned bytes = static_cast<unsigned>(min(static_cast<long long>(kStepBytes), b1 - offset));
-    ring_issue(ring, ptr_a, ptr_b, n, batch, offset, bytes, lane);
-    ++issued;
-  };
-  for (int u = 0; u < kStages - 1 && issued < units; ++u) issue_next();
-  float acc[8];
-  Chunk<4> local;
-  bool has_local = false;
-  for (int unit = 0; unit < units; ++unit) {
-    const int step = unit / batches, batch = unit % batches;
-    if (issued < units) issue_next();
-    if (!ring_wait(ring)) return false;
-    const long long offset = b0 + static_cast<long long>(step) * kStepBytes;
-    const bool active = offset + lane * 16 < b1;
-    if (batch == 0) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      has_local = false;
+struct BulkReduceArgs {
+  const unsigned long long* mask_arr;
+  const int* send_rows;
+  const char* partial;
+  const char* staging;
+  char* out;
+  unsigned* work_counter;
+  long long row_bytes;
+  int tokens;
+  int fan;
+  int self;
+  int partial_rows;
+  bool single_round;
+};
+
+// Returns false when a bounded wait gave up.
+__device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem, unsigned long long* full,
+                                            unsigned long long* empty, StageItem* items_smem) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rsegs = static_cast<int>((a.row_bytes + kSegMaxBytes - 1) / kSegMaxBytes);
+  const long long rseg_bytes = align_up((a.row_bytes + rsegs - 1) / rsegs, 512);
+  const long long items = static_cast<long long>(a.tokens) * rsegs;
+  bool ok = true;
+  if (warp == kConsumerWarps) {
+    // ---------------- producer ----------------
+    auto claim = [&]() -> long long {
+      unsigned v = 0;
+      if (lane == 0) v = atomicAdd(a.work_counter, 1u);
+      return __shfl_sync(0xffffffffu, v, 0);
+    };
+    long long item0 = claim();          // item whose route data is loaded (issued next iteration)
+    long long item1 = claim();          // item claimed, route data not yet requested
+    unsigned long long m0 = 0;
+    int row0 = -1;
+    if (item0 < items) {
+      const int t = static_cast<int>(item0 / rsegs);
+      m0 = a.mask_arr[t];
+      row0 = lane < a.fan ? a.send_rows[static_cast<long long>(t) * a.fan + lane] : -1;
     }
-    const char* stage = ring.buffer + (ring.consumed % kStages) * kStageBytes + lane * 16;
-    const int first = batch * kPeerBatch;
-    const unsigned valid = (first < 32 ? valid_a : valid_b) >> (first & 31);
-#pragma unroll
-    for (int i = 0; i < kPeerBatch; ++i) {
-      if (first + i < n && ((valid >> i) & 1u) && active) {
-        const uint4 v = *reinterpret_cast<const uint4*>(stage + i * kStepBytes);
-        Chunk<4> c;
-        c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
-        if (!single_round && first + i == self_index) {
-          local = c;
-          has_local = true;
-        } else {
-          accumulate<4>(acc, c);
-        }
+    for (unsigned use = 0;; ++use) {
+      const int stage = use % kStages;
+      const unsigned parity = ((use / kStages) & 1u) ^ 1u;
+      // Prefetch: route data of item1, claim of the item after it.
+      unsigned long long m1 = 0;
+      int row1 = -1;
+      if (item1 < items) {
+        const int t1 = static_cast<int>(item1 / rsegs);
+        m1 = a.mask_arr[t1];
+        row1 = lane < a.fan ? a.send_rows[static_cast<long long>(t1) * a.fan + lane] : -1;
       }
+      const long long item2 = item1 < items ? claim() : item1;
+      if (!mbarrier_wait(empty + stage, parity)) { ok = false; break; }
+      if (item0 >= items) {
+        if (lane == 0) {
+          items_smem[stage].end = 1;
+          mbarrier_arrive(full + stage);
+        }
+        break;
+      }
+      const int t = static_cast<int>(item0 / rsegs), seg = static_cast<int>(item0 % rsegs);
+      const int n = __popcll(m0);
+      const long long b0 = seg * rseg_bytes;
+      const int bytes = static_cast<int>(min(a.row_bytes, b0 + rseg_bytes) - b0);
+      const char* src = nullptr;
+      bool is_self = false;
+      if (lane < n) {
+        const int d = nth_set_bit(m0, lane);
+        is_self = d == a.self;
+        if (row0 >= 0 && !(is_self && row0 >= a.partial_rows))
+          src = is_self ? a.partial + static_cast<long long>(row0) * a.row_bytes
+                        : a.staging + (static_cast<long long>(t) * a.fan + lane) * a.row_bytes;
+      }
+      const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
+      const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
+      if (lane == 0) {
+        StageItem& item = items_smem[stage];
+        item.out_offset = static_cast<long long>(t) * a.row_bytes + b0;
+        item.bytes = bytes;
+        item.contributors = n;
+        item.self_index = self_vote ? __ffs(self_vote) - 1 : -1;
+        item.valid = valid;
+        item.end = 0;
+        fence_proxy_async();
+        mbarrier_arrive_expect_tx(full + stage, static_cast<unsigned>(__popc(valid)) * static_cast<unsigned>(bytes));
+      }
+      __syncwarp();
+      if (src != nullptr)
+        bulk_load_to_smem(smem + static_cast<size_t>(stage) * kStageBytes + lane * kSegMaxBytes, src + b0,
+                          static_cast<unsigned>(bytes), full + stage);
+      item0 = item1; m0 = m1; row0 = row1; item1 = item2;
     }
-    ++ring.consumed;
-    if (batch == batches - 1 && active)
-      store_chunk<4>(outp + offset + lane * 16, finish<4>(acc, local, has_local, single_round));
+  } else {
+    // ---------------- consumers ----------------
+    for (unsigned use = 0;; ++use) {
+      const int stage = use % kStages;
+      const unsigned parity = (use / kStages) & 1u;
+      if (!mbarrier_wait(full + stage, parity)) { ok = false; break; }
+      const StageItem item = items_smem[stage];
+      if (item.end) break;
+      const char* base = smem + static_cast<size_t>(stage) * kStageBytes;
+      for (int chunk = tid; chunk * 16 < item.bytes; chunk += kThreads) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        Chunk<4> local;
+        bool has_local = false;
+#pragma unroll
+        for (int j = 0; j < kPeerBatch; ++j) {
+          if (j < item.contributors && ((item.valid >> j) & 1u)) {
+            const uint4 v = *reinterpret_cast<const uint4*>(base + j * kSegMaxBytes + chunk * 16);
+            Chunk<4> c;
+            c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
+            if (!a.single_round && j == item.self_index) {
+              local = c;
+              has_local = true;
+            } else {
+              accumulate<4>(acc, c);
+            }
+          }
+        }
+        store_chunk<4>(a.out + item.out_offset + chunk * 16, finish<4>(acc, local, has_local, a.single_round));
+      }
+      __syncwarp();
+      if (lane == 0) mbarrier_arrive(empty + stage);
+    }
   }
-  return true;
+  return ok;
 }
 
-template <bool kVec16>
+template <bool kVec16, bool kBulk>
 __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_smem) {
   constexpr int kWords = kVec16 ? 4 : 1;
   constexpr int kChunk = kWords * 4;
@@ -400,21 +456,24 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   profile_stamp(op.profile, 2);
 
   // ---- D. rank-order reduce from local memory -----------------------------------------------
-  {
-    __shared__ unsigned long long s_bars[kCombineWarps * kStages];
-    WarpRing ring;
-    ring.buffer = dynamic_smem + static_cast<size_t>(tid >> 5) * kWarpRingBytes;
-    ring.bars = s_bars + (tid >> 5) * kStages;
-    ring.issued = ring.consumed = 0;
-    if (kVec16) {
-      if (lane < kStages) mbarrier_init(ring.bars + lane, 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      fence_proxy_async();
-      __syncwarp();
+  if (kBulk) {
+    __shared__ unsigned long long s_full[kStages], s_empty[kStages];
+    __shared__ StageItem s_items[kStages];
+    if (tid < kStages) {
+      mbarrier_init(s_full + tid, 1);
+      mbarrier_init(s_empty + tid, kConsumerWarps);
     }
-    bool healthy = true;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+    __syncthreads();
+    BulkReduceArgs a;
+    a.mask_arr = mask_arr; a.send_rows = send_rows; a.partial = partial; a.staging = staging;
+    a.out = reinterpret_cast<char*>(op.out); a.work_counter = &hdr->cwork_reduce; a.row_bytes = row_bytes;
+    a.tokens = T; a.fan = fan; a.self = self; a.partial_rows = op.partial_rows; a.single_round = single_round;
+    if (!bulk_reduce(a, dynamic_smem, s_full, s_empty, s_items)) report_error(c, kTimeout, kPhaseCombine, 4, 0);
+  } else {
     const long long items = static_cast<long long>(T) * segs;
-    while (healthy) {
+    while (true) {
       unsigned claimed = 0;
       if (lane == 0) claimed = atomicAdd(&hdr->cwork_reduce, 1u);
       const long long item = __shfl_sync(0xffffffffu, claimed, 0);
@@ -460,9 +519,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
           : __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(self_index < 32 ? ptr_a : ptr_b), self_index & 31);
       const char* const local_ptr = reinterpret_cast<const char*>(local_bits);
 
-      if (kVec16) {
-        healthy = reduce_segment_bulk(ring, ptr_a, ptr_b, n, self_index, single_round, outp, b0, b1, lane);
-      } else if (n <= kPeerBatch) {
+      if (n <= kPeerBatch) {
         // Common case: every contributor's row pointer sits in a register.
         RowPointers rp;
 #pragma unroll
@@ -477,7 +534,6 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
         reduce_rows_generic<kWords>(ptr_a, ptr_b, n, skip, local_ptr, outp, b0, b1, lane, single_round);
       }
     }
-    if (!healthy) report_error(c, kTimeout, kPhaseCombine, 4, 0);
   }
 
   // ---- E. retire the epoch ---------------------------------------------------------------
@@ -496,49 +552,57 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   }
 }
 
-template <bool kVec16>
-__global__ void __launch_bounds__(kThreads, 1) combine_kernel(const __grid_constant__ CombineArgs args) {
+template <bool kVec16, bool kBulk>
+__global__ void __launch_bounds__(kBulk ? kBulkThreads : kThreads, 1)
+combine_kernel(const __grid_constant__ CombineArgs args) {
   extern __shared__ __align__(128) char combine_smem[];
-  combine_body<kVec16>(args.op[blockIdx.y], combine_smem);
+  combine_body<kVec16, kBulk>(args.op[blockIdx.y], combine_smem);
 }
 
-template <bool kVec16>
-cudaError_t prepare_combine_kernel(size_t* dynamic_smem) {
-  *dynamic_smem = kVec16 ? kCombineSmemBytes : 0;
-  if (*dynamic_smem <= 48 * 1024) return cudaSuccess;
-  return cudaFuncSetAttribute(combine_kernel<kVec16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(*dynamic_smem));
+struct CombineVariant {
+  const void* kernel;
+  int threads;
+  size_t dynamic_smem;
+};
+
+// The bulk-copy reduce needs 16-byte rows and at most kPeerBatch contributors per token.
+cudaError_t pick_combine(bool vec16, int fanout, CombineVariant* out) {
+  if (vec16 && fanout <= kPeerBatch) {
+    *out = {reinterpret_cast<const void*>(combine_kernel<true, true>), kBulkThreads, kBulkSmemBytes};
+    return cudaFuncSetAttribute(combine_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(kBulkSmemBytes));
+  }
+  if (vec16) *out = {reinterpret_cast<const void*>(combine_kernel<true, false>), kThreads, 0};
+  else *out = {reinterpret_cast<const void*>(combine_kernel<false, false>), kThreads, 0};
+  return cudaSuccess;
 }
 
 }  // namespace
 
-cudaError_t combine_max_ctas(bool vec16, int* ctas) {
+cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas) {
   int device = 0, sms = 0, per_sm = 0;
   cudaError_t err = cudaGetDevice(&device);
   if (err != cudaSuccess) return err;
   err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (err != cudaSuccess) return err;
-  size_t smem = 0;
-  err = vec16 ? prepare_combine_kernel<true>(&smem) : prepare_combine_kernel<false>(&smem);
+  CombineVariant variant;
+  err = pick_combine(vec16, fanout, &variant);
   if (err != cudaSuccess) return err;
-  err = vec16 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<true>, kThreads, smem)
-              : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, combine_kernel<false>, kThreads, smem);
+  err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, variant.kernel, variant.threads, variant.dynamic_smem);
   if (err != cudaSuccess) return err;
   *ctas = per_sm * sms;
   return cudaSuccess;
 }
 
-cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, bool cooperative,
-                           cudaStream_t stream) {
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout,
+                           bool cooperative, cudaStream_t stream) {
   void* params[] = {const_cast<CombineArgs*>(&args)};
-  size_t smem = 0;
-  cudaError_t err = vec16 ? prepare_combine_kernel<true>(&smem) : prepare_combine_kernel<false>(&smem);
+  CombineVariant variant;
+  cudaError_t err = pick_combine(vec16, fanout, &variant);
   if (err != cudaSuccess) return err;
-  const void* kernel = vec16 ? reinterpret_cast<const void*>(combine_kernel<true>)
-                             : reinterpret_cast<const void*>(combine_kernel<false>);
-  if (!cooperative)
-    return cudaLaunchKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, smem, stream);
-  return cudaLaunchCooperativeKernel(kernel, dim3(ctas_per_rank, ranks, 1), dim3(kThreads, 1, 1), params, smem, stream);
+  const dim3 grid(ctas_per_rank, ranks, 1), block(variant.threads, 1, 1);
+  if (!cooperative) return cudaLaunchKernel(variant.kernel, grid, block, params, variant.dynamic_smem, stream);
+  return cudaLaunchCooperativeKernel(variant.kernel, grid, block, params, variant.dynamic_smem, stream);
 }
 
 }  // namespace epx

@@ -122,7 +122,7 @@ class Engine {
       }
     for (int vec = 0; vec < 2; ++vec) {
       int ctas = 0;
-      cuda_check(combine_max_ctas(vec, &ctas), "combine occupancy query");
+      cuda_check(combine_max_ctas(vec, route_fanout(topk_, world_), &ctas), "combine occupancy query");
       best = std::min(best, ctas);
     }
     return best / static_cast<int>(local_ranks_.size());
@@ -265,7 +265,8 @@ class Engine {
       args.op[i].vec16 = vec16 ? 1 : 0;
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
-    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, cooperative_, stream_of(stream)), "combine launch");
+    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, route_fanout(topk_, world_), cooperative_,
+                              stream_of(stream)), "combine launch");
   }
 
   void scale_rows(const at::Tensor& hidden, const at::Tensor& local_ids, const at::Tensor& weights,

@@ -14,7 +14,7 @@ size_t dispatch_dynamic_smem(int max_tokens, int world);
 // negotiates the same bound through an occupancy query,
 // ep_xpress/csrc/host_sm.cu:2516-2564.)
 cudaError_t dispatch_max_ctas(bool ids64, bool vec16, size_t dynamic_smem, int* ctas);
-cudaError_t combine_max_ctas(bool vec16, int* ctas);
+cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas);
 
 // `cooperative` selects cudaLaunchCooperativeKernel (the driver guarantees that all CTAs are
 // resident together) over a plain launch (cheaper to enqueue; co-residency then rests on the
@@ -22,8 +22,8 @@ cudaError_t combine_max_ctas(bool vec16, int* ctas);
 // other kernel holding the SMs forever).
 cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
                             size_t dynamic_smem, bool cooperative, cudaStream_t stream);
-cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, bool cooperative,
-                           cudaStream_t stream);
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout,
+                           bool cooperative, cudaStream_t stream);
 
 // Synthetic expert used by the validation harness and the communication
 // benchmark: partial[row] = bf16(hidden[row] * sum_k weights[row,k] * factor[local_ids[row,k]])
