@@ -251,13 +251,13 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   bool ok = true;
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
-    auto claim = [&]() -> long long {
-      unsigned v = 0;
-      if (lane == 0) v = atomicAdd(a.work_counter, 1u);
-      return __shfl_sync(0xffffffffu, v, 0);
-    };
-    long long item0 = claim();          // item whose route data is loaded (issued next iteration)
-    long long item1 = claim();          // item claimed, route data not yet requested
+    // Claims are issued early and only broadcast one iteration later, so the atomic's round
+    // trip never sits on the critical path.
+    auto claim_raw = [&]() -> unsigned { return lane == 0 ? atomicAdd(a.work_counter, 1u) : 0u; };
+    auto broadcast = [&](unsigned raw) -> long long { return __shfl_sync(0xffffffffu, raw, 0); };
+    long long item0 = broadcast(claim_raw());   // item whose route data is loaded (issued next iteration)
+    long long item1 = broadcast(claim_raw());   // item claimed, route data not yet requested
+    unsigned raw2 = claim_raw();                // claim in flight
     unsigned long long m0 = 0;
     int row0 = -1;
     if (item0 < items) {
@@ -276,7 +276,6 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
         m1 = a.mask_arr[t1];
         row1 = lane < a.fan ? a.send_rows[static_cast<long long>(t1) * a.fan + lane] : -1;
       }
-      const long long item2 = item1 < items ? claim() : item1;
       if (!mbarrier_wait(empty + stage, parity)) { ok = false; break; }
       if (item0 >= items) {
         if (lane == 0) {
@@ -315,7 +314,9 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       if (src != nullptr)
         bulk_load_to_smem(smem + static_cast<size_t>(stage) * kStageBytes + lane * kSegMaxBytes, src + b0,
                           static_cast<unsigned>(bytes), full + stage);
-      item0 = item1; m0 = m1; row0 = row1; item1 = item2;
+      item0 = item1; m0 = m1; row0 = row1;
+      item1 = broadcast(raw2);
+      raw2 = item1 < items ? claim_raw() : 0xffffffffu;
     }
   } else {
     // ---------------- consumers ----------------
@@ -401,11 +402,11 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   // ---- A. push my rows to the ranks that own the tokens ---------------------------
   {
     const long long items = static_cast<long long>(valid) * segs;
+    unsigned next_claim = lane == 0 ? atomicAdd(&hdr->cwork_push, 1u) : 0u;
     while (true) {
-      unsigned claimed = 0;
-      if (lane == 0) claimed = atomicAdd(&hdr->cwork_push, 1u);
-      const long long item = __shfl_sync(0xffffffffu, claimed, 0);
+      const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
       if (item >= items) break;
+      if (lane == 0) next_claim = atomicAdd(&hdr->cwork_push, 1u);   // in flight while this item is copied
       const long long row = item / segs;
       const int seg = static_cast<int>(item % segs);
       const int source = static_cast<int>(inverse[row * 2]);

@@ -263,11 +263,11 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   const long long items = static_cast<long long>(T) * segs;
   // Work items are claimed from a rank-local counter: SMs differ in how fast their
   // stores drain towards NVLink, and a static split leaves the fast ones idle.
+  unsigned next_claim = lane == 0 ? atomicAdd(&hdr->work_next, 1u) : 0u;
   while (true) {
-    unsigned claimed = 0;
-    if (lane == 0) claimed = atomicAdd(&hdr->work_next, 1u);
-    const long long item = __shfl_sync(0xffffffffu, claimed, 0);
+    const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
     if (item >= items) break;
+    if (lane == 0) next_claim = atomicAdd(&hdr->work_next, 1u);   // in flight while this item is copied
     const int t = static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
     const unsigned long long m = mask_arr[t];
     if (!m) continue;
