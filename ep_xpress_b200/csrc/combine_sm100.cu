@@ -199,10 +199,16 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 // ahead by the producer instead of sitting on every warp's critical path.
 constexpr int kConsumerWarps = kThreads / 32;
 constexpr int kBulkThreads = kThreads + 32;       // + the producer warp
-constexpr int kStages = 3;
+constexpr int kMaxStages = 12;
 constexpr int kSegMaxBytes = 8192;                // largest row segment of one item
-constexpr int kStageBytes = kPeerBatch * kSegMaxBytes;
-constexpr size_t kBulkSmemBytes = static_cast<size_t>(kStages) * kStageBytes;
+constexpr size_t kBulkSmemBytes = 3 * kPeerBatch * kSegMaxBytes;   // 192 KiB ring
+// A stage holds one item: `fan` contributor slots of kSegMaxBytes. Narrow fan-outs get more,
+// smaller stages out of the same ring, so the bytes in flight stay high when few ranks
+// contribute to a token.
+__device__ __forceinline__ int ring_stages(int fan) {
+  const int fit = static_cast<int>(kBulkSmemBytes / (static_cast<size_t>(fan) * kSegMaxBytes));
+  return fit < kMaxStages ? fit : kMaxStages;
+}
 constexpr unsigned kMbarrierSpinLimit = 1u << 22;
 
 struct StageItem {
@@ -248,6 +254,8 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   const int rsegs = static_cast<int>((a.row_bytes + kSegMaxBytes - 1) / kSegMaxBytes);
   const long long rseg_bytes = align_up((a.row_bytes + rsegs - 1) / rsegs, 512);
   const long long items = static_cast<long long>(a.tokens) * rsegs;
+  const int stages = ring_stages(a.fan);
+  const size_t stage_bytes = static_cast<size_t>(a.fan) * kSegMaxBytes;
   bool ok = true;
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
@@ -266,8 +274,8 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       row0 = lane < a.fan ? a.send_rows[static_cast<long long>(t) * a.fan + lane] : -1;
     }
     for (unsigned use = 0;; ++use) {
-      const int stage = use % kStages;
-      const unsigned parity = ((use / kStages) & 1u) ^ 1u;
+      const int stage = use % stages;
+      const unsigned parity = ((use / stages) & 1u) ^ 1u;
       // Prefetch: route data of item1, claim of the item after it.
       unsigned long long m1 = 0;
       int row1 = -1;
@@ -312,7 +320,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       }
       __syncwarp();
       if (src != nullptr)
-        bulk_load_to_smem(smem + static_cast<size_t>(stage) * kStageBytes + lane * kSegMaxBytes, src + b0,
+        bulk_load_to_smem(smem + static_cast<size_t>(stage) * stage_bytes + lane * kSegMaxBytes, src + b0,
                           static_cast<unsigned>(bytes), full + stage);
       item0 = item1; m0 = m1; row0 = row1;
       item1 = broadcast(raw2);
@@ -321,12 +329,12 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   } else {
     // ---------------- consumers ----------------
     for (unsigned use = 0;; ++use) {
-      const int stage = use % kStages;
-      const unsigned parity = (use / kStages) & 1u;
+      const int stage = use % stages;
+      const unsigned parity = (use / stages) & 1u;
       if (!mbarrier_wait(full + stage, parity)) { ok = false; break; }
       const StageItem item = items_smem[stage];
       if (item.end) break;
-      const char* base = smem + static_cast<size_t>(stage) * kStageBytes;
+      const char* base = smem + static_cast<size_t>(stage) * stage_bytes;
       for (int chunk = tid; chunk * 16 < item.bytes; chunk += kThreads) {
         float acc[8];
 #pragma unroll
@@ -458,9 +466,9 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
 
   // ---- D. rank-order reduce from local memory -----------------------------------------------
   if (kBulk) {
-    __shared__ unsigned long long s_full[kStages], s_empty[kStages];
-    __shared__ StageItem s_items[kStages];
-    if (tid < kStages) {
+    __shared__ unsigned long long s_full[kMaxStages], s_empty[kMaxStages];
+    __shared__ StageItem s_items[kMaxStages];
+    if (tid < kMaxStages) {
       mbarrier_init(s_full + tid, 1);
       mbarrier_init(s_empty + tid, kConsumerWarps);
     }

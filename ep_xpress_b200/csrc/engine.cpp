@@ -21,6 +21,7 @@
 namespace py = pybind11;
 
 namespace epx {
+void bind_moe(py::module_& m);   // moe_bindings.cpp
 namespace {
 
 void cuda_check(cudaError_t err, const char* what) {
@@ -414,4 +415,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("status", &Engine::status)
       .def("poke_u64", &Engine::poke_u64)
       .def("peek_u64", &Engine::peek_u64);
+  epx::bind_moe(m);
 }

@@ -1,0 +1,55 @@
+"""tcgen05 grouped SwiGLU runner against a plain PyTorch FP32 statement of the same op."""
+
+import pytest
+import torch
+
+from conftest import gpu_count
+
+from ep_xpress_b200.ops import GroupedSwiGLU, swiglu_reference
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(gpu_count() < 1, reason="needs a CUDA device")]
+
+
+def make_case(rows, topk, experts, hidden, inter, valid, seed, local_fraction=0.6):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = (torch.randn((rows, hidden), generator=g) * 0.5).to(torch.bfloat16)
+    ids = torch.full((rows, topk), -1, dtype=torch.int64)
+    for r in range(rows):
+        chosen = torch.randperm(experts, generator=g)[:min(topk, experts)]
+        keep = torch.rand(len(chosen), generator=g) < local_fraction
+        ids[r, :len(chosen)] = torch.where(keep, chosen, torch.full_like(chosen, -1))
+    weights = torch.rand((rows, topk), generator=g).to(torch.float32)
+    w13 = (torch.randn((experts, 2 * inter, hidden), generator=g) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn((experts, hidden, inter), generator=g) * 0.05).to(torch.bfloat16)
+    count = torch.tensor([valid], dtype=torch.int32)
+    return [t.cuda() for t in (x, ids, weights, count, w13, w2)]
+
+
+@pytest.mark.parametrize("rows,topk,experts,hidden,inter,valid", [
+    (64, 2, 2, 256, 128, 64),
+    (300, 4, 3, 512, 256, 257),
+    (1000, 8, 8, 1024, 384, 1000),
+    (130, 8, 32, 256, 128, 0),
+])
+def test_matches_fp32_reference(rows, topk, experts, hidden, inter, valid):
+    x, ids, weights, count, w13, w2 = make_case(rows, topk, experts, hidden, inter, valid, seed=rows)
+    runner = GroupedSwiGLU(w13, w2, max_rows=rows, topk=topk)
+    out = torch.full((rows, hidden), 7.0, dtype=torch.bfloat16, device="cuda")
+    runner(x, ids, weights, count, out=out)
+    runner.check()
+    want = swiglu_reference(x, ids, weights, valid, w13, w2)
+    got, ref = out[:valid].float(), want[:valid].float()
+    scale = ref.abs().max().clamp(min=1e-3)
+    assert ((got - ref).abs().max() / scale).item() < 2e-2
+    assert (out[valid:] == 7.0).all()          # rows at or above valid_count are not touched
+    again = torch.empty_like(out)
+    runner(x, ids, weights, count, out=again)  # order of pairs inside an expert never changes a result
+    assert torch.equal(again[:valid], out[:valid])
+
+
+def test_pair_bound_overflow_is_reported():
+    x, ids, weights, count, w13, w2 = make_case(512, 4, 2, 256, 128, 512, seed=3, local_fraction=1.0)
+    runner = GroupedSwiGLU(w13, w2, max_rows=512, topk=4, max_local_pairs=128)
+    runner(x, ids, weights, count)
+    with pytest.raises(RuntimeError, match="max_local_pairs"):
+        runner.check()
