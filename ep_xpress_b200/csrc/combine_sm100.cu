@@ -209,7 +209,6 @@ __device__ __forceinline__ int ring_stages(int fan) {
   const int fit = static_cast<int>(kBulkSmemBytes / (static_cast<size_t>(fan) * kSegMaxBytes));
   return fit < kMaxStages ? fit : kMaxStages;
 }
-constexpr unsigned kMbarrierSpinLimit = 1u << 22;
 
 struct StageItem {
   long long out_offset;   // byte offset of the segment inside the output tensor
@@ -225,12 +224,7 @@ __device__ __forceinline__ void mbarrier_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar)) : "memory");
 }
 
-__device__ __forceinline__ bool mbarrier_wait(unsigned long long* bar, unsigned parity) {
-  unsigned spins = 0;
-  while (!mbarrier_try_wait(bar, parity))
-    if (++spins > kMbarrierSpinLimit) return false;
-  return true;
-}
+
 
 struct BulkReduceArgs {
   const unsigned long long* mask_arr;
@@ -245,6 +239,7 @@ struct BulkReduceArgs {
   int self;
   int partial_rows;
   bool single_round;
+  unsigned long long timeout_ns;
 };
 
 // Returns false when a bounded wait gave up.
@@ -284,7 +279,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
         m1 = a.mask_arr[t1];
         row1 = lane < a.fan ? a.send_rows[static_cast<long long>(t1) * a.fan + lane] : -1;
       }
-      if (!mbarrier_wait(empty + stage, parity)) { ok = false; break; }
+      if (!mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns)) { ok = false; break; }
       if (item0 >= items) {
         if (lane == 0) {
           items_smem[stage].end = 1;
@@ -331,7 +326,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
     for (unsigned use = 0;; ++use) {
       const int stage = use % stages;
       const unsigned parity = (use / stages) & 1u;
-      if (!mbarrier_wait(full + stage, parity)) { ok = false; break; }
+      if (!mbarrier_wait_bounded(full + stage, parity, a.timeout_ns)) { ok = false; break; }
       const StageItem item = items_smem[stage];
       if (item.end) break;
       const char* base = smem + static_cast<size_t>(stage) * stage_bytes;
@@ -478,7 +473,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     BulkReduceArgs a;
     a.mask_arr = mask_arr; a.send_rows = send_rows; a.partial = partial; a.staging = staging;
     a.out = reinterpret_cast<char*>(op.out); a.work_counter = &hdr->cwork_reduce; a.row_bytes = row_bytes;
-    a.tokens = T; a.fan = fan; a.self = self; a.partial_rows = op.partial_rows; a.single_round = single_round;
+    a.tokens = T; a.fan = fan; a.self = self; a.partial_rows = op.partial_rows; a.single_round = single_round; a.timeout_ns = c.timeout_ns;
     if (!bulk_reduce(a, dynamic_smem, s_full, s_empty, s_items)) report_error(c, kTimeout, kPhaseCombine, 4, 0);
   } else {
     const long long items = static_cast<long long>(T) * segs;

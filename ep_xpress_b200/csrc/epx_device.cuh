@@ -169,6 +169,17 @@ __device__ __forceinline__ bool mbarrier_try_wait(unsigned long long* bar, unsig
       : "=r"(done) : "r"(smem_address(bar)), "r"(parity) : "memory");
   return done != 0;
 }
+// Waits for the phase with `parity` of an mbarrier, at most `timeout_ns` on the GPU's global
+// timer. Returns false when it gave up; the caller then unwinds and reports an error.
+__device__ __forceinline__ bool mbarrier_wait_bounded(unsigned long long* bar, unsigned parity,
+                                                      unsigned long long timeout_ns) {
+  if (mbarrier_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer_ns();
+  unsigned spins = 0;
+  while (!mbarrier_try_wait(bar, parity))
+    if ((++spins & 255u) == 0 && global_timer_ns() - start > timeout_ns) return false;
+  return true;
+}
 // Global -> shared copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) that
 // signals `bar` with its byte count when the data has landed. Destination is this CTA's own
 // shared memory; one copy per call, no fan-out.

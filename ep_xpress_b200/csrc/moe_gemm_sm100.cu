@@ -43,7 +43,7 @@ constexpr int kBBytes = kTileN * kTileK * 2;
 constexpr int kStageBytesGemm = kABytes + kBBytes;
 constexpr int kGemmThreads = 192;
 constexpr int kAccumColumns = 256;
-constexpr unsigned kGemmSpinLimit = 1u << 24;
+constexpr unsigned long long kGemmWaitNs = 2000000000ull;   // bound of every pipeline wait: 2 s
 
 // ---- PTX wrappers ----------------------------------------------------------------------
 __device__ __forceinline__ bool elect_one() {
@@ -55,10 +55,7 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-  unsigned spins = 0;
-  while (!mbarrier_try_wait(bar, parity))
-    if (++spins > kGemmSpinLimit) return false;
-  return true;
+  return mbarrier_wait_bounded(bar, parity, kGemmWaitNs);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
   asm volatile(
@@ -224,10 +221,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local_tile) {
       const int m_tile = static_cast<int>(tile / p.n_tiles), n_tile = static_cast<int>(tile % p.n_tiles);
       const unsigned buffer = local_tile & 1u;
-      bool ok = true;
-      if (lane == 0) ok = mbar_wait(acc_full + buffer, (local_tile >> 1) & 1u);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) { failed = 1; break; }
+      const bool ok = mbar_wait(acc_full + buffer, (local_tile >> 1) & 1u);
+      if (!__all_sync(0xffffffffu, ok)) { failed = 1; break; }
       tcgen05_fence_after();
       const unsigned taddr = tmem_base + buffer * kAccumColumns + (static_cast<unsigned>(quadrant * 32) << 16);
       const long long row = static_cast<long long>(m_tile) * kTileM + row_in_tile;
