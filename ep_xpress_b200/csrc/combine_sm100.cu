@@ -254,72 +254,91 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   bool ok = true;
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
-    // Claims are issued early and only broadcast one iteration later, so the atomic's round
-    // trip never sits on the critical path.
-    auto claim_raw = [&]() -> unsigned { return lane == 0 ? atomicAdd(a.work_counter, 1u) : 0u; };
-    auto broadcast = [&](unsigned raw) -> long long { return __shfl_sync(0xffffffffu, raw, 0); };
-    long long item0 = broadcast(claim_raw());   // item whose route data is loaded (issued next iteration)
-    long long item1 = broadcast(claim_raw());   // item claimed, route data not yet requested
-    unsigned raw2 = claim_raw();                // claim in flight
-    unsigned long long m0 = 0;
-    int row0 = -1;
-    if (item0 < items) {
-      const int t = static_cast<int>(item0 / rsegs);
-      m0 = a.mask_arr[t];
-      row0 = lane < a.fan ? a.send_rows[static_cast<long long>(t) * a.fan + lane] : -1;
+    // Items of this CTA are a contiguous range (the phase reads local memory only, so a
+    // static split is balanced). Route look-ups are done for 32 items at once - lane L loads
+    // the mask of item L, lane 8q + j the row index of contributor j of item 4r + q - and
+    // the next batch is requested before the current one is issued, so their latency is
+    // paid once per batch instead of once per item.
+    const long long lo = items * blockIdx.x / gridDim.x, hi = items * (blockIdx.x + 1) / gridDim.x;
+    auto load_batch = [&](long long base, unsigned long long& mask, int (&rows)[8]) {
+      const long long mine = base + lane;
+      mask = mine < hi ? a.mask_arr[mine / rsegs] : 0ull;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const long long item = base + 4 * r + (lane >> 3);
+        const int j = lane & 7;
+        rows[r] = (item < hi && j < a.fan) ? a.send_rows[(item / rsegs) * a.fan + j] : -1;
+      }
+    };
+    unsigned long long mask_now = 0, mask_next = 0;
+    int rows_now[8], rows_next[8];
+    load_batch(lo, mask_now, rows_now);
+    unsigned use = 0;
+    for (long long base = lo; base < hi && ok; base += 32) {
+      if (base + 32 < hi) load_batch(base + 32, mask_next, rows_next);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int i = 4 * r + q;
+          const long long item = base + i;
+          const unsigned long long m = __shfl_sync(0xffffffffu, mask_now, i);
+          const int row = __shfl_sync(0xffffffffu, rows_now[r], q * 8 + (lane & 7));
+          if (item >= hi || !ok) continue;                 // warp-uniform
+          const int stage = use % stages;
+          const unsigned parity = ((use / stages) & 1u) ^ 1u;
+          ++use;
+          if (!__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
+            ok = false;
+            continue;
+          }
+          const int t = static_cast<int>(item / rsegs), seg = static_cast<int>(item % rsegs);
+          const int n = __popcll(m);
+          const long long b0 = seg * rseg_bytes;
+          const int bytes = static_cast<int>(min(a.row_bytes, b0 + rseg_bytes) - b0);
+          const char* src = nullptr;
+          bool is_self = false;
+          if (lane < n) {
+            const int d = nth_set_bit(m, lane);
+            is_self = d == a.self;
+            if (row >= 0 && !(is_self && row >= a.partial_rows))
+              src = is_self ? a.partial + static_cast<long long>(row) * a.row_bytes
+                            : a.staging + (static_cast<long long>(t) * a.fan + lane) * a.row_bytes;
+          }
+          const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
+          const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
+          if (lane == 0) {
+            StageItem& slot = items_smem[stage];
+            slot.out_offset = static_cast<long long>(t) * a.row_bytes + b0;
+            slot.bytes = bytes;
+            slot.contributors = n;
+            slot.self_index = self_vote ? __ffs(self_vote) - 1 : -1;
+            slot.valid = valid;
+            slot.end = 0;
+            fence_proxy_async();
+            mbarrier_arrive_expect_tx(full + stage, static_cast<unsigned>(__popc(valid)) * static_cast<unsigned>(bytes));
+          }
+          __syncwarp();
+          if (src != nullptr)
+            bulk_load_to_smem(smem + static_cast<size_t>(stage) * stage_bytes + lane * kSegMaxBytes, src + b0,
+                              static_cast<unsigned>(bytes), full + stage);
+        }
+      }
+      mask_now = mask_next;
+#pragma unroll
+      for (int r = 0; r < 8; ++r) rows_now[r] = rows_next[r];
     }
-    for (unsigned use = 0;; ++use) {
+    if (ok) {                                              // end marker
       const int stage = use % stages;
       const unsigned parity = ((use / stages) & 1u) ^ 1u;
-      // Prefetch: route data of item1, claim of the item after it.
-      unsigned long long m1 = 0;
-      int row1 = -1;
-      if (item1 < items) {
-        const int t1 = static_cast<int>(item1 / rsegs);
-        m1 = a.mask_arr[t1];
-        row1 = lane < a.fan ? a.send_rows[static_cast<long long>(t1) * a.fan + lane] : -1;
-      }
-      if (!mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns)) { ok = false; break; }
-      if (item0 >= items) {
+      if (__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
         if (lane == 0) {
           items_smem[stage].end = 1;
           mbarrier_arrive(full + stage);
         }
-        break;
+      } else {
+        ok = false;
       }
-      const int t = static_cast<int>(item0 / rsegs), seg = static_cast<int>(item0 % rsegs);
-      const int n = __popcll(m0);
-      const long long b0 = seg * rseg_bytes;
-      const int bytes = static_cast<int>(min(a.row_bytes, b0 + rseg_bytes) - b0);
-      const char* src = nullptr;
-      bool is_self = false;
-      if (lane < n) {
-        const int d = nth_set_bit(m0, lane);
-        is_self = d == a.self;
-        if (row0 >= 0 && !(is_self && row0 >= a.partial_rows))
-          src = is_self ? a.partial + static_cast<long long>(row0) * a.row_bytes
-                        : a.staging + (static_cast<long long>(t) * a.fan + lane) * a.row_bytes;
-      }
-      const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
-      const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
-      if (lane == 0) {
-        StageItem& item = items_smem[stage];
-        item.out_offset = static_cast<long long>(t) * a.row_bytes + b0;
-        item.bytes = bytes;
-        item.contributors = n;
-        item.self_index = self_vote ? __ffs(self_vote) - 1 : -1;
-        item.valid = valid;
-        item.end = 0;
-        fence_proxy_async();
-        mbarrier_arrive_expect_tx(full + stage, static_cast<unsigned>(__popc(valid)) * static_cast<unsigned>(bytes));
-      }
-      __syncwarp();
-      if (src != nullptr)
-        bulk_load_to_smem(smem + static_cast<size_t>(stage) * stage_bytes + lane * kSegMaxBytes, src + b0,
-                          static_cast<unsigned>(bytes), full + stage);
-      item0 = item1; m0 = m1; row0 = row1;
-      item1 = broadcast(raw2);
-      raw2 = item1 < items ? claim_raw() : 0xffffffffu;
     }
   } else {
     // ---------------- consumers ----------------

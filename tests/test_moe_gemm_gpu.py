@@ -39,8 +39,9 @@ def test_matches_fp32_reference(rows, topk, experts, hidden, inter, valid):
     runner.check()
     want = swiglu_reference(x, ids, weights, valid, w13, w2)
     got, ref = out[:valid].float(), want[:valid].float()
-    scale = ref.abs().max().clamp(min=1e-3)
-    assert ((got - ref).abs().max() / scale).item() < 2e-2
+    if valid:
+        scale = ref.abs().max().clamp(min=1e-3)
+        assert ((got - ref).abs().max() / scale).item() < 2e-2
     assert (out[valid:] == 7.0).all()          # rows at or above valid_count are not touched
     again = torch.empty_like(out)
     runner(x, ids, weights, count, out=again)  # order of pairs inside an expert never changes a result
