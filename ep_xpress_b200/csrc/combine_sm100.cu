@@ -200,6 +200,10 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 constexpr int kConsumerWarps = kThreads / 32;
 constexpr int kBulkThreads = kThreads + 32;       // + the producer warp
 constexpr int kMaxStages = 12;
+constexpr int kConsumerGroups = 4;
+constexpr int kGroupWarps = kConsumerWarps / kConsumerGroups;
+constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kChunksPerThread = 4;
 constexpr int kSegMaxBytes = 8192;                // largest row segment of one item
 constexpr size_t kBulkSmemBytes = 3 * kPeerBatch * kSegMaxBytes;   // 192 KiB ring
 // A stage holds one item: `fan` contributor slots of kSegMaxBytes. Narrow fan-outs get more,
@@ -328,7 +332,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
 #pragma unroll
       for (int r = 0; r < 8; ++r) rows_now[r] = rows_next[r];
     }
-    if (ok) {                                              // end marker
+    for (int marker = 0; marker < kConsumerGroups && ok; ++marker, ++use) {   // one end marker per group
       const int stage = use % stages;
       const unsigned parity = ((use / stages) & 1u) ^ 1u;
       if (__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
@@ -342,34 +346,49 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
     }
   } else {
     // ---------------- consumers ----------------
-    for (unsigned use = 0;; ++use) {
+    // Four groups of four warps; item number u belongs to group u % 4, so four items are
+    // reduced at once and every thread owns several independent 16-byte chunks of its item
+    // (instruction-level parallelism instead of one dependent chain per item).
+    const int group = warp / kGroupWarps, gtid = tid % kGroupThreads;
+    for (unsigned use = group;; use += kConsumerGroups) {
       const int stage = use % stages;
       const unsigned parity = (use / stages) & 1u;
       if (!mbarrier_wait_bounded(full + stage, parity, a.timeout_ns)) { ok = false; break; }
       const StageItem item = items_smem[stage];
       if (item.end) break;
       const char* base = smem + static_cast<size_t>(stage) * stage_bytes;
-      for (int chunk = tid; chunk * 16 < item.bytes; chunk += kThreads) {
-        float acc[8];
+      const int chunks = item.bytes / 16;
+      for (int first = gtid; first < chunks; first += kGroupThreads * kChunksPerThread) {
+        float acc[kChunksPerThread][8];
+        Chunk<4> local[kChunksPerThread];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        Chunk<4> local;
+        for (int u = 0; u < kChunksPerThread; ++u) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+        }
         bool has_local = false;
+        for (int j = 0; j < item.contributors; ++j) {
+          if (!((item.valid >> j) & 1u)) continue;
+          const bool is_local = !a.single_round && j == item.self_index;
+          has_local |= is_local;
 #pragma unroll
-        for (int j = 0; j < kPeerBatch; ++j) {
-          if (j < item.contributors && ((item.valid >> j) & 1u)) {
-            const uint4 v = *reinterpret_cast<const uint4*>(base + j * kSegMaxBytes + chunk * 16);
-            Chunk<4> c;
-            c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
-            if (!a.single_round && j == item.self_index) {
-              local = c;
-              has_local = true;
-            } else {
-              accumulate<4>(acc, c);
+          for (int u = 0; u < kChunksPerThread; ++u) {
+            const int chunk = first + u * kGroupThreads;
+            if (chunk < chunks) {
+              const uint4 v = *reinterpret_cast<const uint4*>(base + j * kSegMaxBytes + chunk * 16);
+              Chunk<4> c;
+              c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
+              if (is_local) local[u] = c;
+              else accumulate<4>(acc[u], c);
             }
           }
         }
-        store_chunk<4>(a.out + item.out_offset + chunk * 16, finish<4>(acc, local, has_local, a.single_round));
+#pragma unroll
+        for (int u = 0; u < kChunksPerThread; ++u) {
+          const int chunk = first + u * kGroupThreads;
+          if (chunk < chunks)
+            store_chunk<4>(a.out + item.out_offset + chunk * 16, finish<4>(acc[u], local[u], has_local, a.single_round));
+        }
       }
       __syncwarp();
       if (lane == 0) mbarrier_arrive(empty + stage);
@@ -484,7 +503,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     __shared__ StageItem s_items[kMaxStages];
     if (tid < kMaxStages) {
       mbarrier_init(s_full + tid, 1);
-      mbarrier_init(s_empty + tid, kConsumerWarps);
+      mbarrier_init(s_empty + tid, kGroupWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
