@@ -319,7 +319,6 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             slot.self_index = self_vote ? __ffs(self_vote) - 1 : -1;
             slot.valid = valid;
             slot.end = 0;
-            fence_proxy_async();
             mbarrier_arrive_expect_tx(full + stage, static_cast<unsigned>(__popc(valid)) * static_cast<unsigned>(bytes));
           }
           __syncwarp();
@@ -355,7 +354,11 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       const unsigned parity = (use / stages) & 1u;
       if (!mbarrier_wait_bounded(full + stage, parity, a.timeout_ns)) { ok = false; break; }
       const StageItem item = items_smem[stage];
-      if (item.end) break;
+      if (item.end) {                       // release the stage too: later end markers may reuse it
+        __syncwarp();
+        if (lane == 0) mbarrier_arrive(empty + stage);
+        break;
+      }
       const char* base = smem + static_cast<size_t>(stage) * stage_bytes;
       const int chunks = item.bytes / 16;
       for (int first = gtid; first < chunks; first += kGroupThreads * kChunksPerThread) {
