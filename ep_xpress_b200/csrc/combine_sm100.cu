@@ -199,8 +199,8 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 // ahead by the producer instead of sitting on every warp's critical path.
 constexpr int kConsumerWarps = kThreads / 32;
 constexpr int kBulkThreads = kThreads + 32;       // + the producer warp
-constexpr int kMaxStages = 12;
 constexpr int kConsumerGroups = 4;
+constexpr int kMaxStages = 12;
 constexpr int kGroupWarps = kConsumerWarps / kConsumerGroups;
 constexpr int kGroupThreads = kGroupWarps * 32;
 constexpr int kChunksPerThread = 4;
@@ -209,8 +209,15 @@ constexpr size_t kBulkSmemBytes = 3 * kPeerBatch * kSegMaxBytes;   // 192 KiB ri
 // A stage holds one item: `fan` contributor slots of kSegMaxBytes. Narrow fan-outs get more,
 // smaller stages out of the same ring, so the bytes in flight stay high when few ranks
 // contribute to a token.
-__device__ __forceinline__ int ring_stages(int fan) {
-  const int fit = static_cast<int>(kBulkSmemBytes / (static_cast<size_t>(fan) * kSegMaxBytes));
+// The stage count is a multiple of the consumer-group count, so a group always meets a
+// stage in consecutive rounds and the mbarrier phase parity it waits for is unambiguous.
+__device__ __forceinline__ int ring_segment_bytes(int fan) {
+  const int fit = static_cast<int>(kBulkSmemBytes / (static_cast<size_t>(kConsumerGroups) * fan)) / 512 * 512;
+  return fit < kSegMaxBytes ? fit : kSegMaxBytes;
+}
+__device__ __forceinline__ int ring_stages(int fan, int segment_bytes) {
+  const int fit = static_cast<int>(kBulkSmemBytes / (static_cast<size_t>(fan) * segment_bytes)) /
+                  kConsumerGroups * kConsumerGroups;
   return fit < kMaxStages ? fit : kMaxStages;
 }
 
@@ -244,17 +251,20 @@ struct BulkReduceArgs {
   int partial_rows;
   bool single_round;
   unsigned long long timeout_ns;
+  unsigned long long* profile;
 };
 
 // Returns false when a bounded wait gave up.
 __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem, unsigned long long* full,
                                             unsigned long long* empty, StageItem* items_smem) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int rsegs = static_cast<int>((a.row_bytes + kSegMaxBytes - 1) / kSegMaxBytes);
+  const int seg_max = ring_segment_bytes(a.fan);
+  const int rsegs = static_cast<int>((a.row_bytes + seg_max - 1) / seg_max);
   const long long rseg_bytes = align_up((a.row_bytes + rsegs - 1) / rsegs, 512);
   const long long items = static_cast<long long>(a.tokens) * rsegs;
-  const int stages = ring_stages(a.fan);
-  const size_t stage_bytes = static_cast<size_t>(a.fan) * kSegMaxBytes;
+  const int stages = ring_stages(a.fan, seg_max);
+  const size_t stage_bytes = static_cast<size_t>(a.fan) * seg_max;
+  long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
   bool ok = true;
   if (warp == kConsumerWarps) {
     // ---------------- producer ----------------
@@ -292,10 +302,12 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           const int stage = use % stages;
           const unsigned parity = ((use / stages) & 1u) ^ 1u;
           ++use;
+          const long long t0 = clock64();
           if (!__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
             ok = false;
             continue;
           }
+          waited += clock64() - t0;
           const int t = static_cast<int>(item / rsegs), seg = static_cast<int>(item % rsegs);
           const int n = __popcll(m);
           const long long b0 = seg * rseg_bytes;
@@ -323,7 +335,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           }
           __syncwarp();
           if (src != nullptr)
-            bulk_load_to_smem(smem + static_cast<size_t>(stage) * stage_bytes + lane * kSegMaxBytes, src + b0,
+            bulk_load_to_smem(smem + static_cast<size_t>(stage) * stage_bytes + lane * seg_max, src + b0,
                               static_cast<unsigned>(bytes), full + stage);
         }
       }
@@ -352,7 +364,10 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
     for (unsigned use = group;; use += kConsumerGroups) {
       const int stage = use % stages;
       const unsigned parity = (use / stages) & 1u;
+      const long long t0 = clock64();
       if (!mbarrier_wait_bounded(full + stage, parity, a.timeout_ns)) { ok = false; break; }
+      const long long t1 = clock64();
+      waited += t1 - t0;
       const StageItem item = items_smem[stage];
       if (item.end) {                       // release the stage too: later end markers may reuse it
         __syncwarp();
@@ -378,7 +393,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           for (int u = 0; u < kChunksPerThread; ++u) {
             const int chunk = first + u * kGroupThreads;
             if (chunk < chunks) {
-              const uint4 v = *reinterpret_cast<const uint4*>(base + j * kSegMaxBytes + chunk * 16);
+              const uint4 v = *reinterpret_cast<const uint4*>(base + j * seg_max + chunk * 16);
               Chunk<4> c;
               c.w[0] = v.x; c.w[1] = v.y; c.w[2] = v.z; c.w[3] = v.w;
               if (is_local) local[u] = c;
@@ -395,7 +410,13 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       }
       __syncwarp();
       if (lane == 0) mbarrier_arrive(empty + stage);
+      worked += clock64() - t1;
     }
+  }
+  if (a.profile != nullptr && lane == 0 && (warp == 0 || warp == kConsumerWarps)) {
+    unsigned long long* slot = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps + (warp == 0 ? 4 : 6);
+    slot[0] = static_cast<unsigned long long>(waited);
+    slot[1] = static_cast<unsigned long long>(worked);
   }
   return ok;
 }
@@ -514,7 +535,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     BulkReduceArgs a;
     a.mask_arr = mask_arr; a.send_rows = send_rows; a.partial = partial; a.staging = staging;
     a.out = reinterpret_cast<char*>(op.out); a.work_counter = &hdr->cwork_reduce; a.row_bytes = row_bytes;
-    a.tokens = T; a.fan = fan; a.self = self; a.partial_rows = op.partial_rows; a.single_round = single_round; a.timeout_ns = c.timeout_ns;
+    a.tokens = T; a.fan = fan; a.self = self; a.partial_rows = op.partial_rows; a.single_round = single_round; a.timeout_ns = c.timeout_ns; a.profile = op.profile;
     if (!bulk_reduce(a, dynamic_smem, s_full, s_empty, s_items)) report_error(c, kTimeout, kPhaseCombine, 4, 0);
   } else {
     const long long items = static_cast<long long>(T) * segs;

@@ -21,6 +21,8 @@ import torch
 _BUDGET_BYTES = 64 << 20
 DISPATCH_PHASES = ("start", "routed", "barrier", "counts_in", "payload_done", "signalled", "padded", "done")
 COMBINE_PHASES = ("start", "published", "peers_ready", "reduced")
+# combine stamps 4..7 are cycle counts, not times: consumer wait/work, producer wait/work
+COMBINE_CYCLES = ("consumer_wait_cycles", "consumer_work_cycles", "producer_wait_cycles", "producer_other_cycles")
 
 
 class OperationProfile:
@@ -66,6 +68,8 @@ class OperationProfile:
                 if reached.numel():
                     phases[name] = {"first_ns": int(reached.min()) - begin, "last_ns": int(reached.max()) - begin}
             entry = dict(record)
+            if record["kind"] == "combine":
+                entry["cycles"] = {name: float(stamps[:, 4 + i].double().mean()) for i, name in enumerate(COMBINE_CYCLES)}
             entry["phases"] = phases
             entry["elapsed_ns"] = max((p["last_ns"] for p in phases.values()), default=0)
             operations.append(entry)
