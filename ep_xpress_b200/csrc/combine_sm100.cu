@@ -189,36 +189,35 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 
 // ---- reduce phase, bulk-copy variant -------------------------------------------------------
 // (rows 16-byte aligned, at most kPeerBatch contributors per token)
-// One producer warp and sixteen consumer warps share a ring of shared-memory stages. The
-// producer claims (token, row segment) items, and lane j issues ONE bulk copy (TMA) of
-// contributor j's segment - up to 8 KiB each - into the stage; all copies of an item complete
-// on the stage's "full" mbarrier. Consumers add the staged chunks in ascending rank order,
-// store the result and release the stage through its "empty" mbarrier. Data in flight lives
-// in shared memory (up to two items, ~100 KiB per SM), so the phase runs at memory speed with
-// few registers, and the item look-ups (claim, mask, row indices) are prefetched two items
-// ahead by the producer instead of sitting on every warp's critical path.
+// The CTA is four independent pipelines. Each has one producer warp, four consumer warps and
+// a private ring of shared-memory stages. The producer walks its share of the CTA's
+// (token, row segment) items; lane j issues ONE bulk copy (TMA) of contributor j's segment
+// into the stage and all copies of an item complete on the stage's "full" mbarrier. The
+// consumers add the staged chunks in ascending rank order, store the result and release the
+// stage through its "empty" mbarrier. Data in flight lives in shared memory, so the phase
+// needs few registers; a producer's per-item bookkeeping is a serial instruction stream of
+// about a microsecond, which is why there are four of them. Route look-ups (mask, row
+// indices) are loaded for 32 items at once and one batch ahead.
 constexpr int kConsumerWarps = kThreads / 32;
-constexpr int kBulkThreads = kThreads + 32;       // + the producer warp
 constexpr int kConsumerGroups = 4;
-constexpr int kMaxStages = 12;
 constexpr int kGroupWarps = kConsumerWarps / kConsumerGroups;
 constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kBulkThreads = kThreads + 32 * kConsumerGroups;   // + one producer warp per group
+constexpr int kMaxGroupStages = 3;
 constexpr int kChunksPerThread = 4;
 constexpr int kSegMaxBytes = 8192;                // largest row segment of one item
-constexpr size_t kBulkSmemBytes = 3 * kPeerBatch * kSegMaxBytes;   // 192 KiB ring
-// A stage holds one item: `fan` contributor slots of kSegMaxBytes. Narrow fan-outs get more,
-// smaller stages out of the same ring, so the bytes in flight stay high when few ranks
-// contribute to a token.
-// The stage count is a multiple of the consumer-group count, so a group always meets a
-// stage in consecutive rounds and the mbarrier phase parity it waits for is unambiguous.
+constexpr size_t kBulkSmemBytes = 192 * 1024;
+constexpr size_t kGroupSmemBytes = kBulkSmemBytes / kConsumerGroups;
+
+// Segment size: as large as possible while every group still gets two stages of `fan`
+// contributor slots (one being filled while the other is reduced).
 __device__ __forceinline__ int ring_segment_bytes(int fan) {
-  const int fit = static_cast<int>(kBulkSmemBytes / (static_cast<size_t>(kConsumerGroups) * fan)) / 512 * 512;
+  const int fit = static_cast<int>(kGroupSmemBytes / (2 * static_cast<size_t>(fan))) / 512 * 512;
   return fit < kSegMaxBytes ? fit : kSegMaxBytes;
 }
 __device__ __forceinline__ int ring_stages(int fan, int segment_bytes) {
-  const int fit = static_cast<int>(kBulkSmemBytes / (static_cast<size_t>(fan) * segment_bytes)) /
-                  kConsumerGroups * kConsumerGroups;
-  return fit < kMaxStages ? fit : kMaxStages;
+  const int fit = static_cast<int>(kGroupSmemBytes / (static_cast<size_t>(fan) * segment_bytes));
+  return fit < kMaxGroupStages ? fit : kMaxGroupStages;
 }
 
 struct StageItem {
@@ -235,15 +234,12 @@ __device__ __forceinline__ void mbarrier_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar)) : "memory");
 }
 
-
-
 struct BulkReduceArgs {
   const unsigned long long* mask_arr;
   const int* send_rows;
   const char* partial;
   const char* staging;
   char* out;
-  unsigned* work_counter;
   long long row_bytes;
   int tokens;
   int fan;
@@ -254,51 +250,55 @@ struct BulkReduceArgs {
   unsigned long long* profile;
 };
 
-// Returns false when a bounded wait gave up.
-__device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem, unsigned long long* full,
-                                            unsigned long long* empty, StageItem* items_smem) {
+// Barriers and item slots are indexed [group][stage]. Returns false when a bounded wait gave up.
+__device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem, unsigned long long* full_all,
+                                            unsigned long long* empty_all, StageItem* items_all) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool producer = warp >= kConsumerWarps;
+  const int group = producer ? warp - kConsumerWarps : warp / kGroupWarps;
   const int seg_max = ring_segment_bytes(a.fan);
   const int rsegs = static_cast<int>((a.row_bytes + seg_max - 1) / seg_max);
-  const long long rseg_bytes = align_up((a.row_bytes + rsegs - 1) / rsegs, 512);
-  const long long items = static_cast<long long>(a.tokens) * rsegs;
+  const int rseg_bytes = static_cast<int>(align_up((a.row_bytes + rsegs - 1) / rsegs, 512));
+  const int items = a.tokens * rsegs;
   const int stages = ring_stages(a.fan, seg_max);
   const size_t stage_bytes = static_cast<size_t>(a.fan) * seg_max;
+  char* const ring = smem + static_cast<size_t>(group) * kGroupSmemBytes;
+  unsigned long long* const full = full_all + group * kMaxGroupStages;
+  unsigned long long* const empty = empty_all + group * kMaxGroupStages;
+  StageItem* const slots = items_all + group * kMaxGroupStages;
+  // Items of this CTA are a contiguous range (local memory only: a static split is balanced);
+  // the groups take them round-robin.
+  const int lo = static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
+  const int hi = static_cast<int>(static_cast<long long>(items) * (blockIdx.x + 1) / gridDim.x);
+  const int mine = hi - lo > group ? (hi - lo - group + kConsumerGroups - 1) / kConsumerGroups : 0;
   long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
   bool ok = true;
-  if (warp == kConsumerWarps) {
-    // ---------------- producer ----------------
-    // Items of this CTA are a contiguous range (the phase reads local memory only, so a
-    // static split is balanced). Route look-ups are done for 32 items at once - lane L loads
-    // the mask of item L, lane 8q + j the row index of contributor j of item 4r + q - and
-    // the next batch is requested before the current one is issued, so their latency is
-    // paid once per batch instead of once per item.
-    const long long lo = items * blockIdx.x / gridDim.x, hi = items * (blockIdx.x + 1) / gridDim.x;
-    auto load_batch = [&](long long base, unsigned long long& mask, int (&rows)[8]) {
-      const long long mine = base + lane;
-      mask = mine < hi ? a.mask_arr[mine / rsegs] : 0ull;
+  if (producer) {
+    auto item_of = [&](int k) { return lo + group + k * kConsumerGroups; };
+    // Lane L loads the mask of item L of the batch, lane 8q + j the row of contributor j of
+    // item 4r + q.
+    auto load_batch = [&](int base, unsigned long long& mask, int (&rows)[8]) {
+      mask = base + lane < mine ? a.mask_arr[item_of(base + lane) / rsegs] : 0ull;
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
-        const long long item = base + 4 * r + (lane >> 3);
-        const int j = lane & 7;
-        rows[r] = (item < hi && j < a.fan) ? a.send_rows[(item / rsegs) * a.fan + j] : -1;
+        const int k = base + 4 * r + (lane >> 3), j = lane & 7;
+        rows[r] = (k < mine && j < a.fan) ? a.send_rows[static_cast<long long>(item_of(k) / rsegs) * a.fan + j] : -1;
       }
     };
     unsigned long long mask_now = 0, mask_next = 0;
     int rows_now[8], rows_next[8];
-    load_batch(lo, mask_now, rows_now);
+    load_batch(0, mask_now, rows_now);
     unsigned use = 0;
-    for (long long base = lo; base < hi && ok; base += 32) {
-      if (base + 32 < hi) load_batch(base + 32, mask_next, rows_next);
+    for (int base = 0; base < mine && ok; base += 32) {
+      if (base + 32 < mine) load_batch(base + 32, mask_next, rows_next);
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int i = 4 * r + q;
-          const long long item = base + i;
           const unsigned long long m = __shfl_sync(0xffffffffu, mask_now, i);
           const int row = __shfl_sync(0xffffffffu, rows_now[r], q * 8 + (lane & 7));
-          if (item >= hi || !ok) continue;                 // warp-uniform
+          if (base + i >= mine || !ok) continue;                 // warp-uniform
           const int stage = use % stages;
           const unsigned parity = ((use / stages) & 1u) ^ 1u;
           ++use;
@@ -308,10 +308,11 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             continue;
           }
           waited += clock64() - t0;
-          const int t = static_cast<int>(item / rsegs), seg = static_cast<int>(item % rsegs);
+          const int item = item_of(base + i);
+          const int t = item / rsegs, seg = item - t * rsegs;
           const int n = __popcll(m);
-          const long long b0 = seg * rseg_bytes;
-          const int bytes = static_cast<int>(min(a.row_bytes, b0 + rseg_bytes) - b0);
+          const int b0 = seg * rseg_bytes;
+          const int bytes = static_cast<int>(min(a.row_bytes, static_cast<long long>(b0) + rseg_bytes)) - b0;
           const char* src = nullptr;
           bool is_self = false;
           if (lane < n) {
@@ -324,7 +325,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
           const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
           if (lane == 0) {
-            StageItem& slot = items_smem[stage];
+            StageItem& slot = slots[stage];
             slot.out_offset = static_cast<long long>(t) * a.row_bytes + b0;
             slot.bytes = bytes;
             slot.contributors = n;
@@ -335,7 +336,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           }
           __syncwarp();
           if (src != nullptr)
-            bulk_load_to_smem(smem + static_cast<size_t>(stage) * stage_bytes + lane * seg_max, src + b0,
+            bulk_load_to_smem(ring + static_cast<size_t>(stage) * stage_bytes + lane * seg_max, src + b0,
                               static_cast<unsigned>(bytes), full + stage);
         }
       }
@@ -343,12 +344,12 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
 #pragma unroll
       for (int r = 0; r < 8; ++r) rows_now[r] = rows_next[r];
     }
-    for (int marker = 0; marker < kConsumerGroups && ok; ++marker, ++use) {   // one end marker per group
+    if (ok) {                                              // end marker
       const int stage = use % stages;
       const unsigned parity = ((use / stages) & 1u) ^ 1u;
       if (__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
         if (lane == 0) {
-          items_smem[stage].end = 1;
+          slots[stage].end = 1;
           mbarrier_arrive(full + stage);
         }
       } else {
@@ -356,25 +357,18 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       }
     }
   } else {
-    // ---------------- consumers ----------------
-    // Four groups of four warps; item number u belongs to group u % 4, so four items are
-    // reduced at once and every thread owns several independent 16-byte chunks of its item
-    // (instruction-level parallelism instead of one dependent chain per item).
-    const int group = warp / kGroupWarps, gtid = tid % kGroupThreads;
-    for (unsigned use = group;; use += kConsumerGroups) {
+    // ---------------- consumers: four warps per group, several chunks per thread -------------
+    const int gtid = tid % kGroupThreads;
+    for (unsigned use = 0;; ++use) {
       const int stage = use % stages;
       const unsigned parity = (use / stages) & 1u;
       const long long t0 = clock64();
       if (!mbarrier_wait_bounded(full + stage, parity, a.timeout_ns)) { ok = false; break; }
       const long long t1 = clock64();
       waited += t1 - t0;
-      const StageItem item = items_smem[stage];
-      if (item.end) {                       // release the stage too: later end markers may reuse it
-        __syncwarp();
-        if (lane == 0) mbarrier_arrive(empty + stage);
-        break;
-      }
-      const char* base = smem + static_cast<size_t>(stage) * stage_bytes;
+      const StageItem item = slots[stage];
+      if (item.end) break;
+      const char* base = ring + static_cast<size_t>(stage) * stage_bytes;
       const int chunks = item.bytes / 16;
       for (int first = gtid; first < chunks; first += kGroupThreads * kChunksPerThread) {
         float acc[kChunksPerThread][8];
@@ -523,9 +517,9 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
 
   // ---- D. rank-order reduce from local memory -----------------------------------------------
   if (kBulk) {
-    __shared__ unsigned long long s_full[kMaxStages], s_empty[kMaxStages];
-    __shared__ StageItem s_items[kMaxStages];
-    if (tid < kMaxStages) {
+    __shared__ unsigned long long s_full[kConsumerGroups * kMaxGroupStages], s_empty[kConsumerGroups * kMaxGroupStages];
+    __shared__ StageItem s_items[kConsumerGroups * kMaxGroupStages];
+    if (tid < kConsumerGroups * kMaxGroupStages) {
       mbarrier_init(s_full + tid, 1);
       mbarrier_init(s_empty + tid, kGroupWarps);
     }
@@ -534,7 +528,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     __syncthreads();
     BulkReduceArgs a;
     a.mask_arr = mask_arr; a.send_rows = send_rows; a.partial = partial; a.staging = staging;
-    a.out = reinterpret_cast<char*>(op.out); a.work_counter = &hdr->cwork_reduce; a.row_bytes = row_bytes;
+    a.out = reinterpret_cast<char*>(op.out); a.row_bytes = row_bytes;
     a.tokens = T; a.fan = fan; a.self = self; a.partial_rows = op.partial_rows; a.single_round = single_round; a.timeout_ns = c.timeout_ns; a.profile = op.profile;
     if (!bulk_reduce(a, dynamic_smem, s_full, s_empty, s_items)) report_error(c, kTimeout, kPhaseCombine, 4, 0);
   } else {
