@@ -21,7 +21,8 @@
 namespace py = pybind11;
 
 namespace epx {
-void bind_moe(py::module_& m);   // moe_bindings.cpp
+void bind_moe(py::module_& m);        // moe_bindings.cpp
+void bind_host_ring(py::module_& m);  // host_ring.cpp
 namespace {
 
 void cuda_check(cudaError_t err, const char* what) {
@@ -416,4 +417,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("poke_u64", &Engine::poke_u64)
       .def("peek_u64", &Engine::peek_u64);
   epx::bind_moe(m);
+  epx::bind_host_ring(m);
 }

@@ -23,7 +23,7 @@ from pathlib import Path
 _PACKAGE = Path(__file__).resolve().parent
 _CSRC = _PACKAGE / "csrc"
 _NAME = "_epx_native"
-_SOURCES = ("engine.cpp", "heap.cpp", "moe_bindings.cpp", "dispatch_sm100.cu", "combine_sm100.cu", "expert_ops.cu",
+_SOURCES = ("engine.cpp", "heap.cpp", "moe_bindings.cpp", "host_ring.cpp", "dispatch_sm100.cu", "combine_sm100.cu", "expert_ops.cu",
             "moe_gemm_sm100.cu", "moe_noalloc.cu")
 _HEADERS = ("epx_layout.h", "epx_device.cuh", "epx_launch.h", "heap.h", "moe_gemm.h", "moe_noalloc.h")
 _ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
