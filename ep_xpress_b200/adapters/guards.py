@@ -1,0 +1,59 @@
+"""Deployment guards and launch-width policy (no framework import, no CUDA).
+
+Same rules as the reference adapter (ep_xpress/adapters/sglang_config.py:6-116): the EP
+group is the attention-DP group is the TP group, MoE tensor/data parallelism and pipeline
+parallelism are off, experts sit in equal contiguous blocks, the receive capacity comes
+from scheduler-known token counts, and the launch width follows the batch size.
+"""
+
+from __future__ import annotations
+
+
+def validate_server_args(*, tp_size, dp_size, ep_size, pp_size=1, moe_tp_size=1, moe_dp_size=1,
+                         enable_dp_attention=True):
+    """Raise ValueError unless the parallel layout is one this library serves."""
+    if pp_size != 1:
+        raise ValueError("pipeline parallelism is not supported with the EP dispatcher (pp_size must be 1)")
+    if not enable_dp_attention:
+        raise ValueError("attention data parallelism is required: every rank owns its own tokens")
+    if not (tp_size == dp_size == ep_size):
+        raise ValueError("attention DP size, TP size and EP size must be equal")
+    if moe_tp_size != 1 or moe_dp_size != 1:
+        raise ValueError("MoE tensor and data parallelism must be 1: experts are sharded by EP only")
+    if not 1 <= ep_size <= 63:
+        raise ValueError("the EP group must have between 1 and 63 ranks")
+
+
+def validate_runner_config(*, reduce_results, apply_router_weight_on_input=False, activation="silu"):
+    """The expert runner must hand back already-weighted, not-yet-reduced partial rows."""
+    if reduce_results:
+        raise ValueError("reduce_results must be False: combine performs the cross-rank reduction")
+    if apply_router_weight_on_input:
+        raise ValueError("router weights are applied once, on the expert outputs")
+    if activation != "silu":
+        raise ValueError("the grouped expert runner implements SwiGLU (silu) only")
+
+
+def contiguous_expert_map(num_experts, ep_size):
+    if num_experts <= 0 or ep_size <= 0 or num_experts % ep_size:
+        raise ValueError("experts must divide evenly into contiguous blocks per rank")
+    per_rank = num_experts // ep_size
+    return [expert // per_rank for expert in range(num_experts)]
+
+
+def receive_capacity_from_scheduler(token_counts, max_tokens_per_rank):
+    """CPU-known bound of received rows: the sum of every rank's scheduled tokens."""
+    counts = [int(c) for c in token_counts]
+    if not counts or any(c < 0 or c > max_tokens_per_rank for c in counts):
+        raise ValueError("scheduler token counts must be within [0, max_tokens_per_rank] for every rank")
+    return sum(counts)
+
+
+def select_active_channels(local_tokens, effective_channels, *, is_decode, tokens_per_channel_decode=8):
+    """Prefill: one channel per token up to all channels; decode: one per 8 tokens."""
+    if effective_channels < 1:
+        raise ValueError("effective_channels must be positive")
+    if local_tokens <= 0:
+        return 1
+    wanted = -(-local_tokens // tokens_per_channel_decode) if is_decode else local_tokens
+    return max(1, min(effective_channels, wanted))
