@@ -62,6 +62,8 @@ def parse_args():
     parser.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     parser.add_argument("--routing", choices=("uniform", "zipf"), default="uniform")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--graph", choices=("auto", "on", "off"), default="auto",
+                        help="replay the layer from CUDA graphs (auto: on for the decode shape)")
     parser.add_argument("--plain-launch", action="store_true", help="ordinary instead of cooperative launches")
     parser.add_argument("--profile-out", default=None,
                         help="after timing, run 4 profiled steps and write per-CTA phase stamps to PATH.rankR.json")
@@ -118,8 +120,57 @@ class OursArm:
         self.context = Context(self.comm, workloads.contiguous_expert_map(shape["experts"], world), cfg)
         self.layer = IdentityMoELayer(self.context)
 
+    def enable_graph(self, example):
+        """Capture dispatch, expert and combine as three CUDA graphs on the layer's workspace."""
+        import torch
+        from ep_xpress_b200.ops import scale_rows
+        ep, ws = self.context, self.layer.workspace
+        ep.enable_cuda_graph()
+        self.static = [torch.empty_like(t) for t in example]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for dst, src in zip(self.static, example):
+                dst.copy_(src)
+            self.layer.forward(*self.static, stream=side)            # warm the workspace eagerly
+        side.synchronize()
+        ep.prepare_graph_capture()
+        state = {}
+
+        def dispatch():
+            state["batch"] = ep.dispatch_on_stream(*self.static, stream=side, workspace=ws)
+
+        def expert():
+            state["partial"] = scale_rows(ep, state["batch"], stream=side)
+
+        def combine():
+            state["out"] = ep.combine_on_stream(state["partial"], state["batch"].handle, stream=side)
+
+        self.graphs = []
+        for phase in (dispatch, expert, combine):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                phase()
+            self.graphs.append(graph)
+        self.graph_state = state
+        torch.cuda.current_stream().wait_stream(side)
+
     def step(self, x, ids, weights, timing=None):
-        return self.layer.forward(x, ids, weights, timing=timing)
+        if getattr(self, "graphs", None) is None:
+            return self.layer.forward(x, ids, weights, timing=timing)
+        import torch
+        stream = torch.cuda.current_stream()
+        for dst, src in zip(self.static, (x, ids, weights)):
+            dst.copy_(src, non_blocking=True)
+        self.context.prepare_graph_replay(stream)
+        marks = [mark(stream)] if timing is not None else None
+        for graph in self.graphs:
+            graph.replay()
+            if marks is not None:
+                marks.append(mark(stream))
+        if marks is not None:
+            timing.append(marks)
+        return self.graph_state["out"], self.graph_state["batch"].valid_count
 
     def launches_per_step(self):
         return 3
@@ -210,6 +261,9 @@ def run(args):
     host = make_inputs(shape, tokens, world, rank, args.routing, sets)
     device = [tuple(t.cuda(non_blocking=True) for t in batch) for batch in host]
     arm = (OursArm if args.impl == "ours" else ReferenceArm)(shape, tokens, world, rank, local, args.plain_launch)
+    use_graph = args.impl == "ours" and (args.graph == "on" or (args.graph == "auto" and args.config == "decode"))
+    if use_graph:
+        arm.enable_graph(device[0])
     stream = torch.cuda.current_stream()
 
     # ---- device-timed: inputs resident, rotated ---------------------------------
@@ -298,6 +352,7 @@ def run(args):
         "config": {"model": shape["model"], "global_batch": world * tokens, "seq_len": tokens,
                    "tokens_per_rank": tokens, "hidden": shape["hidden"], "experts": shape["experts"],
                    "topk": shape["topk"], "routing": args.routing, "parallelism": f"ep{world}",
+                   "cuda_graph": bool(use_graph),
                    "l2": "inputs rotate over 4 batches; a step touches far more than the 126 MB L2"},
         "dispatch_us_p50": statistics.median(dispatch_us), "combine_us_p50": statistics.median(combine_us),
         "dispatch_combine_us_p50": statistics.median(both_us),
