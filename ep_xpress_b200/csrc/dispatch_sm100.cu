@@ -100,7 +100,11 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   }
 
   // ---- 1. route ------------------------------------------------------------
-  for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+  // A batch of at most one tile (decode) is routed by EVERY CTA redundantly: all CTAs write
+  // identical values and each reads back only what its own threads wrote before a CTA
+  // barrier, so the rank-wide barrier and its round trip through L2 are skipped.
+  const bool solo = ntiles <= 1;
+  for (int tile = solo ? 0 : blockIdx.x; tile < ntiles; tile += solo ? 1 : gridDim.x) {
     const int t = tile * kRouteTile + tid;
     unsigned long long m = 0;
     if (t < T) {
@@ -187,7 +191,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   }
 
   profile_stamp(op.profile, 1);
-  if (!rank_barrier(c, &hdr->bar_count, gridDim.x, kPhaseDispatch)) return;
+  if (!solo && !rank_barrier(c, &hdr->bar_count, gridDim.x, kPhaseDispatch)) return;
   profile_stamp(op.profile, 2);
 
   // ---- 2. publish my count row ----------------------------------------------

@@ -192,7 +192,45 @@ def run_errors(ep, rank, world, args):
     del batch
 
 
-CASES = {"replay": run_replay, "reverse": run_reverse_handles, "graph": run_graph, "errors": run_errors}
+def run_profile(ep, rank, world, args):
+    """Bounded operation profile: per-CTA phase stamps, dropped operations, single readback."""
+    hidden, topk, tokens = args.hidden, 4, args.tokens
+    stream = torch.cuda.current_stream()
+    try:
+        ep.read_combine_profile()
+    except RuntimeError as error:
+        assert "no completed" in str(error)
+    ep.start_combine_profile(max_operations=4)
+    try:
+        ep.start_combine_profile()
+    except RuntimeError as error:
+        assert "stop the current" in str(error)
+    ep.set_combine_profile_label("warm")
+    for iteration in range(3):                       # 6 operations, room for 4
+        xs, ids, ws = group_inputs("uniform", world, tokens, hidden, topk, iteration)
+        batch = ep.dispatch_on_stream(xs[rank].cuda(), ids[rank].cuda(), ws[rank].cuda(), stream=stream)
+        ep.combine_on_stream(scale_rows(ep, batch), batch.handle, stream=stream)
+    report = ep.stop_combine_profile()
+    assert report is ep.read_combine_profile()
+    assert len(report["operations"]) == 4 and report["dropped_operations"] == 2
+    kinds = [op["kind"] for op in report["operations"]]
+    assert kinds == ["dispatch", "combine", "dispatch", "combine"]
+    for op in report["operations"]:
+        assert op["label"] == "warm" and op["elapsed_ns"] > 0 and op["ctas"] >= 1
+        names = list(op["phases"])
+        assert names[0] == "start" and op["phases"]["start"]["first_ns"] == 0
+        lasts = [op["phases"][n]["last_ns"] for n in names]
+        assert lasts == sorted(lasts), (op["kind"], lasts)      # phases are reached in order
+    stats = ep.stats()
+    assert stats["status"] == 0 and stats["dispatch_epoch"] == 3 and stats["combine_epoch"] == 3
+    try:
+        ep.start_combine_profile(max_operations=1 << 30)
+    except ValueError as error:
+        assert "64 MiB budget" in str(error)
+    ep.check()
+
+
+CASES = {"profile": run_profile, "replay": run_replay, "reverse": run_reverse_handles, "graph": run_graph, "errors": run_errors}
 
 
 def main():

@@ -1,0 +1,57 @@
+"""Borrowed-communicator handle with a mocked NCCL library (no GPU, no NCCL)."""
+
+import ctypes
+from unittest import mock
+
+import pytest
+
+from ep_xpress_b200 import Config, Context, NCCLCommHandle
+from ep_xpress_b200 import comm as comm_module
+
+
+class FakeApi:
+    def __init__(self, path):
+        self.path = path
+
+    def integer(self, name, pointer):
+        return {"ncclCommUserRank": 1, "ncclCommCount": 4, "ncclCommCuDevice": 0}[name]
+
+
+def test_borrow_validates_pointer_and_owner():
+    with mock.patch.object(comm_module, "_NcclApi", FakeApi):
+        with pytest.raises(ValueError, match="non-null"):
+            NCCLCommHandle.borrow(0, owner=object(), library_path="x")
+        with pytest.raises(ValueError, match="non-null"):
+            NCCLCommHandle.borrow(True, owner=object(), library_path="x")
+        with pytest.raises(ValueError, match="lifetime owner"):
+            NCCLCommHandle.borrow(1234, owner=None, library_path="x")
+        owner = object()
+        handle = NCCLCommHandle.borrow(ctypes.c_void_p(1234), owner=owner, library_path="lib.so")
+        assert (handle.rank, handle.world_size, handle.get()) == (1, 4, 1234)
+        assert handle._owner is owner and str(handle.device) == "cuda:0"
+
+
+def test_handles_are_not_constructed_directly_and_contexts_reject_raw_pointers():
+    with pytest.raises(TypeError, match="borrow"):
+        NCCLCommHandle()
+    cfg = Config(hidden_size=64, topk=2, max_tokens_per_rank=8)
+    with pytest.raises(TypeError, match="NCCLCommHandle"):
+        Context(42, [0, 1], cfg)
+    with pytest.raises(TypeError):
+        Context(42, [0, 1], cfg, bootstrap_group=None)        # removed keyword of older releases
+    with pytest.raises(TypeError, match="Config"):
+        Context(42, [0, 1], {"hidden_size": 64})
+
+
+def test_get_handle_requires_an_initialised_nccl_group():
+    with pytest.raises(RuntimeError, match="initialize the NCCL process group"):
+        comm_module.get_nccl_comm_handle(None)
+
+
+def test_invalid_rank_from_the_library_is_rejected():
+    class Broken(FakeApi):
+        def integer(self, name, pointer):
+            return {"ncclCommUserRank": 5, "ncclCommCount": 4, "ncclCommCuDevice": 0}[name]
+    with mock.patch.object(comm_module, "_NcclApi", Broken):
+        with pytest.raises(ValueError, match="invalid NCCL communicator"):
+            NCCLCommHandle.borrow(99, owner=object(), library_path="x")

@@ -10,8 +10,6 @@ import pytest
 
 from conftest import gpu_count
 
-pytestmark = [pytest.mark.gpu, pytest.mark.multigpu,
-              pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")]
 
 WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "nvlink_worker.py")
 
@@ -34,18 +32,37 @@ def ranks_available():
     return [n for n in (2, 4, 8) if n <= gpu_count()]
 
 
-@pytest.mark.parametrize("ranks", ranks_available())
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+@pytest.mark.parametrize("ranks", ranks_available() or [2])
 def test_replay_cases(ranks):
     launch("replay", ranks)
 
 
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
 def test_reverse_order_handles():
     launch("reverse", min(gpu_count(), 4))
 
 
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
 def test_cuda_graph_replay_with_changing_routes():
     launch("graph", min(gpu_count(), 4))
 
 
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
 def test_undersized_capacity_poisons_the_group_without_hanging():
     launch("errors", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_operation_profile():
+    launch("profile", 2)
