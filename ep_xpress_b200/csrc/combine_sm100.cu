@@ -432,7 +432,6 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   char* const slot = my_heap + op.slot_off;
   const unsigned long long* const mask_arr = reinterpret_cast<const unsigned long long*>(slot + sl.mask);
   const int* const send_rows = reinterpret_cast<const int*>(slot + sl.send_rows);
-  const long long* const inverse = reinterpret_cast<const long long*>(slot + sl.inverse);
   const int* const ret = reinterpret_cast<const int*>(slot + sl.ret);
   const int* const misc = reinterpret_cast<const int*>(slot + sl.misc);
   const char* const partial = reinterpret_cast<const char*>(op.partial);
@@ -459,17 +458,44 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   __syncthreads();
 
   // ---- A. push my rows to the ranks that own the tokens ---------------------------
+  // Received rows are grouped by source rank. Pushing them in storage order would make every
+  // rank write to rank 0 first, then rank 1, ... (incast: one ingress port saturated, the
+  // rest idle). Items therefore interleave the peers in blocks of kPushBlock rows, starting
+  // with the rank after this one, so that at any moment each rank spreads its stores over
+  // all peers and each peer receives from all ranks.
   {
-    const long long items = static_cast<long long>(valid) * segs;
+    constexpr int kPushBlock = 8;
+    __shared__ int s_rows_from[64], s_first_row[64];
+    __shared__ int s_most;
+    if (tid == 0) {
+      int at = 0, most = 0;
+      for (int r = 0; r < W; ++r) {
+        const int count = reinterpret_cast<const int*>(slot + sl.recv_cnt)[r];
+        s_first_row[r] = at;
+        s_rows_from[r] = count;
+        at += count;
+        if (r != self && count > most) most = count;
+      }
+      s_most = most;
+    }
+    __syncthreads();
+    const int peers = W - 1;
+    const long long blocks = (s_most + kPushBlock - 1) / kPushBlock;
+    const long long items = peers > 0 ? blocks * peers * kPushBlock * segs : 0;
     unsigned next_claim = lane == 0 ? atomicAdd(&hdr->cwork_push, 1u) : 0u;
     while (true) {
       const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
       if (item >= items) break;
       if (lane == 0) next_claim = atomicAdd(&hdr->cwork_push, 1u);   // in flight while this item is copied
-      const long long row = item / segs;
       const int seg = static_cast<int>(item % segs);
-      const int source = static_cast<int>(inverse[row * 2]);
-      if (source == self || source < 0 || source >= W) continue;
+      const long long q = item / segs;
+      const int in_block = static_cast<int>(q % kPushBlock);
+      const long long q2 = q / kPushBlock;
+      const int source = (self + 1 + static_cast<int>(q2 % peers)) % W;
+      const long long from_source = (q2 / peers) * kPushBlock + in_block;
+      if (from_source >= s_rows_from[source]) continue;
+      const long long row = s_first_row[source] + from_source;
+      if (row >= valid) continue;
       const long long back = ret[row];
       const char* src = partial + row * row_bytes;
       char* dst = s_stage[source] + back * row_bytes;
