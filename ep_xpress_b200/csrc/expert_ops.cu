@@ -28,12 +28,27 @@ __global__ void __launch_bounds__(256) scale_rows_kernel(const unsigned short* _
                    (reinterpret_cast<size_t>(partial) % 16 == 0);
   for (long long row = static_cast<long long>(blockIdx.x) * warps_per_cta + (threadIdx.x >> 5); row < valid;
        row += static_cast<long long>(gridDim.x) * warps_per_cta) {
+    // Lanes fetch the slots in parallel (one memory round trip), then the scale is
+    // accumulated in slot order from registers, so the arithmetic stays sequential.
     float scale = 0.f;
-    for (int k = 0; k < topk; ++k) {
-      const long long id = local_ids[row * topk + k];
-      if (id < 0) continue;
-      const float f = factors != nullptr ? factors[id < num_factors ? id : num_factors - 1] : 1.f;
-      scale = __fadd_rn(scale, __fmul_rn(weights[row * topk + k], f));
+    for (int k0 = 0; k0 < topk; k0 += 32) {
+      const int k = k0 + lane;
+      float term = 0.f;
+      bool local = false;
+      if (k < topk) {
+        const long long id = local_ids[row * topk + k];
+        if (id >= 0) {
+          const float f = factors != nullptr ? factors[id < num_factors ? id : num_factors - 1] : 1.f;
+          term = __fmul_rn(weights[row * topk + k], f);
+          local = true;
+        }
+      }
+      const unsigned votes = __ballot_sync(0xffffffffu, local);
+      const int span = min(32, topk - k0);
+      for (int j = 0; j < span; ++j) {
+        const float t = __shfl_sync(0xffffffffu, term, j);
+        if ((votes >> j) & 1u) scale = __fadd_rn(scale, t);
+      }
     }
     const unsigned short* src = hidden + row * hidden_size;
     unsigned short* dst = partial + row * hidden_size;
