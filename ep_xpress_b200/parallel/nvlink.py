@@ -391,6 +391,8 @@ class NVLinkContext(Context):
                 ctas = self._core.pick_ctas(x.shape[0], budget)
                 profile = None if self._profile is None else self._profile.slice_for(
                     "dispatch", self._counter, tag, x.shape[0], capacity, ctas)
+                if profile is None and capturing:
+                    profile = self._decode_slice("dispatch", ctas)
                 with torch.cuda.stream(execution), torch.no_grad():
                     if not same_stream:
                         for tensor in (x, ids, weights):
@@ -411,13 +413,16 @@ class NVLinkContext(Context):
                                   handle, views.count)
             if same_stream:
                 return batch
-            return self._finish(batch, workspace)
+            return self._finish(batch, workspace, metrics={"ctas": ctas, "active_channels": channels,
+                                                           "recv_capacity": capacity})
 
-    def _finish(self, value, workspace=None, tensors=()):
+    def _finish(self, value, workspace=None, tensors=(), metrics=None):
         completed = torch.cuda.Event()
         completed.record(self._work_stream)
         self._pending += 1
-        return Pending(self, value, completed, workspace, tensors)
+        ticket = Pending(self, value, completed, workspace, tensors)
+        ticket._stats = dict(metrics or {})
+        return ticket
 
     def _ticket_waited(self, ticket, consumer):
         with self._lock:
@@ -484,6 +489,8 @@ class NVLinkContext(Context):
                     profile = None if self._profile is None else self._profile.slice_for(
                         "combine", handle.operation, tag, handle.local_token_count, handle.received_count,
                         route.ctas)
+                    if profile is None and capturing:
+                        profile = self._decode_slice("combine", route.ctas)
                     self._core.combine(route.slot, [source], [output], identity=identity, ctas=route.ctas,
                                        stream=execution, profile=profile)
             except BaseException as error:
@@ -496,7 +503,8 @@ class NVLinkContext(Context):
                 if workspace is not None:
                     workspace._combined(execution, capturing=capturing)
                 return output
-            return self._finish(output, workspace, tensors=() if workspace is not None else (output,))
+            return self._finish(output, workspace, tensors=() if workspace is not None else (output,),
+                                metrics={"ctas": route.ctas, "active_channels": route.active_channels})
 
     # ------------------------------------------------------------------ profiling
     def start_combine_profile(self, max_operations=1024):
@@ -530,6 +538,58 @@ class NVLinkContext(Context):
         if report is None:
             raise RuntimeError("no completed profile is available")
         return report
+
+    # ---- decode profile: fixed storage that captured operations keep writing into -----------
+    def prepare_decode_profile(self, max_samples_per_channel=1, *, stage="combine"):
+        """Install fixed counters for CAPTURED operations of ``stage`` ("dispatch" or "combine").
+
+        Call before graph capture (same rule as the reference, ep_xpress/host_sm.py:515-545).
+        Operations captured afterwards stamp their per-CTA phase times into this storage at
+        every replay; it always holds the most recent replay (one sample per CTA, so
+        ``max_samples_per_channel`` above 1 is accepted but not needed).
+        """
+        with self._lock, torch.cuda.device(self.device):
+            self._check_usable()
+            if stage not in ("dispatch", "combine"):
+                raise ValueError("stage must be dispatch or combine")
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("prepare_decode_profile must be called before graph capture")
+            stamps = self._core.native.PROFILE_STAMPS
+            self._decode_profile = {"stage": stage, "ctas": 0, "enabled": True,
+                                    "buffer": torch.zeros((self._core.max_ctas, stamps), dtype=torch.int64,
+                                                          device=self.device)}
+
+    def _decode_slice(self, stage, ctas):
+        state = getattr(self, "_decode_profile", None)
+        if state is None or state["stage"] != stage:
+            return None
+        state["ctas"] = ctas
+        return state["buffer"]
+
+    def start_decode_profile(self):
+        if getattr(self, "_decode_profile", None) is None:
+            raise RuntimeError("prepare_decode_profile is required before the first capture")
+        with torch.cuda.device(self.device):
+            self._decode_profile["buffer"].zero_()
+
+    def stop_decode_profile(self):
+        """Phase stamps (ns, relative to the first CTA's start) of the most recent replay."""
+        from ..utils.profile import COMBINE_PHASES, DISPATCH_PHASES
+        state = getattr(self, "_decode_profile", None)
+        if state is None:
+            raise RuntimeError("prepare_decode_profile is required before the first capture")
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            stamps = state["buffer"][:max(state["ctas"], 1)].cpu()
+        names = DISPATCH_PHASES if state["stage"] == "dispatch" else COMBINE_PHASES
+        started = stamps[:, 0][stamps[:, 0] > 0]
+        begin = int(started.min()) if started.numel() else 0
+        phases = {}
+        for column, name in enumerate(names):
+            reached = stamps[:, column][stamps[:, column] > 0]
+            if reached.numel():
+                phases[name] = {"first_ns": int(reached.min()) - begin, "last_ns": int(reached.max()) - begin}
+        return {"schema": 1, "stage": state["stage"], "ctas": state["ctas"], "phases": phases}
 
     # ------------------------------------------------------------------ teardown
     def _release_resources(self, *, keep_own_heap=False):

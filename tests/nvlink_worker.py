@@ -150,6 +150,7 @@ def run_graph(ep, rank, world, args):
         raise AssertionError("capture without prepare_graph_capture must be rejected")
     torch.cuda.synchronize()
     ep.prepare_graph_capture()
+    ep.prepare_decode_profile(stage="combine")      # fixed counters the captured combine keeps writing
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
         out, batch = layer()
@@ -167,6 +168,9 @@ def run_graph(ep, rank, world, args):
             eager = ep.dispatch_async(xs[rank].cuda(), ids[rank].cuda(), ws[rank].cuda()).wait()
             result = ep.combine_async(scale_rows(ep, eager), eager.handle).wait()
             assert torch.equal(bits(result), bits(eager_want[rank]))
+    decode = ep.stop_decode_profile()
+    assert decode["stage"] == "combine" and decode["phases"]["start"]["first_ns"] == 0
+    assert decode["phases"]["reduced"]["last_ns"] > 0
     ep.check()
 
 
