@@ -49,11 +49,13 @@ def _worker(rank, world, port, case, tmp):
             with pytest.raises(RuntimeError, match="failed state"):
                 ep.dispatch_async(xs[rank], ids[rank], ws[rank])
             ep.close()
+            dist.barrier()
             return
         if case == "invalid":
             with pytest.raises(ValueError, match="same expert twice"):
                 ep.dispatch_async(xs[rank], ids[rank], ws[rank]).wait()
             ep.close()
+            dist.barrier()
             return
         plan = routing.plan_routes(ids, ws, emap, world, topk)
         rows = routing.dispatch_oracle(xs, plan)
@@ -75,6 +77,7 @@ def _worker(rank, world, port, case, tmp):
             ep.dispatch_async(xs[rank], ids[rank], ws[rank], recv_capacity=4)
         ep.check()
         ep.close()
+        dist.barrier()                      # nobody tears the group down while a peer still uses it
     finally:
         dist.destroy_process_group()
 
