@@ -75,6 +75,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--samples", type=int, default=10)
     parser.add_argument("--baseline", action="store_true")
+    parser.add_argument("--single-cta", action="store_true", help="128-row tiles on single CTAs instead of CTA pairs")
     parser.add_argument("--report", default=None)
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -95,7 +96,7 @@ def main():
                      gpu_pool_budget_bytes=64 << 30, slots=1)
         ep = Context(get_nccl_comm_handle(dist.group.WORLD), emap, cfg)
         pairs = int(tokens * args.topk * 1.5) + 1024
-        layer = SwiGLUMoELayer(ep, w13, w2, max_local_pairs=pairs)
+        layer = SwiGLUMoELayer(ep, w13, w2, max_local_pairs=pairs, pair_ctas=not args.single_cta)
         batches = []
         for step in range(4):
             ids, w = workloads.uniform_routing(tokens, args.experts, args.topk, seed=step, rank=rank, weights="sigmoid")
@@ -140,7 +141,7 @@ def main():
         torch.cuda.empty_cache()
     if rank == 0:
         report = {"schema": 1, "world_size": world, "hidden": args.hidden, "inter": args.inter, "experts": args.experts,
-                  "topk": args.topk, "peak_tflops": peak, "peak_source": peak_source, "results": results}
+                  "topk": args.topk, "cta_pairs": not args.single_cta, "peak_tflops": peak, "peak_source": peak_source, "results": results}
         text = json.dumps(report, indent=1)
         print(text)
         if args.report:

@@ -24,7 +24,7 @@ void moe_forward(const at::Tensor& hidden, const at::Tensor& local_ids, const at
                  const at::Tensor& valid_count, const at::Tensor& w13, const at::Tensor& w2, at::Tensor& partial,
                  at::Tensor& sorted_row, at::Tensor& sorted_scale, at::Tensor& entry_pos, at::Tensor& tile_expert,
                  at::Tensor& counters, at::Tensor& error_flag, at::Tensor& sorted_x, at::Tensor& act, at::Tensor& y,
-                 int64_t stream_handle) {
+                 int64_t stream_handle, bool pair) {
   expect(hidden, at::kBFloat16, "hidden");
   expect(local_ids, at::kLong, "local_ids");
   expect(weights, at::kFloat, "weights");
@@ -50,30 +50,31 @@ void moe_forward(const at::Tensor& hidden, const at::Tensor& local_ids, const at
   TORCH_CHECK(hidden_size % 256 == 0 && inter % 128 == 0, "hidden must be a multiple of 256 and inter of 128");
   TORCH_CHECK(partial.size(0) >= rows && partial.size(1) == hidden_size, "partial must be [>= rows, hidden]");
   const int64_t sorted_rows = sorted_row.numel();
-  TORCH_CHECK(sorted_rows % kMoeTileRows == 0 && sorted_scale.numel() == sorted_rows, "sorted buffers mismatch");
+  const int tile = pair ? 2 * kMoeTileRows : kMoeTileRows;
+  TORCH_CHECK(sorted_rows % tile == 0 && sorted_scale.numel() == sorted_rows, "sorted buffers mismatch");
   TORCH_CHECK(entry_pos.numel() >= rows * topk && counters.numel() >= 2 && error_flag.numel() >= 1, "small buffers");
-  TORCH_CHECK(tile_expert.numel() >= sorted_rows / kMoeTileRows, "tile_expert is too small");
+  TORCH_CHECK(tile_expert.numel() >= sorted_rows / tile, "tile_expert is too small");
   TORCH_CHECK(sorted_x.numel() >= sorted_rows * hidden_size && y.numel() >= sorted_rows * hidden_size &&
               act.numel() >= sorted_rows * inter, "workspace tensors are too small");
   c10::cuda::CUDAGuard guard(hidden.device());
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_handle);
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  const int max_tiles = static_cast<int>(sorted_rows / kMoeTileRows);
+  const int max_tiles = static_cast<int>(sorted_rows / tile);
   check(launch_moe_align(reinterpret_cast<const long long*>(local_ids.data_ptr<int64_t>()), weights.data_ptr<float>(),
                          valid_count.data_ptr<int>(), static_cast<int>(rows), static_cast<int>(topk),
                          static_cast<int>(experts), sorted_rows, max_tiles, sorted_row.data_ptr<int>(),
                          sorted_scale.data_ptr<float>(), entry_pos.data_ptr<int>(), tile_expert.data_ptr<int>(),
-                         counters.data_ptr<int>(), error_flag.data_ptr<int>(), stream), "align");
+                         counters.data_ptr<int>(), error_flag.data_ptr<int>(), tile, stream), "align");
   check(launch_moe_gather(hidden.data_ptr(), sorted_row.data_ptr<int>(), counters.data_ptr<int>(), sorted_x.data_ptr(),
                           sorted_rows, static_cast<int>(hidden_size), stream), "gather");
   check(launch_moe_gemm_gate_up(sorted_x.data_ptr(), w13.data_ptr(), act.data_ptr(), counters.data_ptr<int>(),
                                 tile_expert.data_ptr<int>(), error_flag.data_ptr<int>(), sorted_rows,
                                 static_cast<int>(experts), static_cast<int>(hidden_size), static_cast<int>(inter), sms,
-                                stream), "gate/up GEMM");
+                                pair, stream), "gate/up GEMM");
   check(launch_moe_gemm_down(act.data_ptr(), w2.data_ptr(), y.data_ptr(), sorted_scale.data_ptr<float>(),
                              counters.data_ptr<int>(), tile_expert.data_ptr<int>(), error_flag.data_ptr<int>(),
                              sorted_rows, static_cast<int>(experts), static_cast<int>(hidden_size),
-                             static_cast<int>(inter), sms, stream), "down GEMM");
+                             static_cast<int>(inter), sms, pair, stream), "down GEMM");
   check(launch_moe_slot_sum(y.data_ptr(), entry_pos.data_ptr<int>(), valid_count.data_ptr<int>(), partial.data_ptr(),
                             static_cast<int>(rows), static_cast<int>(topk), static_cast<int>(hidden_size), stream),
         "slot sum");
@@ -82,10 +83,10 @@ void moe_forward(const at::Tensor& hidden, const at::Tensor& local_ids, const at
 }  // namespace
 
 void bind_moe(py::module_& m) {
-  m.def("moe_sizes", [](int64_t rows, int topk, int experts) {
-    const MoeSizes s = moe_sizes(rows, topk, experts);
+  m.def("moe_sizes", [](int64_t rows, int topk, int experts, int tile_rows) {
+    const MoeSizes s = moe_sizes(rows, topk, experts, tile_rows);
     return py::make_tuple(s.max_sorted_rows, s.max_tiles);
-  });
+  }, py::arg("rows"), py::arg("topk"), py::arg("experts"), py::arg("tile_rows") = kMoeTileRows);
   m.def("moe_forward", &moe_forward);
   m.attr("MOE_TILE_ROWS") = kMoeTileRows;
 }

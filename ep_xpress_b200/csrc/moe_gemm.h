@@ -17,7 +17,8 @@ struct MoeSizes {
 };
 
 // CPU-known bounds for `rows` received rows, `topk` slots per row and `experts` local experts.
-MoeSizes moe_sizes(long long rows, int topk, int experts);
+// `tile_rows` is 128, or 256 when the GEMMs run on CTA pairs.
+MoeSizes moe_sizes(long long rows, int topk, int experts, int tile_rows = kMoeTileRows);
 
 // Groups the (row, slot) pairs of this rank's experts by expert into 128-row tiles.
 //   sorted_row   int32 [max_sorted_rows]  source row of every sorted position, -1 = padding
@@ -29,7 +30,7 @@ MoeSizes moe_sizes(long long rows, int topk, int experts);
 cudaError_t launch_moe_align(const long long* local_ids, const float* weights, const int* valid_count, int rows,
                              int topk, int experts, long long max_sorted_rows, int max_tiles, int* sorted_row,
                              float* sorted_scale, int* entry_pos, int* tile_expert, int* counters,
-                             int* error_flag, cudaStream_t stream);
+                             int* error_flag, int tile_rows, cudaStream_t stream);
 
 // sorted_x[pos] = hidden[sorted_row[pos]] (zero rows for padding) for the tiles in use.
 cudaError_t launch_moe_gather(const void* hidden, const int* sorted_row, const int* counters, void* sorted_x,
@@ -37,14 +38,16 @@ cudaError_t launch_moe_gather(const void* hidden, const int* sorted_row, const i
 
 // GEMM 1: act[pos, :] = silu(x W1_e) * (x W3_e).  w13 is [experts, 2 * inter, hidden] (gate rows
 // first, then up rows), K-major. GEMM 2: y[pos, :] = (act W2_e) * sorted_scale[pos], w2 is
-// [experts, hidden, inter]. Shapes: hidden % 256 == 0, inter % 128 == 0.
+// [experts, hidden, inter]. Shapes: hidden % 256 == 0, inter % 128 == 0. `pair` runs the GEMM on
+// clusters of two CTAs (tcgen05 cta_group::2, 256-row tiles: align with tile_rows = 256).
 cudaError_t launch_moe_gemm_gate_up(const void* sorted_x, const void* w13, void* act, const int* counters,
                                     const int* tile_expert, int* error_flag, long long max_sorted_rows,
-                                    int experts, int hidden_size, int inter_size, int sms, cudaStream_t stream);
+                                    int experts, int hidden_size, int inter_size, int sms, bool pair,
+                                    cudaStream_t stream);
 cudaError_t launch_moe_gemm_down(const void* act, const void* w2, void* y, const float* sorted_scale,
                                  const int* counters, const int* tile_expert, int* error_flag,
                                  long long max_sorted_rows, int experts, int hidden_size, int inter_size, int sms,
-                                 cudaStream_t stream);
+                                 bool pair, cudaStream_t stream);
 
 // partial[row] = bf16(sum over slots, in slot order, of float(y[entry_pos[row, slot]])) for rows
 // below *valid_count.

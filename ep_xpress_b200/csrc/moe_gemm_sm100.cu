@@ -270,6 +270,209 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 
+// ---- the same GEMM on CTA pairs (thread-block clusters of two, tcgen05 cta_group::2) ------------
+// One 128 x 256 tile per SM needs 48 KB of operands per k-step; at full tensor rate that is
+// more L2 bandwidth x latency than four stages of shared memory can keep in flight. A pair
+// of CTAs computes a 256 x 256 tile instead: each CTA stages its own 128 rows of A and HALF
+// of the B tile (32 KB per k-step, six stages), the leader CTA's elected thread issues
+// tcgen05.mma.cta_group::2 which reads both CTAs' shared memory and writes each CTA's half
+// of the accumulator into that CTA's own TMEM, and both CTAs run their own epilogue. Both
+// producers complete their TMA loads on the LEADER's full barrier; the leader commits stage
+// releases and accumulator hand-offs to both CTAs' barriers. No load fans out to more than
+// one CTA: each CTA fetches exactly the bytes it keeps.
+constexpr int kPairStages = 6;
+constexpr int kPairBBytes = kBBytes / 2;
+constexpr int kPairStageBytes = kABytes + kPairBBytes;
+constexpr size_t kPairSmemBytes = static_cast<size_t>(kPairStages) * kPairStageBytes + 1024;
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory object in CTA `rank` of this cluster.
+__device__ __forceinline__ unsigned peer_smem_address(const void* local, unsigned rank) {
+  unsigned out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_address(local)), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_address) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, unsigned bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_address(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(unsigned* smem_result, unsigned columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(smem_address(smem_result)), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned address, unsigned columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                               unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(unsigned bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
+               : "memory");
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p) {
+  extern __shared__ __align__(1024) unsigned char gemm_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) &
+                                                         ~static_cast<uintptr_t>(1023));
+  __shared__ unsigned long long full_bar[kPairStages], empty_bar[kPairStages];
+  __shared__ unsigned long long acc_full[2], acc_empty[2];
+  __shared__ unsigned tmem_base_slot;
+  __shared__ volatile int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_ctarank();           // 0 = leader
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbarrier_init(full_bar + s, 1);                // leader's: one arrive.expect_tx + both CTAs' bytes
+      mbarrier_init(empty_bar + s, 1);               // one commit from the leader per use
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbarrier_init(acc_full + b, 1);                // one commit from the leader per tile
+      mbarrier_init(acc_empty + b, 8);               // leader's: four epilogue warps of each CTA
+    }
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  if (warp == 1) tmem_alloc_pair(&tmem_base_slot, 2 * kAccumColumns);
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync();                                    // both CTAs' barriers exist before anyone signals
+  tcgen05_fence_after();
+  const unsigned tmem_base = tmem_base_slot;
+
+  const int m_tiles = *p.num_m_tiles;                // 256-row tiles
+  const long long total_tiles = static_cast<long long>(m_tiles) * p.n_tiles;
+  const long long cluster_id = blockIdx.x / 2, clusters = gridDim.x / 2;
+  constexpr int kOutTile = kMode == 0 ? kTileN / 2 : kTileN;
+  constexpr int kPairM = 2 * kTileM;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (elect_one()) {
+      unsigned use = 0;
+      for (long long tile = cluster_id; tile < total_tiles && !failed; tile += clusters) {
+        const int m_tile = static_cast<int>(tile / p.n_tiles), n_tile = static_cast<int>(tile % p.n_tiles);
+        const int expert = p.tile_expert[m_tile];
+        // Mode 0: the leader keeps the gate rows, its peer the up rows. Mode 1: halves of the tile.
+        const int b_row = expert * p.b_rows_per_expert + n_tile * kOutTile +
+                          (kMode == 0 ? static_cast<int>(rank) * p.up_row_offset : static_cast<int>(rank) * (kTileN / 2));
+        for (int k = 0; k < p.k_steps; ++k, ++use) {
+          const int s = use % kPairStages;
+          if (!mbar_wait(empty_bar + s, ((use / kPairStages) & 1u) ^ 1u)) { failed = 1; break; }
+          unsigned char* a_dst = smem + static_cast<size_t>(s) * kPairStageBytes;
+          const unsigned leader_full = peer_smem_address(full_bar + s, 0);
+          if (rank == 0) mbarrier_arrive_expect_tx(full_bar + s, 2 * kPairStageBytes);
+          tma_load_2d_pair(a_dst, &map_a, k * kTileK, m_tile * kPairM + static_cast<int>(rank) * kTileM, leader_full);
+          tma_load_2d_pair(a_dst + kABytes, &map_b, k * kTileK, b_row, leader_full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader only) ----------------
+    if (rank == 0 && elect_one()) {
+      constexpr unsigned idesc = instruction_descriptor(kPairM, kTileN);
+      unsigned use = 0, local_tile = 0;
+      for (long long tile = cluster_id; tile < total_tiles && !failed; tile += clusters, ++local_tile) {
+        const unsigned buffer = local_tile & 1u;
+        if (!mbar_wait(acc_empty + buffer, ((local_tile >> 1) & 1u) ^ 1u)) { failed = 1; break; }
+        tcgen05_fence_after();
+        const unsigned tmem_d = tmem_base + buffer * kAccumColumns;
+        for (int k = 0; k < p.k_steps; ++k, ++use) {
+          const int s = use % kPairStages;
+          if (!mbar_wait(full_bar + s, (use / kPairStages) & 1u)) { failed = 1; break; }
+          tcgen05_fence_after();
+          const unsigned char* a_tile = smem + static_cast<size_t>(s) * kPairStageBytes;
+          const unsigned long long a_desc = smem_descriptor(a_tile);
+          const unsigned long long b_desc = smem_descriptor(a_tile + kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kTileK / 16; ++kk)
+            umma_bf16_pair(tmem_d, a_desc + 2 * kk, b_desc + 2 * kk, idesc, (k | kk) != 0 ? 1u : 0u);
+          umma_commit_pair(peer_smem_address(empty_bar + s, 0));     // both CTAs may refill the stage
+          umma_commit_pair(peer_smem_address(empty_bar + s, 1));
+        }
+        if (failed) break;
+        umma_commit_pair(peer_smem_address(acc_full + buffer, 0));   // both epilogues may read
+        umma_commit_pair(peer_smem_address(acc_full + buffer, 1));
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+    const int quadrant = warp & 3;
+    const int row_in_tile = static_cast<int>(rank) * kTileM + quadrant * 32 + lane;
+    unsigned local_tile = 0;
+    for (long long tile = cluster_id; tile < total_tiles; tile += clusters, ++local_tile) {
+      const int m_tile = static_cast<int>(tile / p.n_tiles), n_tile = static_cast<int>(tile % p.n_tiles);
+      const unsigned buffer = local_tile & 1u;
+      const bool ok = mbar_wait(acc_full + buffer, (local_tile >> 1) & 1u);
+      if (!__all_sync(0xffffffffu, ok)) { failed = 1; break; }
+      tcgen05_fence_after();
+      const unsigned taddr = tmem_base + buffer * kAccumColumns + (static_cast<unsigned>(quadrant * 32) << 16);
+      const long long row = static_cast<long long>(m_tile) * kPairM + row_in_tile;
+      __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(p.out) + row * p.out_columns +
+                               static_cast<long long>(n_tile) * kOutTile;
+      const float scale = kMode == 1 ? p.row_scale[row] : 1.f;
+#pragma unroll 1
+      for (int chunk = 0; chunk < kOutTile / 32; ++chunk) {
+        unsigned first[32];
+        unsigned second[32];
+        tmem_load_32(taddr + chunk * 32, first);
+        if (kMode == 0) tmem_load_32(taddr + kTileN / 2 + chunk * 32, second);
+        tmem_load_wait();
+        unsigned packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float lo, hi;
+          if (kMode == 0) {
+            const float g0 = __uint_as_float(first[2 * i]), g1 = __uint_as_float(first[2 * i + 1]);
+            lo = (g0 / (1.f + __expf(-g0))) * __uint_as_float(second[2 * i]);
+            hi = (g1 / (1.f + __expf(-g1))) * __uint_as_float(second[2 * i + 1]);
+          } else {
+            lo = __uint_as_float(first[2 * i]) * scale;
+            hi = __uint_as_float(first[2 * i + 1]) * scale;
+          }
+          packed[i] = static_cast<unsigned>(float_to_bf16_bits(lo)) | (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(out_row + chunk * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(peer_smem_address(acc_empty + buffer, 0));   // the leader's barrier
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync();                                    // the peer is done with this CTA's barriers and TMEM
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, 2 * kAccumColumns);
+  }
+  if (threadIdx.x == 0 && failed) atomicExch(p.error_flag, 1);
+}
+
 // ---- align / gather / slot-sum helper kernels ---------------------------------------------------
 constexpr int kAlignThreads = 1024;
 constexpr int kMaxLocalExperts = 1024;
@@ -288,7 +491,7 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(const long lon
                                                                   const float* __restrict__ weights,
                                                                   const int* __restrict__ valid_count, int rows,
                                                                   int topk, int experts, long long max_sorted_rows,
-                                                                  int max_tiles, int* sorted_row, float* sorted_scale,
+                                                                  int max_tiles, int tile, int* sorted_row, float* sorted_scale,
                                                                   int* entry_pos, int* tile_expert, int* counters,
                                                                   int* error_flag) {
   __shared__ int s_count[kMaxLocalExperts];
@@ -305,16 +508,16 @@ __global__ void __launch_bounds__(kAlignThreads) moe_align_kernel(const long lon
   if (threadIdx.x == 0) {
     int offset = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
-      const int padded = (s_count[e] + kTileM - 1) / kTileM * kTileM;
+      const int padded = (s_count[e] + tile - 1) / tile * tile;
       s_offset[e] = offset;
-      for (int t = 0; t < padded / kTileM && tiles < max_tiles; ++t) tile_expert[tiles++] = e;
+      for (int t = 0; t < padded / tile && tiles < max_tiles; ++t) tile_expert[tiles++] = e;
       offset += padded;
     }
     if (offset > max_sorted_rows) {           // the caller's bound on local pairs was too small
       atomicExch(error_flag, 2);
       offset = static_cast<int>(max_sorted_rows);
     }
-    counters[0] = tiles < offset / kTileM ? tiles : offset / kTileM;
+    counters[0] = tiles < offset / tile ? tiles : offset / tile;
     counters[1] = offset;
   }
   __syncthreads();
@@ -421,6 +624,27 @@ cudaError_t make_map(CUtensorMap* map, const void* base, long long rows, long lo
 constexpr size_t kGemmSmemBytes = static_cast<size_t>(kGemmStages) * kStageBytesGemm + 1024;
 
 template <int kMode>
+cudaError_t launch_gemm_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& params, int sms,
+                             cudaStream_t stream) {
+  cudaError_t err = cudaFuncSetAttribute(grouped_gemm_pair_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kPairSmemBytes));
+  if (err != cudaSuccess) return err;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(sms / 2 * 2, 1, 1);
+  config.blockDim = dim3(kGemmThreads, 1, 1);
+  config.dynamicSmemBytes = kPairSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 2;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, grouped_gemm_pair_kernel<kMode>, map_a, map_b, params);
+}
+
+template <int kMode>
 cudaError_t launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemmParams& params, int sms,
                         cudaStream_t stream) {
   cudaError_t err = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -432,25 +656,25 @@ cudaError_t launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, cons
 
 }  // namespace
 
-MoeSizes moe_sizes(long long rows, int topk, int experts) {
+MoeSizes moe_sizes(long long rows, int topk, int experts, int tile_rows) {
   const long long per_row = topk < experts ? topk : experts;
   const long long entries = rows * per_row;
   MoeSizes sizes;
-  sizes.max_tiles = static_cast<int>((entries + kTileM - 1) / kTileM + experts);
-  sizes.max_sorted_rows = static_cast<long long>(sizes.max_tiles) * kTileM;
+  sizes.max_tiles = static_cast<int>((entries + tile_rows - 1) / tile_rows + experts);
+  sizes.max_sorted_rows = static_cast<long long>(sizes.max_tiles) * tile_rows;
   return sizes;
 }
 
 cudaError_t launch_moe_align(const long long* local_ids, const float* weights, const int* valid_count, int rows,
                              int topk, int experts, long long max_sorted_rows, int max_tiles, int* sorted_row,
                              float* sorted_scale, int* entry_pos, int* tile_expert, int* counters,
-                             int* error_flag, cudaStream_t stream) {
-  if (experts > kMaxLocalExperts) return cudaErrorInvalidValue;
+                             int* error_flag, int tile_rows, cudaStream_t stream) {
+  if (experts > kMaxLocalExperts || (tile_rows != kTileM && tile_rows != 2 * kTileM)) return cudaErrorInvalidValue;
   moe_fill_kernel<<<296, 256, 0, stream>>>(sorted_row, sorted_scale, max_sorted_rows, entry_pos,
                                            static_cast<long long>(rows) * topk);
   moe_align_kernel<<<1, kAlignThreads, 0, stream>>>(local_ids, weights, valid_count, rows, topk, experts,
-                                                    max_sorted_rows, max_tiles, sorted_row, sorted_scale, entry_pos,
-                                                    tile_expert, counters, error_flag);
+                                                    max_sorted_rows, max_tiles, tile_rows, sorted_row, sorted_scale,
+                                                    entry_pos, tile_expert, counters, error_flag);
   return cudaGetLastError();
 }
 
@@ -464,7 +688,8 @@ cudaError_t launch_moe_gather(const void* hidden, const int* sorted_row, const i
 
 cudaError_t launch_moe_gemm_gate_up(const void* sorted_x, const void* w13, void* act, const int* counters,
                                     const int* tile_expert, int* error_flag, long long max_sorted_rows,
-                                    int experts, int hidden_size, int inter_size, int sms, cudaStream_t stream) {
+                                    int experts, int hidden_size, int inter_size, int sms, bool pair,
+                                    cudaStream_t stream) {
   if (hidden_size % kTileK || inter_size % kMoeGateUpTile) return cudaErrorInvalidValue;
   CUtensorMap map_a, map_b;
   cudaError_t err = make_map(&map_a, sorted_x, max_sorted_rows, hidden_size, kTileM);
@@ -481,18 +706,19 @@ cudaError_t launch_moe_gemm_gate_up(const void* sorted_x, const void* w13, void*
   params.out_columns = inter_size;
   params.b_rows_per_expert = 2 * inter_size;
   params.up_row_offset = inter_size;
-  return launch_gemm<0>(map_a, map_b, params, sms, stream);
+  return pair ? launch_gemm_pair<0>(map_a, map_b, params, sms, stream)
+              : launch_gemm<0>(map_a, map_b, params, sms, stream);
 }
 
 cudaError_t launch_moe_gemm_down(const void* act, const void* w2, void* y, const float* sorted_scale,
                                  const int* counters, const int* tile_expert, int* error_flag,
                                  long long max_sorted_rows, int experts, int hidden_size, int inter_size, int sms,
-                                 cudaStream_t stream) {
+                                 bool pair, cudaStream_t stream) {
   if (inter_size % kTileK || hidden_size % kMoeDownTile) return cudaErrorInvalidValue;
   CUtensorMap map_a, map_b;
   cudaError_t err = make_map(&map_a, act, max_sorted_rows, inter_size, kTileM);
   if (err != cudaSuccess) return err;
-  err = make_map(&map_b, w2, static_cast<long long>(experts) * hidden_size, inter_size, kTileN);
+  err = make_map(&map_b, w2, static_cast<long long>(experts) * hidden_size, inter_size, pair ? kTileN / 2 : kTileN);
   if (err != cudaSuccess) return err;
   GemmParams params{};
   params.num_m_tiles = counters;
@@ -505,7 +731,8 @@ cudaError_t launch_moe_gemm_down(const void* act, const void* w2, void* y, const
   params.out_columns = hidden_size;
   params.b_rows_per_expert = hidden_size;
   params.up_row_offset = 0;
-  return launch_gemm<1>(map_a, map_b, params, sms, stream);
+  return pair ? launch_gemm_pair<1>(map_a, map_b, params, sms, stream)
+              : launch_gemm<1>(map_a, map_b, params, sms, stream);
 }
 
 cudaError_t launch_moe_slot_sum(const void* y, const int* entry_pos, const int* valid_count, void* partial,

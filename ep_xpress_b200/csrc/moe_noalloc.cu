@@ -105,15 +105,16 @@ extern "C" int epx_moe_forward_noalloc(const void* hidden, const long long* loca
   if (err != cudaSuccess) return fail(err);
   const long long sorted_rows = sizes.max_sorted_rows;   // <= kSortedRows, a multiple of 128
   err = epx::launch_moe_align(local_ids, weights, valid_count, rows, topk, experts, sorted_rows, sizes.max_tiles,
-                              sorted_row, sorted_scale, entry_pos, tile_expert, counters, error_flag, stream);
+                              sorted_row, sorted_scale, entry_pos, tile_expert, counters, error_flag,
+                              epx::kMoeTileRows, stream);
   if (err != cudaSuccess) return fail(err);
   err = epx::launch_moe_gather(hidden, sorted_row, counters, sorted_x, sorted_rows, hidden_size, stream);
   if (err != cudaSuccess) return fail(err);
   err = epx::launch_moe_gemm_gate_up(sorted_x, w13, act, counters, tile_expert, error_flag, sorted_rows, experts,
-                                     hidden_size, inter_size, state->sms, stream);
+                                     hidden_size, inter_size, state->sms, false, stream);
   if (err != cudaSuccess) return fail(err);
   err = epx::launch_moe_gemm_down(act, w2, y, sorted_scale, counters, tile_expert, error_flag, sorted_rows, experts,
-                                  hidden_size, inter_size, state->sms, stream);
+                                  hidden_size, inter_size, state->sms, false, stream);
   if (err != cudaSuccess) return fail(err);
   err = epx::launch_moe_slot_sum(y, entry_pos, valid_count, partial, rows, topk, hidden_size, stream);
   if (err != cudaSuccess) return fail(err);

@@ -15,13 +15,15 @@ class SwiGLUMoELayer:
     :mod:`ep_xpress_b200.ops.moe`.
     """
 
-    def __init__(self, context, w13, w2, *, recv_capacity=None, local_tokens=None, max_local_pairs=None):
+    def __init__(self, context, w13, w2, *, recv_capacity=None, local_tokens=None, max_local_pairs=None,
+                 pair_ctas=True):
         cfg = context.config
         self.context = context
         capacity = context.world_size * cfg.max_tokens_per_rank if recv_capacity is None else recv_capacity
         tokens = cfg.max_tokens_per_rank if local_tokens is None else local_tokens
         self.workspace = context.create_workspace(capacity, tokens)
-        self.experts = GroupedSwiGLU(w13, w2, max_rows=capacity, topk=cfg.topk, max_local_pairs=max_local_pairs)
+        self.experts = GroupedSwiGLU(w13, w2, max_rows=capacity, topk=cfg.topk, max_local_pairs=max_local_pairs,
+                                     pair_ctas=pair_ctas)
         self.kernel_launches_per_forward = 2 + self.experts.kernel_launches_per_forward
 
     def forward(self, x, topk_ids, topk_weights, *, stream=None, timing=None):

@@ -22,7 +22,7 @@ from .. import native as _native_loader
 
 
 class GroupedSwiGLU:
-    def __init__(self, w13, w2, *, max_rows, topk, max_local_pairs=None):
+    def __init__(self, w13, w2, *, max_rows, topk, max_local_pairs=None, pair_ctas=False):
         """``max_local_pairs`` bounds the (row, slot) pairs whose expert lives on this rank.
 
         The default is the worst case (every slot of every row is local). A tighter,
@@ -40,8 +40,9 @@ class GroupedSwiGLU:
         self.native = _native_loader.load()
         self.w13, self.w2 = w13.contiguous(), w2.contiguous()
         self.experts, self.hidden, self.inter, self.topk, self.max_rows = experts, hidden, inter, topk, max_rows
-        tile = self.native.MOE_TILE_ROWS
-        worst_rows, _ = self.native.moe_sizes(max_rows, topk, experts)
+        self.pair_ctas = bool(pair_ctas)        # GEMMs on clusters of two CTAs (256-row tiles)
+        tile = self.native.MOE_TILE_ROWS * (2 if self.pair_ctas else 1)
+        worst_rows, _ = self.native.moe_sizes(max_rows, topk, experts, tile)
         if max_local_pairs is None:
             sorted_rows = worst_rows
         else:
@@ -68,7 +69,7 @@ class GroupedSwiGLU:
         stream = stream or torch.cuda.current_stream(hidden.device)
         self.native.moe_forward(hidden, local_ids, weights, valid_count, self.w13, self.w2, out, self.sorted_row,
                                 self.sorted_scale, self.entry_pos, self.tile_expert, self.counters, self.error_flag,
-                                self.sorted_x, self.act, self.y, stream.cuda_stream)
+                                self.sorted_x, self.act, self.y, stream.cuda_stream, self.pair_ctas)
         return out
 
     __call__ = forward

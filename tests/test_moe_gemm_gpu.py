@@ -48,6 +48,28 @@ def test_matches_fp32_reference(rows, topk, experts, hidden, inter, valid):
     assert torch.equal(again[:valid], out[:valid])
 
 
+@pytest.mark.parametrize("rows,topk,experts,hidden,inter,valid", [
+    (64, 2, 2, 256, 128, 64),
+    (700, 4, 3, 512, 256, 650),
+    (1000, 8, 8, 1024, 384, 1000),
+])
+def test_cta_pairs_match_fp32_reference_and_single_cta_path(rows, topk, experts, hidden, inter, valid):
+    """tcgen05 cta_group::2 on clusters of two CTAs (256-row tiles) against the same oracle."""
+    x, ids, weights, count, w13, w2 = make_case(rows, topk, experts, hidden, inter, valid, seed=rows + 1)
+    pair = GroupedSwiGLU(w13, w2, max_rows=rows, topk=topk, pair_ctas=True)
+    out = torch.full((rows, hidden), 7.0, dtype=torch.bfloat16, device="cuda")
+    pair(x, ids, weights, count, out=out)
+    pair.check()
+    want = swiglu_reference(x, ids, weights, valid, w13, w2)
+    scale = want[:valid].float().abs().max().clamp(min=1e-3)
+    assert ((out[:valid].float() - want[:valid].float()).abs().max() / scale).item() < 2e-2
+    assert (out[valid:] == 7.0).all()
+    single = GroupedSwiGLU(w13, w2, max_rows=rows, topk=topk)
+    other = torch.empty_like(out)
+    single(x, ids, weights, count, out=other)
+    assert torch.equal(other[:valid], out[:valid])     # same accumulation order per output row
+
+
 def test_pair_bound_overflow_is_reported():
     x, ids, weights, count, w13, w2 = make_case(512, 4, 2, 256, 128, 512, seed=3, local_fraction=1.0)
     runner = GroupedSwiGLU(w13, w2, max_rows=512, topk=4, max_local_pairs=128)
