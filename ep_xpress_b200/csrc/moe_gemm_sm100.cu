@@ -565,27 +565,45 @@ __global__ void __launch_bounds__(256) moe_slot_sum_kernel(const uint4* __restri
   const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x / 32);
   for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x / 32) + (threadIdx.x >> 5); row < valid;
        row += warps) {
-    for (int base = lane; base < vecs_per_row; base += 32) {
-      float acc[8];
+    // Lane k holds the sorted position of slot k (fetched once per row, not once per chunk).
+    const int slots = min(topk, 32);
+    const int my_pos = lane < slots ? entry_pos[row * topk + lane] : -1;
+    for (int start = 0; start < vecs_per_row; start += 64) {          // warp-uniform; two chunks per lane in flight
+      const int base = start + lane;
+      float acc[2][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
       for (int k = 0; k < topk; ++k) {
-        const int pos = entry_pos[row * topk + k];
+        const int pos = k < 32 ? __shfl_sync(0xffffffffu, my_pos, k) : entry_pos[row * topk + k];
         if (pos < 0) continue;
-        const uint4 v = y[static_cast<long long>(pos) * vecs_per_row + base];
-        const unsigned w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(w[i] << 16));
-          acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+        for (int u = 0; u < 2; ++u) {
+          const int at = base + u * 32;
+          if (at < vecs_per_row) {
+            const uint4 v = y[static_cast<long long>(pos) * vecs_per_row + at];
+            const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc[u][2 * i] = __fadd_rn(acc[u][2 * i], __uint_as_float(w[i] << 16));
+              acc[u][2 * i + 1] = __fadd_rn(acc[u][2 * i + 1], __uint_as_float(w[i] & 0xffff0000u));
+            }
+          }
         }
       }
-      unsigned out[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        out[i] = static_cast<unsigned>(float_to_bf16_bits(acc[2 * i])) |
-                 (static_cast<unsigned>(float_to_bf16_bits(acc[2 * i + 1])) << 16);
-      partial[row * vecs_per_row + base] = make_uint4(out[0], out[1], out[2], out[3]);
+      for (int u = 0; u < 2; ++u) {
+        const int at = base + u * 32;
+        if (at < vecs_per_row) {
+          unsigned out[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            out[i] = static_cast<unsigned>(float_to_bf16_bits(acc[u][2 * i])) |
+                     (static_cast<unsigned>(float_to_bf16_bits(acc[u][2 * i + 1])) << 16);
+          partial[row * vecs_per_row + at] = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+      }
     }
   }
 }
