@@ -1,0 +1,54 @@
+"""Heap carving and Python/native layout agreement (no GPU: only host functions of the runtime)."""
+
+import pytest
+
+from ep_xpress_b200 import Config, native
+from ep_xpress_b200.parallel.core import HeapAllocator
+
+
+def test_allocator_first_fit_coalescing_and_exhaustion():
+    heap = HeapAllocator(4096, 4096 + 10 * 4096)
+    a = heap.allocate(4096)
+    b = heap.allocate(2 * 4096 - 1)          # rounded up to whole pages
+    c = heap.allocate(4096)
+    assert (a, b, c) == (4096, 8192, 16384)
+    heap.release(b)
+    assert heap.allocate(4096) == 8192      # first fit reuses the hole
+    heap.release(a)
+    heap.release(8192)
+    assert heap.allocate(3 * 4096) == 4096  # neighbouring holes were merged
+    assert heap.free_bytes == 6 * 4096
+    with pytest.raises(MemoryError, match="workspace_pool_bytes"):
+        heap.allocate(7 * 4096)
+    with pytest.raises(KeyError):
+        heap.release(12345)
+    with pytest.raises(ValueError):
+        HeapAllocator(100, 4096)
+
+
+@pytest.mark.parametrize("hidden,topk,tokens,world", [(256, 2, 64, 2), (7168, 8, 4096, 8), (258, 3, 17, 5),
+                                                      (2048, 33, 100, 63), (64, 1, 1, 1)])
+def test_python_layout_mirrors_the_native_layout(hidden, topk, tokens, world):
+    m = native.load()
+    cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens)
+    assert m.ctrl_bytes(world) == cfg.ctrl_bytes(world)
+    assert m.slot_bytes(world * tokens, tokens, hidden, topk, world) == cfg.nvlink_slot_bytes(world)
+    assert m.slot_bytes(10, 3, hidden, topk, world) == cfg.nvlink_slot_bytes(world, 10, 3)
+    assert cfg.heap_bytes(world) >= cfg.ctrl_bytes(world) + cfg.slots * cfg.nvlink_slot_bytes(world)
+
+
+def test_expert_runner_bounds():
+    m = native.load()
+    assert m.moe_sizes(1024, 8, 32) == (12288, 96)
+    assert m.moe_sizes(1024, 8, 32, 256) == ((8192 // 256 + 32) * 256, 64)
+    assert m.moe_sizes(10, 8, 2)[1] == 1 + 2            # at most min(topk, experts) local slots per row
+
+
+def test_build_identity_is_stable_and_lazy_import_does_not_touch_cuda():
+    import subprocess
+    import sys
+    assert native.build_identity() == native.build_identity()
+    code = ("import sys, ep_xpress_b200; assert 'torch' not in sys.modules; "
+            "assert 'ep_xpress_b200.native' not in sys.modules; print(ep_xpress_b200.__all__)")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
