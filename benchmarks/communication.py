@@ -47,6 +47,8 @@ def parse_args():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--samples", type=int, default=20)
     parser.add_argument("--nccl-reference", action="store_true")
+    parser.add_argument("--items-per-cta", type=int, default=None, help="launch-width policy (see set_tuning)")
+    parser.add_argument("--max-ctas", type=int, default=None, help="cap on CTAs per operation")
     parser.add_argument("--report", default=None, help="write the JSON report here (rank 0)")
     return parser.parse_args()
 
@@ -149,7 +151,7 @@ def run_tokens(ep, args, shape, tokens, rank, world, owner):
             samples["combine"].append(marks[2].elapsed_time(marks[3]) * 1e3)
             samples["layer"].append(marks[0].elapsed_time(marks[3]) * 1e3)
     ep.check()
-    result = {"tokens_per_rank": tokens, "capacity": capacity}
+    result = {"tokens_per_rank": tokens, "capacity": capacity, "ctas": state["batch"].handle._plan.ctas}
     for name, values in samples.items():
         result[name + "_us"] = summarize(max_over_ranks(values, world))
     mean_bytes = sum(volumes) / len(volumes)
@@ -199,6 +201,8 @@ def main():
                                                  max_tokens_per_rank=max(args.tokens)).nvlink_slot_bytes(world))
     ep = Context(get_nccl_comm_handle(dist.group.WORLD), emap, cfg)
     ep.enable_cuda_graph()
+    if args.items_per_cta is not None or args.max_ctas is not None:
+        ep.set_tuning(items_per_cta=args.items_per_cta, max_ctas=args.max_ctas)
     report = {"schema": 1, "world_size": world, "shape": args.shape, **shape, "routing": args.routing,
               "warmup": args.warmup, "samples": args.samples, "timing": "CUDA events, max over ranks per sample",
               "link_gbs_measured": LINK_GBS_MEASURED, "results": []}

@@ -151,6 +151,10 @@ class Config:
 
     def pool_bytes(self, world_size, *, local_world_size=None) -> int:
         """Host memory of the host-staged transport: one send ring per rank and phase."""
+        if self.internode_transport == "gin":
+            if not _is_int(local_world_size) or not _is_int(world_size) or local_world_size >= world_size:
+                raise ValueError("GIN host budgeting requires this node's local_world_size < world_size")
+            return local_world_size * self.gin_producer_bytes(local_world_size)
         _check_world(world_size)
         if self.device_transport:
             return 0
@@ -189,6 +193,49 @@ class Config:
         slot = self.nvlink_slot_bytes(world_size)
         reserve = self.workspace_pool_bytes or 2 * slot
         return _round_up(self.ctrl_bytes(world_size) + self.slots * slot + reserve, 2 << 20)
+
+    def mapped_arena_bytes(self, topk, channels=None, queue_peers=1, *, dispatch_banks=0) -> int:
+        """Host-mapped queue bytes of one producer: always 0 here.
+
+        The reference sizes a mapped ``/dev/shm`` arena per producer with this helper
+        (ep_xpress/config.py:167-191). The device transports of this library stage nothing in
+        host memory (``heap_bytes`` is their footprint, in HBM), so the answer is zero for every
+        legal argument; the arguments are still validated so that budgeting code ported from
+        the reference fails on the same mistakes.
+        """
+        if not _is_int(dispatch_banks) or dispatch_banks not in (0, 2):
+            raise ValueError("dispatch_banks must be 0 or 2")
+        if dispatch_banks and not topk:
+            raise ValueError("extra dispatch banks are only valid for dispatch")
+        if not _is_int(queue_peers) or not 1 <= queue_peers <= 63 or (topk and queue_peers != 1):
+            raise ValueError("queue_peers must be in [1, 63] and dispatch requires one queue")
+        return 0
+
+    # ---- multi-node (GIN) staging layout: sizing only, the transport itself is gated ----------
+    def _gin_record_bytes(self) -> int:
+        """One dispatch record on the wire: BF16 row, K int32 ids, K fp32 weights, token index."""
+        return _round_up(self.hidden_size * 2 + self.topk * 8 + 4, 128)
+
+    def gin_producer_bytes(self, local_world_size) -> int:
+        """Host bytes one producer needs on its node: its dispatch records (read by the node's
+        other ranks) followed by one combine row slot per (local peer, token).
+        Same arithmetic as ep_xpress/config.py:103-112."""
+        if not _is_int(local_world_size) or not 1 <= local_world_size <= 256:
+            raise ValueError("local_world_size must be an integer in [1, 256]")
+        records = _round_up(128 + self.max_tokens_per_rank * self._gin_record_bytes(), 4096)
+        rows = local_world_size * self.max_tokens_per_rank * self.hidden_size * 2
+        return _round_up(records + rows, 4096)
+
+    def gin_registered_bytes(self, world_size) -> int:
+        """GPU bytes one rank registers with the network: a count header, a send window plus one
+        receive window per rank of dispatch records, and FP32-wide combine rows per source rank,
+        rounded to 2 MiB registration granules (ep_xpress/config.py:114-123)."""
+        if not _is_int(world_size) or not 2 <= world_size <= 256:
+            raise ValueError("GIN world_size must be an integer in [2, 256]")
+        header = _round_up(world_size * 8, 128)
+        windows = (world_size + 1) * self.max_tokens_per_rank * self._gin_record_bytes()
+        rows = world_size * self.max_tokens_per_rank * self.hidden_size * 4
+        return _round_up(header + windows + rows, 2 << 20)
 
     def mailbox_arena_bytes(self, world_size, *, packet_rows=0) -> int:
         """Decode mailboxes are ordinary slots of the heap; no separate arena exists."""

@@ -521,10 +521,10 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
 
   // ---- B. signal ------------------------------------------------------------------------
   if (tid == 0) {
-    __threadfence_system();
+    __threadfence_system();   // this CTA's peer stores are performed system-wide before it arrives
     const unsigned prev = atomicAdd(&hdr->cdone_count, 1u);
     s_last = (prev == gridDim.x - 1) ? 1 : 0;
-    if (s_last) __threadfence_system();
+    if (s_last) __threadfence();   // acquire side of the arrival counter; the flag store below releases at sys scope
   }
   __syncthreads();
   if (s_last && tid < W && tid != self) {

@@ -353,10 +353,10 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   __syncthreads();
   profile_stamp(op.profile, 4);
   if (tid == 0) {
-    __threadfence_system();
+    __threadfence_system();   // this CTA's peer stores are performed system-wide before it arrives
     const unsigned prev = atomicAdd(&hdr->done_count, 1u);
     s_last = (prev == gridDim.x - 1) ? 1 : 0;
-    if (s_last) __threadfence_system();
+    if (s_last) __threadfence();   // acquire side of the arrival counter; the flag store below releases at sys scope
   }
   __syncthreads();
   if (s_last) {

@@ -107,6 +107,7 @@ class TransportCore:
         ctrl = self.engine.ctrl_bytes()
         self._allocators = [HeapAllocator(ctrl, heap_bytes) for _ in self.local_ranks]
         self.max_ctas = max(1, min(self.engine.max_ctas(config.max_tokens_per_rank), self.engine.sm_count()))
+        self.items_per_cta = native.THREADS // 32   # (token, row segment) work items a CTA should find
         self.launches = 0
 
     # ---- slots ---------------------------------------------------------------
@@ -150,7 +151,7 @@ class TransportCore:
         """CTAs per rank: enough warps for every (token, 2 KiB row segment), within the budget."""
         budget = self.max_ctas if budget is None else max(1, min(budget, self.max_ctas))
         segments = max(1, self.hidden * 2 // 2048)
-        wanted = -(-max(tokens, 1) * segments // (self.native.THREADS // 32))
+        wanted = -(-max(tokens, 1) * segments // max(1, self.items_per_cta))
         return max(1, min(budget, wanted))
 
     def dispatch(self, slot: Slot, xs, ids, weights, capacities, *, identity=0, ctas=None, stream=None,

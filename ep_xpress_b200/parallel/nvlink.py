@@ -183,6 +183,7 @@ class NVLinkContext(Context):
                 self._release_resources()
                 raise RuntimeError("peer heap mapping failed: " + "; ".join(failures))
             self._core.max_ctas = min(width for width, _ in negotiated)
+            self._negotiated_ctas = self._core.max_ctas
             self.effective_channels = min(config.channels, 32)
             self._work_stream = torch.cuda.Stream(self.device)
             comm.barrier()
@@ -224,6 +225,20 @@ class NVLinkContext(Context):
                     "max_ctas": self._core.max_ctas, "effective_channels": self.effective_channels}
 
     # ------------------------------------------------------------------ graphs
+    def set_tuning(self, *, items_per_cta=None, max_ctas=None):
+        """Launch-width policy: a CTA is launched per ``items_per_cta`` (token, 2 KiB row segment)
+        work items, at most ``max_ctas`` (never above the width negotiated at bootstrap). Call it
+        between operations, before graph capture; every rank may choose its own values."""
+        with self._lock:
+            if items_per_cta is not None:
+                if int(items_per_cta) < 1:
+                    raise ValueError("items_per_cta must be positive")
+                self._core.items_per_cta = int(items_per_cta)
+            if max_ctas is not None:
+                if not 1 <= int(max_ctas) <= self._negotiated_ctas:
+                    raise ValueError(f"max_ctas must be within 1..{self._negotiated_ctas}")
+                self._core.max_ctas = int(max_ctas)
+
     def enable_cuda_graph(self):
         """Allow capture of direct-stream operations. Call on every rank, outside capture."""
         with self._lock:

@@ -71,3 +71,31 @@ def test_gin_is_gated_at_context_creation():
     cfg = Config(hidden_size=64, topk=2, max_tokens_per_rank=8, transport="host_sm", internode_transport="gin")
     with pytest.raises(NotImplementedError, match="second node"):
         Context(None, [0], cfg)
+
+
+def test_multinode_sizing_helpers_follow_the_record_layout():
+    cfg = Config(hidden_size=256, topk=2, max_tokens_per_rank=64, transport="host_sm", internode_transport="gin")
+    record = 640                                   # 512 B row + 16 B ids/weights + 4 B token -> 128-byte units
+    records = (128 + 64 * record + 4095) // 4096 * 4096
+    assert cfg.gin_producer_bytes(4) == (records + 4 * 64 * 512 + 4095) // 4096 * 4096
+    granule = 2 << 20
+    raw = 128 + (16 + 1) * 64 * record + 16 * 64 * 256 * 4
+    assert cfg.gin_registered_bytes(16) == (raw + granule - 1) // granule * granule
+    assert cfg.pool_bytes(16, local_world_size=4) == 4 * cfg.gin_producer_bytes(4)
+    with pytest.raises(ValueError, match="local_world_size < world_size"):
+        cfg.pool_bytes(16, local_world_size=16)
+    with pytest.raises(ValueError, match=r"\[2, 256\]"):
+        cfg.gin_registered_bytes(1)
+    with pytest.raises(ValueError, match=r"\[1, 256\]"):
+        cfg.gin_producer_bytes(True)
+
+
+def test_mapped_arena_is_empty_but_validated():
+    cfg = Config(hidden_size=256, topk=2, max_tokens_per_rank=64)
+    assert cfg.mapped_arena_bytes(2) == 0 and cfg.mapped_arena_bytes(0, queue_peers=8) == 0
+    with pytest.raises(ValueError, match="dispatch_banks"):
+        cfg.mapped_arena_bytes(2, dispatch_banks=1)
+    with pytest.raises(ValueError, match="only valid for dispatch"):
+        cfg.mapped_arena_bytes(0, dispatch_banks=2)
+    with pytest.raises(ValueError, match="queue_peers"):
+        cfg.mapped_arena_bytes(2, queue_peers=2)

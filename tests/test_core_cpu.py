@@ -3,7 +3,7 @@
 import pytest
 
 from ep_xpress_b200 import Config, native
-from ep_xpress_b200.parallel.core import HeapAllocator
+from ep_xpress_b200.parallel.core import HeapAllocator, TransportCore
 
 
 def test_allocator_first_fit_coalescing_and_exhaustion():
@@ -52,3 +52,12 @@ def test_build_identity_is_stable_and_lazy_import_does_not_touch_cuda():
             "assert 'ep_xpress_b200.native' not in sys.modules; print(ep_xpress_b200.__all__)")
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
     assert out.returncode == 0, out.stderr
+
+
+def test_launch_width_follows_items_per_cta():
+    core = object.__new__(TransportCore)
+    core.hidden, core.max_ctas, core.items_per_cta = 7168, 148, 16
+    assert core.pick_ctas(128) == 56 and core.pick_ctas(4096) == 148 and core.pick_ctas(1) == 1
+    assert core.pick_ctas(128, budget=30) == 30 and core.pick_ctas(0) == 1
+    core.items_per_cta = 4
+    assert core.pick_ctas(8) == 14 and core.pick_ctas(128) == 148

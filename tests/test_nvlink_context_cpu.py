@@ -65,6 +65,7 @@ def ctx():
     c._work_stream = FakeStream("work")
     core = mock.Mock()
     core.max_ctas = 100
+    c._negotiated_ctas = 100
     core.pick_ctas.side_effect = lambda tokens, budget=None: budget
     core.create_slot.side_effect = lambda capacity, tokens, stream=None: fake_slot(capacity, tokens)
     c._core = core
@@ -234,3 +235,15 @@ def test_device_status_surfaces_at_check(ctx):
         ctx.ep.check()
     with pytest.raises(RuntimeError, match="failed state"):
         ctx.ep.check()
+
+
+def test_set_tuning_bounds_the_launch_width(ctx):
+    ctx.ep.set_tuning(items_per_cta=4, max_ctas=40)
+    assert ctx.core.items_per_cta == 4 and ctx.core.max_ctas == 40
+    ctx.ep.dispatch_on_stream(*inputs(), active_channels=2)
+    assert ctx.core.dispatch.call_args[1]["ctas"] == 20          # half of the lowered budget
+    with pytest.raises(ValueError, match="within 1..100"):
+        ctx.ep.set_tuning(max_ctas=101)                            # never above the negotiated width
+    with pytest.raises(ValueError, match="positive"):
+        ctx.ep.set_tuning(items_per_cta=0)
+    assert ctx.core.max_ctas == 40 and ctx.ep._failed is None      # misuse does not poison the context
