@@ -62,6 +62,8 @@ def parse_args():
     parser.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     parser.add_argument("--routing", choices=("uniform", "zipf"), default="uniform")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--cpu-numa", choices=("auto", "off"), default="auto",
+                        help="auto: run on the CPUs of the GPU's NUMA node before pinned memory is allocated")
     parser.add_argument("--graph", choices=("auto", "on", "off"), default="auto",
                         help="replay the layer from CUDA graphs (auto: on for the decode shape)")
     parser.add_argument("--plain-launch", action="store_true", help="ordinary instead of cooperative launches")
@@ -258,6 +260,10 @@ def run(args):
     shape = SHAPES[args.config]
     tokens = shape["tokens"] if args.tokens is None else args.tokens
     sets = 4
+    placement = {"bound": False, "reason": "--cpu-numa off"}
+    if args.cpu_numa == "auto":
+        from ep_xpress_b200.utils import numa
+        placement = numa.bind_to_device(local)
     host = make_inputs(shape, tokens, world, rank, args.routing, sets)
     device = [tuple(t.cuda(non_blocking=True) for t in batch) for batch in host]
     arm = (OursArm if args.impl == "ours" else ReferenceArm)(shape, tokens, world, rank, local, args.plain_launch)
@@ -316,7 +322,7 @@ def run(args):
                 stream.wait_event(ready[slot])
                 out, valid = arm.step(*staging[slot])
                 consumed[slot].record(stream)
-                result = torch.stack([out.float().sum(), valid.float().sum()])
+                result = torch.stack([out.sum(dtype=torch.float32), valid.sum(dtype=torch.float32)])
                 result_host.copy_(result, non_blocking=True)
                 stream.synchronize()                     # the host reads this step's result
                 checksum += float(result_host[0])
@@ -352,7 +358,7 @@ def run(args):
         "config": {"model": shape["model"], "global_batch": world * tokens, "seq_len": tokens,
                    "tokens_per_rank": tokens, "hidden": shape["hidden"], "experts": shape["experts"],
                    "topk": shape["topk"], "routing": args.routing, "parallelism": f"ep{world}",
-                   "cuda_graph": bool(use_graph),
+                   "cuda_graph": bool(use_graph), "cpu_numa": placement,
                    "l2": "inputs rotate over 4 batches; a step touches far more than the 126 MB L2"},
         "dispatch_us_p50": statistics.median(dispatch_us), "combine_us_p50": statistics.median(combine_us),
         "dispatch_combine_us_p50": statistics.median(both_us),
