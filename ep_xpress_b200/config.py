@@ -64,6 +64,7 @@ class Config:
     combine_rounding: str = "two_step"        # "two_step" (single-node reference) or "single" (multi-node reference)
     zero_padding: bool = True                 # keep activation rows above valid_count at zero
     cooperative_launch: bool = True           # driver-guaranteed co-residency of the transport CTAs
+    combine_streaming: str = "auto"           # reduce while peers still push: "auto" (large batches), "on", "off"
 
     @property
     def device_transport(self) -> bool:
@@ -117,6 +118,8 @@ class Config:
             raise NotImplementedError("transport must be nvlink, host_sm or host_ce")
         if self.combine_rounding not in ("two_step", "single"):
             raise ValueError("combine_rounding must be two_step or single")
+        if self.combine_streaming not in ("auto", "on", "off"):
+            raise ValueError("combine_streaming must be auto, on or off")
         if device:
             if self.hidden_size % 2 or self.hidden_size > (1 << 31) - 1:
                 raise ValueError("host_sm requires an even hidden size that fits int32")

@@ -198,25 +198,25 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 // needs few registers; a producer's per-item bookkeeping is a serial instruction stream of
 // about a microsecond, which is why there are four of them. Route look-ups (mask, row
 // indices) are loaded for 32 items at once and one batch ahead.
-constexpr int kConsumerWarps = kThreads / 32;
-constexpr int kConsumerGroups = 4;
-constexpr int kGroupWarps = kConsumerWarps / kConsumerGroups;
+constexpr int kGroupWarps = 4;                    // consumer warps of one pipeline
 constexpr int kGroupThreads = kGroupWarps * 32;
-constexpr int kBulkThreads = kThreads + 32 * kConsumerGroups;   // + one producer warp per group
+constexpr int kMaxGroups = 4;
+constexpr int kBulkThreads = kThreads + 32 * kMaxGroups;   // 20 warps in either role layout
+constexpr int kStreamGroups = 3;                  // streamed launches: 3 pipelines (15 warps) ...
+constexpr int kPushWarps = kBulkThreads / 32 - kStreamGroups * (kGroupWarps + 1);   // ... + 5 push warps
 constexpr int kMaxGroupStages = 3;
 constexpr int kChunksPerThread = 4;
 constexpr int kSegMaxBytes = 8192;                // largest row segment of one item
 constexpr size_t kBulkSmemBytes = 192 * 1024;
-constexpr size_t kGroupSmemBytes = kBulkSmemBytes / kConsumerGroups;
 
 // Segment size: as large as possible while every group still gets two stages of `fan`
 // contributor slots (one being filled while the other is reduced).
-__device__ __forceinline__ int ring_segment_bytes(int fan) {
-  const int fit = static_cast<int>(kGroupSmemBytes / (2 * static_cast<size_t>(fan))) / 512 * 512;
+__device__ __forceinline__ int ring_segment_bytes(int fan, size_t group_smem) {
+  const int fit = static_cast<int>(group_smem / (2 * static_cast<size_t>(fan))) / 512 * 512;
   return fit < kSegMaxBytes ? fit : kSegMaxBytes;
 }
-__device__ __forceinline__ int ring_stages(int fan, int segment_bytes) {
-  const int fit = static_cast<int>(kGroupSmemBytes / (static_cast<size_t>(fan) * segment_bytes));
+__device__ __forceinline__ int ring_stages(int fan, int segment_bytes, size_t group_smem) {
+  const int fit = static_cast<int>(group_smem / (static_cast<size_t>(fan) * segment_bytes));
   return fit < kMaxGroupStages ? fit : kMaxGroupStages;
 }
 
@@ -248,33 +248,51 @@ struct BulkReduceArgs {
   bool single_round;
   unsigned long long timeout_ns;
   unsigned long long* profile;
+  // streamed launches only: progress words of the peers and what this epoch's words start with
+  const RankCtx* ctx;
+  const unsigned long long* progress;
+  unsigned long long epoch_base;
 };
 
 // Barriers and item slots are indexed [group][stage]. Returns false when a bounded wait gave up.
+// Called by the first kGroups * (kGroupWarps + 1) warps of the CTA: consumers first, then one
+// producer warp per group. kStreamed: the peers are still pushing while this runs, so a
+// producer checks, before it copies a token's rows, that every remote contributor has
+// published progress beyond the row it owes (cached per peer; re-read only when short), and
+// the CTAs take items round-robin so that each of them owns tokens from every part of the
+// batch, the early ones included.
+template <int kGroups, bool kStreamed>
 __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem, unsigned long long* full_all,
                                             unsigned long long* empty_all, StageItem* items_all) {
+  constexpr int kConsumerWarps = kGroups * kGroupWarps;
+  constexpr size_t kGroupSmemBytes = kBulkSmemBytes / kGroups;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool producer = warp >= kConsumerWarps;
   const int group = producer ? warp - kConsumerWarps : warp / kGroupWarps;
-  const int seg_max = ring_segment_bytes(a.fan);
+  const int seg_max = ring_segment_bytes(a.fan, kGroupSmemBytes);
   const int rsegs = static_cast<int>((a.row_bytes + seg_max - 1) / seg_max);
   const int rseg_bytes = static_cast<int>(align_up((a.row_bytes + rsegs - 1) / rsegs, 512));
   const int items = a.tokens * rsegs;
-  const int stages = ring_stages(a.fan, seg_max);
+  const int stages = ring_stages(a.fan, seg_max, kGroupSmemBytes);
   const size_t stage_bytes = static_cast<size_t>(a.fan) * seg_max;
   char* const ring = smem + static_cast<size_t>(group) * kGroupSmemBytes;
   unsigned long long* const full = full_all + group * kMaxGroupStages;
   unsigned long long* const empty = empty_all + group * kMaxGroupStages;
   StageItem* const slots = items_all + group * kMaxGroupStages;
-  // Items of this CTA are a contiguous range (local memory only: a static split is balanced);
-  // the groups take them round-robin.
-  const int lo = static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
+  // Items of this CTA are a contiguous range (local memory only: a static split is balanced),
+  // or every gridDim.x-th item when streamed; the groups take them round-robin.
+  const int lo = kStreamed ? static_cast<int>(blockIdx.x)
+                           : static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
   const int hi = static_cast<int>(static_cast<long long>(items) * (blockIdx.x + 1) / gridDim.x);
-  const int mine = hi - lo > group ? (hi - lo - group + kConsumerGroups - 1) / kConsumerGroups : 0;
+  const int stride = kStreamed ? static_cast<int>(gridDim.x) : 1;
+  const int cta_items = kStreamed ? (items > lo ? (items - lo + stride - 1) / stride : 0)
+                                  : hi - static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
+  const int mine = cta_items > group ? (cta_items - group + kGroups - 1) / kGroups : 0;
   long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
   bool ok = true;
   if (producer) {
-    auto item_of = [&](int k) { return lo + group + k * kConsumerGroups; };
+    auto item_of = [&](int k) { return lo + (group + k * kGroups) * stride; };
+    unsigned long long seen_lo = 0, seen_hi = 0;           // progress word of peer `lane` / `lane + 32`
     // Lane L loads the mask of item L of the batch, lane 8q + j the row of contributor j of
     // item 4r + q.
     auto load_batch = [&](int base, unsigned long long& mask, int (&rows)[8]) {
@@ -321,6 +339,28 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             if (row >= 0 && !(is_self && row >= a.partial_rows))
               src = is_self ? a.partial + static_cast<long long>(row) * a.row_bytes
                             : a.staging + (static_cast<long long>(t) * a.fan + lane) * a.row_bytes;
+          }
+          if (kStreamed) {
+            // Contributor `lane` is rank d and owes row `row` of d's receive buffer.
+            const int d = lane < n ? nth_set_bit(m, lane) : 0;
+            const bool remote = src != nullptr && !is_self;
+            const unsigned long long target = a.epoch_base + static_cast<unsigned long long>(row < 0 ? 0 : row) + 1ull;
+            const unsigned long long lo_word = __shfl_sync(0xffffffffu, seen_lo, d & 31);
+            const unsigned long long hi_word = __shfl_sync(0xffffffffu, seen_hi, d & 31);
+            const bool behind = remote && (d < 32 ? lo_word : hi_word) < target;
+            if (__any_sync(0xffffffffu, behind)) {
+              bool fine = true;
+              if (behind)
+                fine = bounded_wait(*a.ctx, kPhaseCombine, 5, [&] { return ld_acquire_sys(a.progress + d) >= target; });
+              if (!__all_sync(0xffffffffu, fine)) {
+                ok = false;
+                continue;
+              }
+              const int world = a.ctx->world;
+              seen_lo = lane < world ? ld_acquire_sys(a.progress + lane) : 0ull;
+              seen_hi = lane + 32 < world ? ld_acquire_sys(a.progress + lane + 32) : 0ull;
+              fence_proxy_async();      // the rows were written by generic stores; the copies below are async-proxy reads
+            }
           }
           const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
           const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
@@ -407,7 +447,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       worked += clock64() - t1;
     }
   }
-  if (a.profile != nullptr && lane == 0 && (warp == 0 || warp == kConsumerWarps)) {
+  if (a.profile != nullptr && lane == 0 && (warp == 0 || warp == kConsumerWarps)) {   // group 0
     unsigned long long* slot = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps + (warp == 0 ? 4 : 6);
     slot[0] = static_cast<unsigned long long>(waited);
     slot[1] = static_cast<unsigned long long>(worked);
@@ -415,8 +455,123 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   return ok;
 }
 
-template <bool kVec16, bool kBulk>
+// ---- push phase -----------------------------------------------------------------------------
+// Received rows are grouped by source rank. Pushing them in storage order would make every
+// rank write to rank 0 first, then rank 1, ... (incast: one ingress port saturated, the rest
+// idle). Work items (row, row segment) therefore interleave the peers in blocks of kPushBlock
+// rows, starting with the rank after this one, so that at any moment each rank spreads its
+// stores over all peers and each peer receives from all ranks.
+constexpr int kPushBlock = 8;
+
+struct PushArgs {
+  const int* rows_from;     // [W] rows received from each rank
+  const int* first_row;     // [W] first row of each rank in the receive buffer
+  char* const* stage;       // [W] staging plane of each rank
+  const char* partial;
+  const int* ret;
+  long long row_bytes;
+  long long seg_bytes;
+  int segs;
+  long long chunk_bytes;    // streamed push: progress is published about this often
+  int most;                 // most rows received from one peer
+  int valid;
+  int self;
+  int world;
+};
+
+template <int kWords, int kUnroll>
+__device__ __forceinline__ void push_item(const PushArgs& p, long long item, int lane) {
+  constexpr int kChunk = kWords * 4;
+  const int peers = p.world - 1;
+  const int seg = static_cast<int>(item % p.segs);
+  const long long q = item / p.segs;
+  const int in_block = static_cast<int>(q % kPushBlock);
+  const long long q2 = q / kPushBlock;
+  const int source = (p.self + 1 + static_cast<int>(q2 % peers)) % p.world;
+  const long long from_source = (q2 / peers) * kPushBlock + in_block;
+  if (from_source >= p.rows_from[source]) return;
+  const long long row = p.first_row[source] + from_source;
+  if (row >= p.valid) return;
+  const long long back = p.ret[row];
+  const char* src = p.partial + row * p.row_bytes;
+  char* dst = p.stage[source] + back * p.row_bytes;
+  const long long b0 = seg * p.seg_bytes;
+  const long long b1 = min(p.row_bytes, b0 + p.seg_bytes);
+  for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
+    Chunk<kWords> v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long off = base + static_cast<long long>(u) * 32 * kChunk;
+      if (off < b1) v[u] = load_local_chunk<kWords>(src + off);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long off = base + static_cast<long long>(u) * 32 * kChunk;
+      if (off < b1) store_chunk<kWords>(dst + off, v[u]);
+    }
+  }
+}
+
+// Streamed push, run by the kPushWarps last warps of every CTA while the other warps already
+// reduce. The item order is cut into up to kMaxPushChunks chunks of whole blocks. A warp
+// whose next claimed item lies beyond chunk c will never store into c again: it fences its
+// stores system-wide and counts itself out of c. The warp that completes the count publishes,
+// to every peer, how many of that peer's rows have now certainly arrived (as a row index in
+// this rank's receive buffer, the coordinate the peer recorded at dispatch), with a max
+// update so that a delayed publication can never take progress back.
+template <int kWords>
+__device__ __forceinline__ void push_streamed(const PushArgs& p, const RankCtx& c, CtrlHeader* hdr, size_t ready_offset,
+                                              unsigned epoch, int lane) {
+  const int peers = p.world - 1;
+  const long long blocks = peers > 0 ? (p.most + kPushBlock - 1) / kPushBlock : 0;
+  const long long per_block = static_cast<long long>(peers) * kPushBlock * p.segs;
+  const long long items = blocks * per_block;
+  long long wanted = blocks * kPushBlock * peers * p.row_bytes / (p.chunk_bytes > 0 ? p.chunk_bytes : 1);
+  if (wanted > kMaxPushChunks) wanted = kMaxPushChunks;
+  if (wanted > blocks) wanted = blocks;
+  const int chunks = wanted < 1 ? 1 : static_cast<int>(wanted);
+  const unsigned everyone = gridDim.x * static_cast<unsigned>(kPushWarps);
+  int current = 0;                                     // chunk this warp may still store into
+  unsigned next_claim = lane == 0 ? atomicAdd(&hdr->cwork_push, 1u) : 0u;
+  while (true) {
+    const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
+    int item_chunk = chunks;
+    if (item < items) {
+      const long long block = item / per_block;
+      item_chunk = current;
+      while (item_chunk + 1 < chunks && blocks * (item_chunk + 1) / chunks <= block) ++item_chunk;
+    }
+    while (current < item_chunk) {                     // leave chunk `current` behind
+      __syncwarp();
+      unsigned before = 0;
+      if (lane == 0) {
+        __threadfence_system();                        // this warp's stores are performed system-wide
+        before = atomicAdd(&hdr->cpush_done[current], 1u);
+        if (before == everyone - 1) __threadfence();   // acquire side of the count
+      }
+      before = __shfl_sync(0xffffffffu, before, 0);
+      if (before == everyone - 1) {
+        const long long pushed = blocks * (current + 1) / chunks * kPushBlock;   // rows per peer, at least
+        for (int d = lane; d < p.world; d += 32) {
+          if (d == p.self) continue;
+          const long long rows = p.rows_from[d] < pushed ? p.rows_from[d] : pushed;
+          const unsigned long long progress = current == chunks - 1
+              ? 0xffffffffull : static_cast<unsigned long long>(p.first_row[d] + rows);
+          unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[d] + ready_offset) + p.self;
+          red_max_release_sys(word, (static_cast<unsigned long long>(epoch) << 32) | progress);
+        }
+      }
+      ++current;
+    }
+    if (item >= items) break;
+    if (lane == 0) next_claim = atomicAdd(&hdr->cwork_push, 1u);   // in flight while this item is copied
+    push_item<kWords, 8>(p, item, lane);
+  }
+}
+
+template <bool kVec16, bool kBulk, bool kStreamed>
 __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_smem) {
+  static_assert(kBulk || !kStreamed, "streaming needs the bulk-copy reduce");
   constexpr int kWords = kVec16 ? 4 : 1;
   constexpr int kChunk = kWords * 4;
   constexpr int kUnroll = 4;
@@ -441,10 +596,17 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
 
   __shared__ char* s_stage[64];
   __shared__ int s_need[64];
+  __shared__ int s_rows_from[64], s_first_row[64];
+  __shared__ int s_most;
   __shared__ int s_last;
+  __shared__ unsigned long long s_full[kMaxGroups * kMaxGroupStages], s_empty[kMaxGroups * kMaxGroupStages];
+  __shared__ StageItem s_items[kMaxGroups * kMaxGroupStages];
 
   profile_stamp(op.profile, 0);
   const unsigned e = ld_volatile_u32(&hdr->comb_epoch) + 1;
+  // Progress words carry (epoch << 32 | rows pushed); "everything" is the largest row count.
+  const unsigned long long epoch_base = static_cast<unsigned long long>(e) << 32;
+  const unsigned long long all_pushed = epoch_base | 0xffffffffull;
   if (tid < W) {
     const unsigned long long off = reinterpret_cast<const unsigned long long*>(slot + sl.peer_off)[tid];
     const int cap = reinterpret_cast<const int*>(slot + sl.peer_cap)[tid];
@@ -452,33 +614,58 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     s_stage[tid] = c.heap[tid] + off + pl.staging;
     s_need[tid] = (tid != self && reinterpret_cast<const int*>(slot + sl.send_cnt)[tid] > 0) ? 1 : 0;
   }
+  if (tid == 64) {
+    int at = 0, most = 0;
+    for (int r = 0; r < W; ++r) {
+      const int count = reinterpret_cast<const int*>(slot + sl.recv_cnt)[r];
+      s_first_row[r] = at;
+      s_rows_from[r] = count;
+      at += count;
+      if (r != self && count > most) most = count;
+    }
+    s_most = most;
+  }
+  if (kBulk) {
+    if (tid < kMaxGroups * kMaxGroupStages) {
+      mbarrier_init(s_full + tid, 1);
+      mbarrier_init(s_empty + tid, kGroupWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
   const int valid = min(misc[kValidCount], op.partial_rows);
   const int segs = op.segments;
   const long long seg_bytes = align_up((row_bytes + segs - 1) / segs, 32 * kChunk * kUnroll);
   __syncthreads();
 
-  // ---- A. push my rows to the ranks that own the tokens ---------------------------
-  // Received rows are grouped by source rank. Pushing them in storage order would make every
-  // rank write to rank 0 first, then rank 1, ... (incast: one ingress port saturated, the
-  // rest idle). Items therefore interleave the peers in blocks of kPushBlock rows, starting
-  // with the rank after this one, so that at any moment each rank spreads its stores over
-  // all peers and each peer receives from all ranks.
-  {
-    constexpr int kPushBlock = 8;
-    __shared__ int s_rows_from[64], s_first_row[64];
-    __shared__ int s_most;
-    if (tid == 0) {
-      int at = 0, most = 0;
-      for (int r = 0; r < W; ++r) {
-        const int count = reinterpret_cast<const int*>(slot + sl.recv_cnt)[r];
-        s_first_row[r] = at;
-        s_rows_from[r] = count;
-        at += count;
-        if (r != self && count > most) most = count;
-      }
-      s_most = most;
+  PushArgs push;
+  push.rows_from = s_rows_from; push.first_row = s_first_row; push.stage = s_stage;
+  push.partial = partial; push.ret = ret; push.row_bytes = row_bytes; push.seg_bytes = seg_bytes;
+  push.chunk_bytes = op.push_chunk_bytes; push.segs = segs; push.most = s_most; push.valid = valid; push.self = self; push.world = W;
+  BulkReduceArgs reduce;
+  reduce.mask_arr = mask_arr; reduce.send_rows = send_rows; reduce.partial = partial; reduce.staging = staging;
+  reduce.out = reinterpret_cast<char*>(op.out); reduce.row_bytes = row_bytes;
+  reduce.tokens = T; reduce.fan = fan; reduce.self = self; reduce.partial_rows = op.partial_rows;
+  reduce.single_round = single_round; reduce.timeout_ns = c.timeout_ns; reduce.profile = op.profile;
+  reduce.ctx = &c;
+  reduce.progress = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready);
+  reduce.epoch_base = epoch_base;
+
+  if (kStreamed) {
+    // ---- push and reduce side by side ----------------------------------------------------
+    constexpr int kReduceWarps = kStreamGroups * (kGroupWarps + 1);
+    if ((tid >> 5) >= kReduceWarps) {
+      push_streamed<kWords>(push, c, hdr, cl.ready, e, lane);
+      if (op.profile != nullptr && tid == kReduceWarps * 32)
+        op.profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + 1] = global_timer_ns();
+    } else {
+      profile_stamp(op.profile, 2);
+      if (!bulk_reduce<kStreamGroups, true>(reduce, dynamic_smem, s_full, s_empty, s_items))
+        report_error(c, kTimeout, kPhaseCombine, 4, 0);
     }
-    __syncthreads();
+  } else {
+  // ---- A. push my rows to the ranks that own the tokens ---------------------------
+  {
     const int peers = W - 1;
     const long long blocks = (s_most + kPushBlock - 1) / kPushBlock;
     const long long items = peers > 0 ? blocks * peers * kPushBlock * segs : 0;
@@ -487,33 +674,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
       if (item >= items) break;
       if (lane == 0) next_claim = atomicAdd(&hdr->cwork_push, 1u);   // in flight while this item is copied
-      const int seg = static_cast<int>(item % segs);
-      const long long q = item / segs;
-      const int in_block = static_cast<int>(q % kPushBlock);
-      const long long q2 = q / kPushBlock;
-      const int source = (self + 1 + static_cast<int>(q2 % peers)) % W;
-      const long long from_source = (q2 / peers) * kPushBlock + in_block;
-      if (from_source >= s_rows_from[source]) continue;
-      const long long row = s_first_row[source] + from_source;
-      if (row >= valid) continue;
-      const long long back = ret[row];
-      const char* src = partial + row * row_bytes;
-      char* dst = s_stage[source] + back * row_bytes;
-      const long long b0 = seg * seg_bytes;
-      const long long b1 = min(row_bytes, b0 + seg_bytes);
-      for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
-        Chunk<kWords> v[kUnroll];
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-          const long long off = base + static_cast<long long>(u) * 32 * kChunk;
-          if (off < b1) v[u] = load_local_chunk<kWords>(src + off);
-        }
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-          const long long off = base + static_cast<long long>(u) * 32 * kChunk;
-          if (off < b1) store_chunk<kWords>(dst + off, v[u]);
-        }
-      }
+      push_item<kWords, kUnroll>(push, item, lane);
     }
   }
   __syncthreads();
@@ -524,39 +685,28 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     __threadfence_system();   // this CTA's peer stores are performed system-wide before it arrives
     const unsigned prev = atomicAdd(&hdr->cdone_count, 1u);
     s_last = (prev == gridDim.x - 1) ? 1 : 0;
-    if (s_last) __threadfence();   // acquire side of the arrival counter; the flag store below releases at sys scope
+    if (s_last) __threadfence();   // acquire side of the arrival counter; the update below releases at sys scope
   }
   __syncthreads();
   if (s_last && tid < W && tid != self) {
-    unsigned long long* flag = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.ready) + self;
-    st_release_sys(flag, static_cast<unsigned long long>(e));
+    unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.ready) + self;
+    red_max_release_sys(word, all_pushed);
   }
 
   // ---- C. wait for the peers that push to me ----------------------------------------------
   bool ok = true;
   if (tid < W && s_need[tid]) {
-    const unsigned long long* flag = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready) + tid;
-    ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(flag) >= e; });
+    const unsigned long long* word = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready) + tid;
+    ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(word) >= all_pushed; });
   }
   if (!__syncthreads_and(ok)) return;
   profile_stamp(op.profile, 2);
 
   // ---- D. rank-order reduce from local memory -----------------------------------------------
   if (kBulk) {
-    __shared__ unsigned long long s_full[kConsumerGroups * kMaxGroupStages], s_empty[kConsumerGroups * kMaxGroupStages];
-    __shared__ StageItem s_items[kConsumerGroups * kMaxGroupStages];
-    if (tid < kConsumerGroups * kMaxGroupStages) {
-      mbarrier_init(s_full + tid, 1);
-      mbarrier_init(s_empty + tid, kGroupWarps);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    fence_proxy_async();
-    __syncthreads();
-    BulkReduceArgs a;
-    a.mask_arr = mask_arr; a.send_rows = send_rows; a.partial = partial; a.staging = staging;
-    a.out = reinterpret_cast<char*>(op.out); a.row_bytes = row_bytes;
-    a.tokens = T; a.fan = fan; a.self = self; a.partial_rows = op.partial_rows; a.single_round = single_round; a.timeout_ns = c.timeout_ns; a.profile = op.profile;
-    if (!bulk_reduce(a, dynamic_smem, s_full, s_empty, s_items)) report_error(c, kTimeout, kPhaseCombine, 4, 0);
+    fence_proxy_async();      // the rows were written by generic stores; the reduce reads them through the async proxy
+    if (!bulk_reduce<kMaxGroups, false>(reduce, dynamic_smem, s_full, s_empty, s_items))
+      report_error(c, kTimeout, kPhaseCombine, 4, 0);
   } else {
     const long long items = static_cast<long long>(T) * segs;
     while (true) {
@@ -622,6 +772,8 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     }
   }
 
+  }   // !kStreamed
+
   // ---- E. retire the epoch ---------------------------------------------------------------
   __syncthreads();
   profile_stamp(op.profile, 3);
@@ -632,17 +784,18 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       hdr->cfin_count = 0;
       hdr->cwork_push = 0;
       hdr->cwork_reduce = 0;
+      for (int chunk = 0; chunk < kMaxPushChunks; ++chunk) hdr->cpush_done[chunk] = 0;
       hdr->comb_epoch = e;
       __threadfence();
     }
   }
 }
 
-template <bool kVec16, bool kBulk>
+template <bool kVec16, bool kBulk, bool kStreamed>
 __global__ void __launch_bounds__(kBulk ? kBulkThreads : kThreads, 1)
 combine_kernel(const __grid_constant__ CombineArgs args) {
   extern __shared__ __align__(128) char combine_smem[];
-  combine_body<kVec16, kBulk>(args.op[blockIdx.y], combine_smem);
+  combine_body<kVec16, kBulk, kStreamed>(args.op[blockIdx.y], combine_smem);
 }
 
 struct CombineVariant {
@@ -651,15 +804,21 @@ struct CombineVariant {
   size_t dynamic_smem;
 };
 
-// The bulk-copy reduce needs 16-byte rows and at most kPeerBatch contributors per token.
-cudaError_t pick_combine(bool vec16, int fanout, CombineVariant* out) {
+// The bulk-copy reduce needs 16-byte rows and at most kPeerBatch contributors per token;
+// streaming (push and reduce side by side) exists for the bulk-copy reduce only.
+cudaError_t pick_combine(bool vec16, int fanout, bool streamed, CombineVariant* out) {
   if (vec16 && fanout <= kPeerBatch) {
-    *out = {reinterpret_cast<const void*>(combine_kernel<true, true>), kBulkThreads, kBulkSmemBytes};
-    return cudaFuncSetAttribute(combine_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (streamed) {
+      *out = {reinterpret_cast<const void*>(combine_kernel<true, true, true>), kBulkThreads, kBulkSmemBytes};
+      return cudaFuncSetAttribute(combine_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(kBulkSmemBytes));
+    }
+    *out = {reinterpret_cast<const void*>(combine_kernel<true, true, false>), kBulkThreads, kBulkSmemBytes};
+    return cudaFuncSetAttribute(combine_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(kBulkSmemBytes));
   }
-  if (vec16) *out = {reinterpret_cast<const void*>(combine_kernel<true, false>), kThreads, 0};
-  else *out = {reinterpret_cast<const void*>(combine_kernel<false, false>), kThreads, 0};
+  if (vec16) *out = {reinterpret_cast<const void*>(combine_kernel<true, false, false>), kThreads, 0};
+  else *out = {reinterpret_cast<const void*>(combine_kernel<false, false, false>), kThreads, 0};
   return cudaSuccess;
 }
 
@@ -671,20 +830,26 @@ cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas) {
   if (err != cudaSuccess) return err;
   err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (err != cudaSuccess) return err;
-  CombineVariant variant;
-  err = pick_combine(vec16, fanout, &variant);
-  if (err != cudaSuccess) return err;
-  err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, variant.kernel, variant.threads, variant.dynamic_smem);
-  if (err != cudaSuccess) return err;
-  *ctas = per_sm * sms;
+  int fewest = 1 << 30;
+  for (int streamed = 0; streamed < 2; ++streamed) {
+    CombineVariant variant;
+    err = pick_combine(vec16, fanout, streamed != 0, &variant);
+    if (err != cudaSuccess) return err;
+    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, variant.kernel, variant.threads, variant.dynamic_smem);
+    if (err != cudaSuccess) return err;
+    if (per_sm < fewest) fewest = per_sm;
+  }
+  *ctas = fewest * sms;
   return cudaSuccess;
 }
 
+bool combine_can_stream(bool vec16, int fanout) { return vec16 && fanout <= kPeerBatch; }
+
 cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout,
-                           bool cooperative, cudaStream_t stream) {
+                           bool streamed, bool cooperative, cudaStream_t stream) {
   void* params[] = {const_cast<CombineArgs*>(&args)};
   CombineVariant variant;
-  cudaError_t err = pick_combine(vec16, fanout, &variant);
+  cudaError_t err = pick_combine(vec16, fanout, streamed && combine_can_stream(vec16, fanout), &variant);
   if (err != cudaSuccess) return err;
   const dim3 grid(ctas_per_rank, ranks, 1), block(variant.threads, 1, 1);
   if (!cooperative) return cudaLaunchKernel(variant.kernel, grid, block, params, variant.dynamic_smem, stream);

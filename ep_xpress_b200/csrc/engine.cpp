@@ -97,6 +97,12 @@ class Engine {
     if (tables_ != nullptr) cudaFree(tables_);
   }
 
+  // -1: stream the combine push when the batch is large (default); 0: never; 1: whenever possible.
+  // `chunk_bytes`: how much a rank pushes between two progress publications (0 keeps the value).
+  void set_combine_streaming(int mode, int64_t chunk_bytes) {
+    streaming_ = mode;
+    if (chunk_bytes > 0) push_chunk_bytes_ = chunk_bytes;
+  }
   int sm_count() const { return sms_; }
   std::vector<int> experts_per_rank() const { return experts_per_rank_; }
   size_t ctrl_bytes() const { return ctrl_layout(world_).bytes; }
@@ -265,9 +271,13 @@ class Engine {
     for (size_t i = 0; i < n; ++i) {
       args.op[i].segments = segments;
       args.op[i].vec16 = vec16 ? 1 : 0;
+      args.op[i].push_chunk_bytes = push_chunk_bytes_;
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
-    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, route_fanout(topk_, world_), cooperative_,
+    const int fanout = route_fanout(topk_, world_);
+    const int64_t pushed_bytes = max_tokens * fanout * static_cast<int64_t>(hidden_) * 2;
+    const bool streamed = world_ > 1 && (streaming_ > 0 || (streaming_ < 0 && pushed_bytes >= kStreamingBytes));
+    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, fanout, streamed, cooperative_,
                               stream_of(stream)), "combine launch");
   }
 
@@ -365,6 +375,9 @@ class Engine {
   std::vector<int> local_ranks_;
   int hidden_, topk_, device_;
   bool cooperative_ = true;
+  int streaming_ = -1;
+  int64_t push_chunk_bytes_ = 16ll << 20;
+  static constexpr int64_t kStreamingBytes = 32ll << 20;
   int sms_ = 0;
   std::vector<int> experts_per_rank_;
   std::vector<char*> own_heap_;
@@ -399,6 +412,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("heaps"), py::arg("timeout_seconds"), py::arg("single_round"), py::arg("device"),
            py::arg("cooperative") = true)
       .def("sm_count", &Engine::sm_count)
+      .def("set_combine_streaming", &Engine::set_combine_streaming, py::arg("mode"), py::arg("chunk_bytes") = 0)
       .def("experts_per_rank", &Engine::experts_per_rank)
       .def("ctrl_bytes", &Engine::ctrl_bytes)
       .def("ctrl_offsets", &Engine::ctrl_offsets)

@@ -25,6 +25,10 @@ __device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long
 __device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// Monotone publication: the word only ever grows, whichever writer's update lands last.
+__device__ __forceinline__ void red_max_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.sys.global.max.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }

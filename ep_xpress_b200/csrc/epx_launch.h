@@ -22,8 +22,14 @@ cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas);
 // other kernel holding the SMs forever).
 cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
                             size_t dynamic_smem, bool cooperative, cudaStream_t stream);
+// `streamed`: push and reduce run side by side in every CTA (a few warps push while the others
+// already reduce the tokens whose rows have arrived) instead of one after the other. Worth it
+// when the pushed volume is many megabytes; it is ignored where the bulk-copy reduce does not
+// apply (`combine_can_stream`). Every rank may choose on its own: the progress words that
+// peers exchange are the same in both modes.
+bool combine_can_stream(bool vec16, int fanout);
 cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout,
-                           bool cooperative, cudaStream_t stream);
+                           bool streamed, bool cooperative, cudaStream_t stream);
 
 // Synthetic expert used by the validation harness and the communication
 // benchmark: partial[row] = bf16(hidden[row] * sum_k weights[row,k] * factor[local_ids[row,k]])

@@ -62,15 +62,17 @@ struct CtrlHeader {
   unsigned cwork_push;      // combine: next unclaimed (row, segment) item of the push phase
   unsigned cwork_reduce;    // combine: next unclaimed (token, segment) item of the reduce phase
   unsigned reserved0;
-  unsigned long long reserved[25];
+  unsigned cpush_done[8];   // combine, streamed push: push warps that left chunk c behind them
+  unsigned long long reserved[21];
 };
+constexpr int kMaxPushChunks = 8;
 static_assert(sizeof(CtrlHeader) == 256, "control header is one 256-byte block");
 
 struct CtrlLayout {
   size_t cnt;    // u64 [2][W][W]  counts row of every source, by generation parity
   size_t addr;   // u64 [2][W][4]  (slot offset >> 8, slot capacity, row bound, -) of every peer
   size_t done;   // u64 [2][W]     "all my rows for you are stored"
-  size_t ready;  // u64 [W]        combine: "my partial plane is readable" (monotone)
+  size_t ready;  // u64 [W]        combine: (epoch << 32 | rows of yours I have pushed), monotone, max-updated
   size_t ident;  // u64 [2][W]     diagnostics: operation identity of every peer
   size_t perr;   // u32 [W]        error code published by a failing peer
   size_t bytes;  // size of the whole control region
@@ -197,6 +199,7 @@ struct CombineOp {
   int segments;
   int vec16;
   int partial_rows;       // rows of `partial`; rows at or above it are not pushed
+  long long push_chunk_bytes;  // streamed launches: bytes pushed between two progress publications
 };
 
 struct DispatchArgs { DispatchOp op[kMaxEmulatedRanks]; };

@@ -104,6 +104,7 @@ class TransportCore:
                                     [list(map(int, row)) for row in heaps], float(config.timeout_seconds),
                                     config.combine_rounding == "single", self.device.index,
                                     bool(config.cooperative_launch))
+        self.engine.set_combine_streaming({"auto": -1, "off": 0, "on": 1}[config.combine_streaming])
         ctrl = self.engine.ctrl_bytes()
         self._allocators = [HeapAllocator(ctrl, heap_bytes) for _ in self.local_ranks]
         self.max_ctas = max(1, min(self.engine.max_ctas(config.max_tokens_per_rank), self.engine.sm_count()))

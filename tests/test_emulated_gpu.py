@@ -154,3 +154,59 @@ def test_invalid_routes_are_reported():
             statuses = group.status()
             assert statuses[0][0] == 1
             assert statuses[1][0] in (0, 4)
+
+
+@pytest.mark.parametrize("world,hidden,topk,tokens,chunk_bytes,ctas", [
+    (2, 256, 2, 64, 0, None),            # one chunk: everything is published at the end
+    (4, 2048, 4, 700, 64 << 10, None),   # eight chunks, several row segments
+    (8, 1024, 8, 300, 32 << 10, 12),     # full fan-out, few CTAs per rank
+    (3, 64, 4, 600, 4 << 10, 5),         # tiny rows, more tokens than one route tile
+    (4, 264, 4, 33, 1 << 10, None),      # rows that are not 16-byte multiples: the register path runs instead
+])
+def test_streamed_combine_matches_the_oracle(world, hidden, topk, tokens, chunk_bytes, ctas):
+    """Push and reduce side by side: progress words gate each token, results stay bit-exact."""
+    experts = world * 4
+    cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=2.0,
+                 combine_streaming="on")
+    emap = workloads.round_robin_expert_map(experts, world)
+    with EmulatedGroup(world, emap, cfg) as group:
+        group.core.engine.set_combine_streaming(1, chunk_bytes)
+        slot = group.create_slot()
+        for seed in range(4):
+            xs, ids, ws = [], [], []
+            for rank in range(world):
+                n = tokens if seed != 1 else max(tokens - 7 * rank, 0)          # uneven batches, one empty-ish
+                i, w = (workloads.zipf_routing if seed == 3 else workloads.uniform_routing)(
+                    n, experts, topk, seed=seed, rank=rank)
+                xs.append(workloads.gaussian_payload(n, hidden, seed=seed, rank=rank))
+                ids.append(i)
+                ws.append(w)
+            run_round(group, slot, xs, ids, ws, emap, direct_partial=(seed != 2), ctas=ctas,
+                      rounding="two_step")
+
+
+def test_streamed_and_sequential_combine_agree_across_slots():
+    """Two outstanding handles combined in reverse order, one mode per slot use."""
+    world, hidden, topk, tokens = 4, 512, 4, 96
+    experts = world * 2
+    cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=2.0)
+    emap = workloads.contiguous_expert_map(experts, world)
+    with EmulatedGroup(world, emap, cfg) as group:
+        dev = group.device
+        slots = [group.create_slot(), group.create_slot()]
+        outs = {}
+        for mode in (1, 0):
+            group.core.engine.set_combine_streaming(mode, 16 << 10)
+            batches = []
+            for index, slot in enumerate(slots):
+                xs = [workloads.gaussian_payload(tokens, hidden, seed=index, rank=r).to(dev) for r in range(world)]
+                routes = [workloads.uniform_routing(tokens, experts, topk, seed=index, rank=r) for r in range(world)]
+                batch = group.dispatch(slot, xs, [i.to(dev) for i, _ in routes], [w.to(dev) for _, w in routes])
+                batches.append([group.scale_rows(b) for b in batch])
+            for index in (1, 0):                                     # reverse order
+                result = group.combine(slots[index], batches[index], [tokens] * world)
+                outs[(mode, index)] = [o.clone() for o in result]
+            assert all(status[0] == 0 for status in group.status())
+        for index in (0, 1):
+            for rank in range(world):
+                assert torch.equal(bits(outs[(1, index)][rank]), bits(outs[(0, index)][rank]))
