@@ -62,6 +62,8 @@ def parse_args():
     parser.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     parser.add_argument("--routing", choices=("uniform", "zipf"), default="uniform")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--combine-streaming", choices=("auto", "on", "off"), default="auto",
+                        help="ours: reduce while peers still push (auto: large batches only)")
     parser.add_argument("--cpu-numa", choices=("auto", "off"), default="auto",
                         help="auto: run on the CPUs of the GPU's NUMA node before pinned memory is allocated")
     parser.add_argument("--graph", choices=("auto", "on", "off"), default="auto",
@@ -110,7 +112,7 @@ def make_inputs(shape, tokens, world, rank, routing, sets):
 class OursArm:
     name = "ours"
 
-    def __init__(self, shape, tokens, world, rank, local, plain_launch=False):
+    def __init__(self, shape, tokens, world, rank, local, plain_launch=False, combine_streaming="auto"):
         import torch.distributed as dist
         from ep_xpress_b200 import Config, Context, get_nccl_comm_handle
         from ep_xpress_b200.models import IdentityMoELayer
@@ -118,8 +120,11 @@ class OursArm:
         self.comm = get_nccl_comm_handle(dist.group.WORLD)
         cfg = Config(hidden_size=shape["hidden"], topk=shape["topk"], max_tokens_per_rank=tokens,
                      timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30,
-                     cooperative_launch=not plain_launch)
+                     cooperative_launch=not plain_launch, combine_streaming=combine_streaming)
         self.context = Context(self.comm, workloads.contiguous_expert_map(shape["experts"], world), cfg)
+        if os.environ.get("EPX_PUSH_CHUNK_BYTES"):
+            self.context._core.engine.set_combine_streaming({"auto": -1, "off": 0, "on": 1}[combine_streaming],
+                                                            int(os.environ["EPX_PUSH_CHUNK_BYTES"]))
         self.layer = IdentityMoELayer(self.context)
 
     def enable_graph(self, example):
@@ -185,7 +190,7 @@ class ReferenceArm:
     """The reference's own library and stock code path; nothing of this repository's runtime."""
     name = "reference"
 
-    def __init__(self, shape, tokens, world, rank, local, plain_launch=False):
+    def __init__(self, shape, tokens, world, rank, local, plain_launch=False, combine_streaming="auto"):
         import torch
         import torch.distributed as dist
         os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
@@ -266,7 +271,8 @@ def run(args):
         placement = numa.bind_to_device(local)
     host = make_inputs(shape, tokens, world, rank, args.routing, sets)
     device = [tuple(t.cuda(non_blocking=True) for t in batch) for batch in host]
-    arm = (OursArm if args.impl == "ours" else ReferenceArm)(shape, tokens, world, rank, local, args.plain_launch)
+    arm = (OursArm if args.impl == "ours" else ReferenceArm)(shape, tokens, world, rank, local, args.plain_launch,
+                                                                      args.combine_streaming)
     use_graph = args.impl == "ours" and (args.graph == "on" or (args.graph == "auto" and args.config == "decode"))
     if use_graph:
         arm.enable_graph(device[0])

@@ -47,6 +47,7 @@ def parse_args():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--samples", type=int, default=20)
     parser.add_argument("--nccl-reference", action="store_true")
+    parser.add_argument("--combine-streaming", choices=("auto", "on", "off"), default="auto")
     parser.add_argument("--items-per-cta", type=int, default=None, help="launch-width policy (see set_tuning)")
     parser.add_argument("--max-ctas", type=int, default=None, help="cap on CTAs per operation")
     parser.add_argument("--report", default=None, help="write the JSON report here (rank 0)")
@@ -197,6 +198,7 @@ def main():
     owner = torch.tensor(emap)
     cfg = Config(hidden_size=shape["hidden"], topk=shape["topk"], max_tokens_per_rank=max(args.tokens),
                  timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30, slots=1,
+                 combine_streaming=args.combine_streaming,
                  workspace_pool_bytes=2 * Config(hidden_size=shape["hidden"], topk=shape["topk"],
                                                  max_tokens_per_rank=max(args.tokens)).nvlink_slot_bytes(world))
     ep = Context(get_nccl_comm_handle(dist.group.WORLD), emap, cfg)
@@ -204,7 +206,7 @@ def main():
     if args.items_per_cta is not None or args.max_ctas is not None:
         ep.set_tuning(items_per_cta=args.items_per_cta, max_ctas=args.max_ctas)
     report = {"schema": 1, "world_size": world, "shape": args.shape, **shape, "routing": args.routing,
-              "warmup": args.warmup, "samples": args.samples, "timing": "CUDA events, max over ranks per sample",
+              "combine_streaming": args.combine_streaming, "warmup": args.warmup, "samples": args.samples, "timing": "CUDA events, max over ranks per sample",
               "link_gbs_measured": LINK_GBS_MEASURED, "results": []}
     for tokens in args.tokens:
         report["results"].append(run_tokens(ep, args, shape, tokens, rank, world, owner))

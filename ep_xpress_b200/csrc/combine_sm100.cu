@@ -289,6 +289,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
                                   : hi - static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
   const int mine = cta_items > group ? (cta_items - group + kGroups - 1) / kGroups : 0;
   long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
+  unsigned long long t_first = 0, t_half = 0;   // TEMP
   bool ok = true;
   if (producer) {
     auto item_of = [&](int k) { return lo + (group + k * kGroups) * stride; };
@@ -361,6 +362,11 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
               seen_hi = lane + 32 < world ? ld_acquire_sys(a.progress + lane + 32) : 0ull;
               fence_proxy_async();      // the rows were written by generic stores; the copies below are async-proxy reads
             }
+          }
+          if (kStreamed && a.profile != nullptr && group == 0 && lane == 0) {   // TEMP instrumentation
+            unsigned long long* st = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps;
+            if (base + i == 0) t_first = global_timer_ns() - st[0];
+            if (base + i == mine / 2) t_half = global_timer_ns() - st[0];
           }
           const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
           const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
@@ -451,6 +457,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
     unsigned long long* slot = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps + (warp == 0 ? 4 : 6);
     slot[0] = static_cast<unsigned long long>(waited);
     slot[1] = static_cast<unsigned long long>(worked);
+    if (kStreamed && warp != 0) { slot[0] = t_first; slot[1] = t_half; }   // TEMP
   }
   return ok;
 }
@@ -512,60 +519,93 @@ __device__ __forceinline__ void push_item(const PushArgs& p, long long item, int
   }
 }
 
-// Streamed push, run by the kPushWarps last warps of every CTA while the other warps already
-// reduce. The item order is cut into up to kMaxPushChunks chunks of whole blocks. A warp
-// whose next claimed item lies beyond chunk c will never store into c again: it fences its
-// stores system-wide and counts itself out of c. The warp that completes the count publishes,
-// to every peer, how many of that peer's rows have now certainly arrived (as a row index in
-// this rank's receive buffer, the coordinate the peer recorded at dispatch), with a max
-// update so that a delayed publication can never take progress back.
-template <int kWords>
-__device__ __forceinline__ void push_streamed(const PushArgs& p, const RankCtx& c, CtrlHeader* hdr, size_t ready_offset,
-                                              unsigned epoch, int lane) {
+// ---- streamed push ------------------------------------------------------------------------------
+// Run by the last kPushWarps warps of every CTA while the other warps already reduce. The item
+// order is cut into up to kMaxPushChunks chunks of whole blocks, and after each chunk the rank
+// tells every peer how many of that peer's rows have certainly arrived (as a row index in this
+// rank's receive buffer, the coordinate the peer recorded at dispatch).
+//
+// "Certainly arrived" needs a system-scope fence behind the stores, and under a saturated link
+// such a fence takes tens of microseconds (the posted writes queued ahead of it have to drain).
+// The warps that store therefore never fence: a warp whose next claimed item lies beyond chunk
+// c only counts itself out of c in shared memory. The CTA's herald warp waits for that count,
+// runs the fence (cumulative over the stores it has observed through the count), counts the CTA
+// out of the chunk in the rank's header, and the herald of the last CTA publishes - with a max
+// update, so that a delayed publication can never take progress back.
+struct PushPlan {
+  long long blocks;      // blocks of kPushBlock rows per peer
+  long long per_block;   // work items of one block over all peers
+  long long items;
+  int chunks;
+};
+
+__device__ __forceinline__ PushPlan plan_push(const PushArgs& p) {
+  PushPlan plan;
   const int peers = p.world - 1;
-  const long long blocks = peers > 0 ? (p.most + kPushBlock - 1) / kPushBlock : 0;
-  const long long per_block = static_cast<long long>(peers) * kPushBlock * p.segs;
-  const long long items = blocks * per_block;
-  long long wanted = blocks * kPushBlock * peers * p.row_bytes / (p.chunk_bytes > 0 ? p.chunk_bytes : 1);
+  plan.blocks = peers > 0 ? (p.most + kPushBlock - 1) / kPushBlock : 0;
+  plan.per_block = static_cast<long long>(peers) * kPushBlock * p.segs;
+  plan.items = plan.blocks * plan.per_block;
+  long long wanted = plan.blocks * kPushBlock * peers * p.row_bytes / (p.chunk_bytes > 0 ? p.chunk_bytes : 1);
   if (wanted > kMaxPushChunks) wanted = kMaxPushChunks;
-  if (wanted > blocks) wanted = blocks;
-  const int chunks = wanted < 1 ? 1 : static_cast<int>(wanted);
-  const unsigned everyone = gridDim.x * static_cast<unsigned>(kPushWarps);
+  if (wanted > plan.blocks) wanted = plan.blocks;
+  plan.chunks = wanted < 1 ? 1 : static_cast<int>(wanted);
+  return plan;
+}
+
+template <int kWords>
+__device__ __forceinline__ void push_streamed(const PushArgs& p, CtrlHeader* hdr, int* left_behind, int lane) {
+  const PushPlan plan = plan_push(p);
   int current = 0;                                     // chunk this warp may still store into
   unsigned next_claim = lane == 0 ? atomicAdd(&hdr->cwork_push, 1u) : 0u;
   while (true) {
     const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
-    int item_chunk = chunks;
-    if (item < items) {
-      const long long block = item / per_block;
+    int item_chunk = plan.chunks;
+    if (item < plan.items) {
+      const long long block = item / plan.per_block;
       item_chunk = current;
-      while (item_chunk + 1 < chunks && blocks * (item_chunk + 1) / chunks <= block) ++item_chunk;
+      while (item_chunk + 1 < plan.chunks && plan.blocks * (item_chunk + 1) / plan.chunks <= block) ++item_chunk;
     }
-    while (current < item_chunk) {                     // leave chunk `current` behind
+    if (current < item_chunk) {
       __syncwarp();
-      unsigned before = 0;
       if (lane == 0) {
-        __threadfence_system();                        // this warp's stores are performed system-wide
-        before = atomicAdd(&hdr->cpush_done[current], 1u);
-        if (before == everyone - 1) __threadfence();   // acquire side of the count
+        __threadfence_block();
+        for (; current < item_chunk; ++current) atomicAdd(left_behind + current, 1);
       }
-      before = __shfl_sync(0xffffffffu, before, 0);
-      if (before == everyone - 1) {
-        const long long pushed = blocks * (current + 1) / chunks * kPushBlock;   // rows per peer, at least
-        for (int d = lane; d < p.world; d += 32) {
-          if (d == p.self) continue;
-          const long long rows = p.rows_from[d] < pushed ? p.rows_from[d] : pushed;
-          const unsigned long long progress = current == chunks - 1
-              ? 0xffffffffull : static_cast<unsigned long long>(p.first_row[d] + rows);
-          unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[d] + ready_offset) + p.self;
-          red_max_release_sys(word, (static_cast<unsigned long long>(epoch) << 32) | progress);
-        }
-      }
-      ++current;
+      current = item_chunk;
     }
-    if (item >= items) break;
+    if (item >= plan.items) break;
     if (lane == 0) next_claim = atomicAdd(&hdr->cwork_push, 1u);   // in flight while this item is copied
     push_item<kWords, 8>(p, item, lane);
+  }
+}
+
+__device__ __forceinline__ void herald_streamed(const PushArgs& p, const RankCtx& c, CtrlHeader* hdr,
+                                                size_t ready_offset, unsigned epoch, const int* left_behind, int lane) {
+  const PushPlan plan = plan_push(p);
+  const volatile int* counts = left_behind;
+  for (int chunk = 0; chunk < plan.chunks; ++chunk) {
+    unsigned before = 0;
+    bool ok = true;
+    if (lane == 0) {
+      ok = bounded_wait(c, kPhaseCombine, 6, [&] { return counts[chunk] >= kPushWarps - 1; });
+      if (ok) {
+        __threadfence_system();                          // every store the CTA made into this chunk has landed
+        before = atomicAdd(&hdr->cpush_done[chunk], 1u);
+        if (before == gridDim.x - 1) __threadfence();    // acquire side of the count
+      }
+    }
+    if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) return;
+    before = __shfl_sync(0xffffffffu, before, 0);
+    if (before != gridDim.x - 1) continue;
+    const long long pushed = plan.blocks * (chunk + 1) / plan.chunks * kPushBlock;   // rows per peer, at least
+    for (int d = lane; d < p.world; d += 32) {
+      if (d == p.self) continue;
+      const long long rows = p.rows_from[d] < pushed ? p.rows_from[d] : pushed;
+      const unsigned long long progress = chunk == plan.chunks - 1
+          ? 0xffffffffull : static_cast<unsigned long long>(p.first_row[d] + rows);
+      unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[d] + ready_offset) + p.self;
+      red_max_release_sys(word, (static_cast<unsigned long long>(epoch) << 32) | progress);
+    }
   }
 }
 
@@ -598,6 +638,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   __shared__ int s_need[64];
   __shared__ int s_rows_from[64], s_first_row[64];
   __shared__ int s_most;
+  __shared__ int s_left_behind[kMaxPushChunks];   // streamed: push warps that are done with chunk c
   __shared__ int s_last;
   __shared__ unsigned long long s_full[kMaxGroups * kMaxGroupStages], s_empty[kMaxGroups * kMaxGroupStages];
   __shared__ StageItem s_items[kMaxGroups * kMaxGroupStages];
@@ -614,6 +655,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     s_stage[tid] = c.heap[tid] + off + pl.staging;
     s_need[tid] = (tid != self && reinterpret_cast<const int*>(slot + sl.send_cnt)[tid] > 0) ? 1 : 0;
   }
+  if (tid >= 96 && tid < 96 + kMaxPushChunks) s_left_behind[tid - 96] = 0;
   if (tid == 64) {
     int at = 0, most = 0;
     for (int r = 0; r < W; ++r) {
@@ -654,8 +696,10 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   if (kStreamed) {
     // ---- push and reduce side by side ----------------------------------------------------
     constexpr int kReduceWarps = kStreamGroups * (kGroupWarps + 1);
-    if ((tid >> 5) >= kReduceWarps) {
-      push_streamed<kWords>(push, c, hdr, cl.ready, e, lane);
+    if ((tid >> 5) == kBulkThreads / 32 - 1) {
+      herald_streamed(push, c, hdr, cl.ready, e, s_left_behind, lane);
+    } else if ((tid >> 5) >= kReduceWarps) {
+      push_streamed<kWords>(push, hdr, s_left_behind, lane);
       if (op.profile != nullptr && tid == kReduceWarps * 32)
         op.profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + 1] = global_timer_ns();
     } else {
