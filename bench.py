@@ -122,9 +122,6 @@ class OursArm:
                      timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30,
                      cooperative_launch=not plain_launch, combine_streaming=combine_streaming)
         self.context = Context(self.comm, workloads.contiguous_expert_map(shape["experts"], world), cfg)
-        if os.environ.get("EPX_PUSH_CHUNK_BYTES"):
-            self.context._core.engine.set_combine_streaming({"auto": -1, "off": 0, "on": 1}[combine_streaming],
-                                                            int(os.environ["EPX_PUSH_CHUNK_BYTES"]))
         self.layer = IdentityMoELayer(self.context)
 
     def enable_graph(self, example):

@@ -64,7 +64,7 @@ class Config:
     combine_rounding: str = "two_step"        # "two_step" (single-node reference) or "single" (multi-node reference)
     zero_padding: bool = True                 # keep activation rows above valid_count at zero
     cooperative_launch: bool = True           # driver-guaranteed co-residency of the transport CTAs
-    combine_streaming: str = "auto"           # reduce while peers still push: "auto" (large batches), "on", "off"
+    combine_streaming: str = "auto"           # reduce while peers still push: "on"; "off"/"auto": push, then reduce
 
     @property
     def device_transport(self) -> bool:

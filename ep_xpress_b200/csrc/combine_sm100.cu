@@ -22,12 +22,14 @@
 //   A. push    work items (received row, row segment) claimed from a local counter:
 //              rows whose source is a peer are stored to that peer's staging plane
 //              at the return slot the dispatch recorded next to the row;
-//   B. signal  the last CTA publishes the monotone combine epoch to every peer
-//              after a system fence;
-//   C. wait    bounded, for the epoch of exactly the peers this rank sent rows to;
+//   B. signal  the last CTA publishes its progress word (epoch << 32 | rows pushed, here
+//              "all") to every peer after a system fence, as a max update;
+//   C. wait    bounded, for that word of exactly the peers this rank sent rows to;
 //   D. reduce  work items (token, segment): staging rows and the local partial row
 //              are read from this GPU's own memory and reduced in rank order;
 //   E. retire  the last CTA advances the device epoch.
+// A streamed variant (opt-in) runs A and D side by side: a few warps push and publish
+// progress chunk by chunk while the others reduce the tokens whose rows have arrived.
 // No trailing handshake is needed: a staging plane is only rewritten by the combine
 // of a later dispatch on the same slot, which cannot complete before this rank has
 // entered that dispatch, i.e. finished this reduce.
@@ -289,7 +291,6 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
                                   : hi - static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
   const int mine = cta_items > group ? (cta_items - group + kGroups - 1) / kGroups : 0;
   long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
-  unsigned long long t_first = 0, t_half = 0;   // TEMP
   bool ok = true;
   if (producer) {
     auto item_of = [&](int k) { return lo + (group + k * kGroups) * stride; };
@@ -362,11 +363,6 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
               seen_hi = lane + 32 < world ? ld_acquire_sys(a.progress + lane + 32) : 0ull;
               fence_proxy_async();      // the rows were written by generic stores; the copies below are async-proxy reads
             }
-          }
-          if (kStreamed && a.profile != nullptr && group == 0 && lane == 0) {   // TEMP instrumentation
-            unsigned long long* st = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps;
-            if (base + i == 0) t_first = global_timer_ns() - st[0];
-            if (base + i == mine / 2) t_half = global_timer_ns() - st[0];
           }
           const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
           const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
@@ -457,7 +453,6 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
     unsigned long long* slot = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps + (warp == 0 ? 4 : 6);
     slot[0] = static_cast<unsigned long long>(waited);
     slot[1] = static_cast<unsigned long long>(worked);
-    if (kStreamed && warp != 0) { slot[0] = t_first; slot[1] = t_half; }   // TEMP
   }
   return ok;
 }

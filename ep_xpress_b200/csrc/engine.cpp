@@ -97,7 +97,10 @@ class Engine {
     if (tables_ != nullptr) cudaFree(tables_);
   }
 
-  // -1: stream the combine push when the batch is large (default); 0: never; 1: whenever possible.
+  // 1: push and reduce side by side wherever the bulk-copy reduce applies; 0 or -1: one after
+  // the other. (-1, "auto", is reserved for a size rule; on B200 the sequential order measured
+  // faster at every size tried, because a system-scope fence does not complete while the same SM
+  // keeps storing to a peer, so progress cannot be published before the push is over.)
   // `chunk_bytes`: how much a rank pushes between two progress publications (0 keeps the value).
   void set_combine_streaming(int mode, int64_t chunk_bytes) {
     streaming_ = mode;
@@ -275,8 +278,7 @@ class Engine {
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
     const int fanout = route_fanout(topk_, world_);
-    const int64_t pushed_bytes = max_tokens * fanout * static_cast<int64_t>(hidden_) * 2;
-    const bool streamed = world_ > 1 && (streaming_ > 0 || (streaming_ < 0 && pushed_bytes >= kStreamingBytes));
+    const bool streamed = world_ > 1 && streaming_ > 0;
     cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, fanout, streamed, cooperative_,
                               stream_of(stream)), "combine launch");
   }
@@ -377,7 +379,6 @@ class Engine {
   bool cooperative_ = true;
   int streaming_ = -1;
   int64_t push_chunk_bytes_ = 16ll << 20;
-  static constexpr int64_t kStreamingBytes = 32ll << 20;
   int sms_ = 0;
   std::vector<int> experts_per_rank_;
   std::vector<char*> own_heap_;
