@@ -113,9 +113,16 @@ def main():
         phases = {}
         for name, (a, b) in {"dispatch": (0, 1), "experts": (1, 2), "combine": (2, 3), "layer": (0, 3)}.items():
             phases[name] = statistics.median(max_over_ranks([m[a].elapsed_time(m[b]) * 1e3 for m in timing], world))
-        local_pairs = float(layer.experts.counters[1].item())           # tile-padded rows actually multiplied
+        sorted_rows = float(layer.experts.counters[1].item())           # tile-padded rows the GEMMs walked
+        # Useful work only: (token, slot) pairs whose expert lives on this rank, mean over the batches.
+        owner = torch.tensor(emap, device="cuda")
+        mine = torch.stack([torch.bincount(owner[ids].flatten(), minlength=world) for _, ids, _ in batches]).sum(0)
+        if world > 1:
+            dist.all_reduce(mine)
+        local_pairs = float(mine[rank].item()) / len(batches)
         flops = local_pairs * 3 * 2 * args.hidden * args.inter
-        entry = {"tokens_per_rank": tokens, "phase_us_p50": phases, "sorted_rows_rank0": local_pairs,
+        entry = {"tokens_per_rank": tokens, "phase_us_p50": phases, "sorted_rows_rank0": sorted_rows,
+                 "local_pairs_rank0": local_pairs,
                  "expert_tflops": flops / (phases["experts"] * 1e-6) / 1e12,
                  "expert_fraction_of_" + peak_source + "_peak": flops / (phases["experts"] * 1e-6) / 1e12 / peak}
         if args.baseline:
