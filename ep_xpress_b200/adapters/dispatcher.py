@@ -70,9 +70,10 @@ def close_contexts():
 
 class EPDispatcher:
     def __init__(self, comm, placement, config, *, layer_id, group_key=None, context_factory=None,
-                 enable_cuda_graph=False):
+                 enable_cuda_graph=False, channel_policy=None):
         self.layer_id = layer_id
         self.config = config
+        self.channel_policy = dict(channel_policy or {})     # see adapters.env.channel_policy_from_env
         self.context = shared_context(comm, placement, config, group_key=group_key, factory=context_factory)
         if enable_cuda_graph and not getattr(self.context, "_graph_enabled", False):
             self.context.enable_cuda_graph()
@@ -100,7 +101,8 @@ class EPDispatcher:
         tokens = hidden_states.shape[0]
         capacity = receive_capacity_from_scheduler(token_counts, cfg.max_tokens_per_rank)
         small_decode = is_decode and tokens <= max(cfg.decode_max_tokens, 0)
-        channels = select_active_channels(tokens, self.context.effective_channels, is_decode=is_decode)
+        channels = select_active_channels(tokens, self.context.effective_channels, is_decode=is_decode,
+                                          **self.channel_policy)
         kwargs = dict(stream=stream, recv_capacity=capacity, active_channels=channels, tag=("layer", self.layer_id))
         if is_decode or small_decode:
             kwargs["workspace"] = self._workspace(capacity, tokens)

@@ -24,6 +24,17 @@ _FIELDS = {
     "EPX_GPU_POOL_BUDGET_BYTES": ("gpu_pool_budget_bytes", int),
     "EPX_WORKSPACE_POOL_BYTES": ("workspace_pool_bytes", int),
     "EPX_COOPERATIVE_LAUNCH": ("cooperative_launch", "bool"),
+    "EPX_COMBINE_STREAMING": ("combine_streaming", str),
+}
+
+# Per-operation launch width of the dispatcher (not Config fields: they never change what is
+# allocated). Counterparts of the reference's adaptive / prefill / decode channel variables
+# (ep_xpress/adapters/sglang.py:107-176).
+_POLICY = {
+    "EPX_ADAPTIVE_CHANNELS": ("adaptive", "bool"),
+    "EPX_PREFILL_CHANNELS": ("prefill_override", int),
+    "EPX_DECODE_CHANNELS": ("decode_override", int),
+    "EPX_DECODE_TOKENS_PER_CHANNEL": ("tokens_per_channel_decode", int),
 }
 
 PRESETS = {
@@ -60,7 +71,7 @@ def config_from_env(hidden_size, topk, max_tokens_per_rank, env=None, preset=Non
         if preset not in PRESETS:
             raise ValueError(f"unknown preset {preset!r}; choose from {sorted(PRESETS)}")
         values.update(PRESETS[preset])
-    unknown = [k for k in env if k.startswith("EPX_") and k not in _FIELDS and k != "EPX_PRESET"]
+    unknown = [k for k in env if k.startswith("EPX_") and k not in _FIELDS and k not in _POLICY and k != "EPX_PRESET"]
     if unknown:
         raise ValueError(f"unknown configuration variables: {sorted(unknown)}")
     values.update({k: v for k, v in env.items() if k in _FIELDS})
@@ -70,3 +81,15 @@ def config_from_env(hidden_size, topk, max_tokens_per_rank, env=None, preset=Non
         kwargs[field] = _parse(name, kind, text)
     kwargs.update(overrides)
     return Config(hidden_size=hidden_size, topk=topk, max_tokens_per_rank=max_tokens_per_rank, **kwargs)
+
+
+def channel_policy_from_env(env=None):
+    """Keyword arguments for ``select_active_channels`` / ``EPDispatcher(channel_policy=...)``."""
+    env = os.environ if env is None else env
+    policy = {}
+    for name, (key, kind) in _POLICY.items():
+        if name in env:
+            policy[key] = _parse(name, kind, env[name])
+    if policy.get("tokens_per_channel_decode", 1) < 1:
+        raise ValueError("EPX_DECODE_TOKENS_PER_CHANNEL must be positive")
+    return policy

@@ -49,11 +49,40 @@ def receive_capacity_from_scheduler(token_counts, max_tokens_per_rank):
     return sum(counts)
 
 
-def select_active_channels(local_tokens, effective_channels, *, is_decode, tokens_per_channel_decode=8):
-    """Prefill: one channel per token up to all channels; decode: one per 8 tokens."""
+def select_active_channels(tokens, effective_channels, *, is_decode, tokens_per_channel_decode=8, adaptive=True,
+                           prefill_override=0, decode_override=0):
+    """Channels (= share of the CTA budget) for one operation.
+
+    A phase override asks for a fixed count and is clamped to what was allocated; with
+    ``adaptive=False`` every operation uses all channels; otherwise prefill takes one channel
+    per token and decode one per ``tokens_per_channel_decode`` tokens, up to all channels
+    (the policy of the reference's adapter, ep_xpress/adapters/sglang_config.py:88-116). Each
+    rank launches its own kernels and only synchronises its own CTAs, so ranks may arrive at
+    different widths; pass the group's global token count when the same width is wanted
+    everywhere.
+    """
     if effective_channels < 1:
         raise ValueError("effective_channels must be positive")
-    if local_tokens <= 0:
+    for name, value in (("prefill_override", prefill_override), ("decode_override", decode_override)):
+        if isinstance(value, bool) or not isinstance(value, int) or value < 0:
+            raise ValueError(f"{name} must be a non-negative integer")
+    override = decode_override if is_decode else prefill_override
+    if override:
+        return min(effective_channels, override)
+    if not adaptive:
+        return effective_channels
+    if tokens <= 0:
         return 1
-    wanted = -(-local_tokens // tokens_per_channel_decode) if is_decode else local_tokens
+    wanted = -(-tokens // tokens_per_channel_decode) if is_decode else tokens
     return max(1, min(effective_channels, wanted))
+
+
+def validate_expert_runner(*, activation="silu", is_gated=True, gemm1_alpha=None, gemm1_clamp_limit=None,
+                           swiglu_limit=None):
+    """Static scope of the count-aware BF16 expert runner (``ops.GroupedSwiGLU``): gated SiLU
+    without activation modifiers, checked once per model
+    (ep_xpress/adapters/sglang_config.py:76-85)."""
+    if activation != "silu" or not is_gated:
+        raise ValueError("the grouped expert runner requires gated SiLU")
+    if any(value is not None for value in (gemm1_alpha, gemm1_clamp_limit, swiglu_limit)):
+        raise ValueError("the grouped expert runner does not support activation modifiers")

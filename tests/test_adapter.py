@@ -154,3 +154,39 @@ def test_config_from_env_precedence_and_validation():
         adapters.config_from_env(64, 2, 16, env={}, preset="h100")
     with pytest.raises(ValueError, match="channels"):
         adapters.config_from_env(64, 2, 16, env={"EPX_CHANNELS": "64"})
+
+
+def test_channel_overrides_and_fixed_width():
+    pick = adapters.select_active_channels
+    assert pick(4096, 8, is_decode=False, prefill_override=3) == 3
+    assert pick(4, 8, is_decode=True, decode_override=32) == 8           # clamped to what was allocated
+    assert pick(4, 8, is_decode=True, prefill_override=3) == 1           # the other phase's override is ignored
+    assert pick(1, 8, is_decode=True, adaptive=False) == 8
+    with pytest.raises(ValueError, match="decode_override"):
+        pick(4, 8, is_decode=True, decode_override=-1)
+    with pytest.raises(ValueError, match="prefill_override"):
+        pick(4, 8, is_decode=False, prefill_override=True)
+
+
+def test_expert_runner_scope():
+    adapters.validate_expert_runner()
+    with pytest.raises(ValueError, match="gated SiLU"):
+        adapters.validate_expert_runner(activation="gelu")
+    with pytest.raises(ValueError, match="gated SiLU"):
+        adapters.validate_expert_runner(is_gated=False)
+    with pytest.raises(ValueError, match="activation modifiers"):
+        adapters.validate_expert_runner(swiglu_limit=7.0)
+
+
+def test_channel_policy_from_environment():
+    env = {"EPX_ADAPTIVE_CHANNELS": "0", "EPX_DECODE_CHANNELS": "2", "EPX_COMBINE_STREAMING": "on"}
+    policy = adapters.channel_policy_from_env(env)
+    assert policy == {"adaptive": False, "decode_override": 2}
+    cfg = adapters.config_from_env(64, 2, 8, env=env)                  # policy variables are not unknown
+    assert cfg.combine_streaming == "on"
+    assert adapters.select_active_channels(100, 8, is_decode=True, **policy) == 2
+    assert adapters.select_active_channels(100, 8, is_decode=False, **policy) == 8
+    with pytest.raises(ValueError, match="EPX_DECODE_TOKENS_PER_CHANNEL"):
+        adapters.channel_policy_from_env({"EPX_DECODE_TOKENS_PER_CHANNEL": "0"})
+    with pytest.raises(ValueError, match="not a valid value"):
+        adapters.channel_policy_from_env({"EPX_PREFILL_CHANNELS": "many"})
