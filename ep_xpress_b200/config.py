@@ -64,6 +64,7 @@ class Config:
     combine_rounding: str = "two_step"        # "two_step" (single-node reference) or "single" (multi-node reference)
     zero_padding: bool = True                 # keep activation rows above valid_count at zero
     cooperative_launch: bool = True           # driver-guaranteed co-residency of the transport CTAs
+    debug_delay_ns: int = 0                   # debugging: random sleeps below this bound at kernel phase boundaries
     combine_streaming: str = "auto"           # reduce while peers still push: "on"; "off"/"auto": push, then reduce
 
     @property
@@ -118,6 +119,8 @@ class Config:
             raise NotImplementedError("transport must be nvlink, host_sm or host_ce")
         if self.combine_rounding not in ("two_step", "single"):
             raise ValueError("combine_rounding must be two_step or single")
+        if not _is_int(self.debug_delay_ns) or not 0 <= self.debug_delay_ns <= 1_000_000:
+            raise ValueError("debug_delay_ns must be an integer in [0, 1000000]")
         if self.combine_streaming not in ("auto", "on", "off"):
             raise ValueError("combine_streaming must be auto, on or off")
         if device:
@@ -195,7 +198,8 @@ class Config:
         """Peer-mapped HBM one rank allocates at bootstrap."""
         slot = self.nvlink_slot_bytes(world_size)
         reserve = self.workspace_pool_bytes or 2 * slot
-        return _round_up(self.ctrl_bytes(world_size) + self.slots * slot + reserve, 2 << 20)
+        guards = 8192 * (self.slots + 16) if self.diagnostics else 0     # guard bands around every slot
+        return _round_up(self.ctrl_bytes(world_size) + self.slots * slot + reserve + guards, 2 << 20)
 
     def mapped_arena_bytes(self, topk, channels=None, queue_peers=1, *, dispatch_banks=0) -> int:
         """Host-mapped queue bytes of one producer: always 0 here.

@@ -704,6 +704,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     }
   } else {
   // ---- A. push my rows to the ranks that own the tokens ---------------------------
+  debug_delay(c, 4);
   {
     const int peers = W - 1;
     const long long blocks = (s_most + kPushBlock - 1) / kPushBlock;
@@ -718,6 +719,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   }
   __syncthreads();
   profile_stamp(op.profile, 1);
+  debug_delay(c, 5);
 
   // ---- B. signal ------------------------------------------------------------------------
   if (tid == 0) {
@@ -740,6 +742,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   }
   if (!__syncthreads_and(ok)) return;
   profile_stamp(op.profile, 2);
+  debug_delay(c, 6);
 
   // ---- D. rank-order reduce from local memory -----------------------------------------------
   if (kBulk) {

@@ -193,6 +193,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   profile_stamp(op.profile, 1);
   if (!solo && !rank_barrier(c, &hdr->bar_count, gridDim.x, kPhaseDispatch)) return;
   profile_stamp(op.profile, 2);
+  debug_delay(c, 1);
 
   // ---- 2. publish my count row ----------------------------------------------
   if (tid < W) {
@@ -215,13 +216,26 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   }
 
   // ---- 3. wait for every rank's counts and addresses ---------------------------
+  // A word of a LATER generation in this parity's place means the group is out of step (a rank
+  // ran more dispatches than this one): that is reported at once instead of timing out.
   bool ok = true;
-  for (int i = tid; i < W * W && ok; i += kThreads)
-    ok = bounded_wait(c, kPhaseDispatch, 3, [&] { return tag_of(ld_acquire_sys(my_cnt + i)) == g; });
+  for (int i = tid; i < W * W && ok; i += kThreads) {
+    bool ahead = false;
+    ok = bounded_wait(c, kPhaseDispatch, 3, [&] {
+      const unsigned tag = tag_of(ld_acquire_sys(my_cnt + i));
+      ahead = static_cast<int>(tag - g) > 0;
+      return tag == g || ahead;
+    });
+    if (ok && ahead) {
+      report_error(c, kIdentityMismatch, kPhaseDispatch, 7, static_cast<unsigned>(i / W));
+      ok = false;
+    }
+  }
   for (int i = tid; i < W * 4 && ok; i += kThreads)
     ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(my_addr + i)) == g; });
   if (!__syncthreads_and(ok)) return;
   profile_stamp(op.profile, 3);
+  debug_delay(c, 2);
 
   if (tid < W) {
     const int d = tid;
@@ -350,6 +364,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
 
   // ---- 5. signal -----------------------------------------------------------------
   const int valid = s_ok[self] ? s_total[self] : 0;
+  debug_delay(c, 3);
   __syncthreads();
   profile_stamp(op.profile, 4);
   if (tid == 0) {

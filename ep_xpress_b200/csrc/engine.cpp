@@ -62,7 +62,8 @@ class Engine {
     cuda_check(cudaMemcpy(tables_, expert_to_rank.data(), sizeof(int) * experts, cudaMemcpyHostToDevice), "upload");
     cuda_check(cudaMemcpy(tables_ + experts, local_index.data(), sizeof(int) * experts, cudaMemcpyHostToDevice),
                "upload");
-    std::vector<RankCtx> host(local_ranks_.size());
+    std::vector<RankCtx>& host = host_ctx_;
+    host.resize(local_ranks_.size());
     for (size_t i = 0; i < local_ranks_.size(); ++i) {
       TORCH_CHECK(local_ranks_[i] >= 0 && local_ranks_[i] < world, "local rank is outside the group");
       TORCH_CHECK(heaps[i].size() == static_cast<size_t>(world), "a heap table needs one address per rank");
@@ -101,6 +102,16 @@ class Engine {
   // the other. (-1, "auto", is reserved for a size rule; on B200 the sequential order measured
   // faster at every size tried, because a system-scope fence does not complete while the same SM
   // keeps storing to a peer, so progress cannot be published before the push is over.)
+  // Debugging: every CTA sleeps a pseudo-random time below `ns` at each phase boundary, which
+  // shakes the interleaving of ranks and CTAs without changing any result.
+  void set_debug_delay(int64_t ns) {
+    TORCH_CHECK(ns >= 0 && ns <= 1000000, "debug delay must be within [0, 1 ms]");
+    c10::cuda::CUDAGuard guard(device_);
+    for (RankCtx& c : host_ctx_) c.debug_delay_ns = static_cast<unsigned>(ns);
+    cuda_check(cudaDeviceSynchronize(), "quiesce before changing the debug delay");
+    cuda_check(cudaMemcpy(ctx_, host_ctx_.data(), sizeof(RankCtx) * host_ctx_.size(), cudaMemcpyHostToDevice),
+               "upload rank contexts");
+  }
   // `chunk_bytes`: how much a rank pushes between two progress publications (0 keeps the value).
   void set_combine_streaming(int mode, int64_t chunk_bytes) {
     streaming_ = mode;
@@ -377,6 +388,7 @@ class Engine {
   std::vector<int> local_ranks_;
   int hidden_, topk_, device_;
   bool cooperative_ = true;
+  std::vector<RankCtx> host_ctx_;
   int streaming_ = -1;
   int64_t push_chunk_bytes_ = 16ll << 20;
   int sms_ = 0;
@@ -413,6 +425,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("heaps"), py::arg("timeout_seconds"), py::arg("single_round"), py::arg("device"),
            py::arg("cooperative") = true)
       .def("sm_count", &Engine::sm_count)
+      .def("set_debug_delay", &Engine::set_debug_delay)
       .def("set_combine_streaming", &Engine::set_combine_streaming, py::arg("mode"), py::arg("chunk_bytes") = 0)
       .def("experts_per_rank", &Engine::experts_per_rank)
       .def("ctrl_bytes", &Engine::ctrl_bytes)

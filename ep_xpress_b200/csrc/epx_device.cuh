@@ -194,6 +194,22 @@ __device__ __forceinline__ void bulk_load_to_smem(void* dst, const void* src, un
 // Orders earlier generic-proxy accesses of this thread before later async-proxy (bulk copy) ones.
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+// Debugging aid that shakes the interleaving of ranks and CTAs: thread 0 of the CTA sleeps for a
+// pseudo-random time below RankCtx::debug_delay_ns (a hash of rank, CTA, call site and the
+// clock), then the CTA proceeds together. Off (zero) it costs one uniform branch. The results
+// of every operation must not depend on it; the tests run the oracle comparison with it on.
+__device__ __forceinline__ void debug_delay(const RankCtx& c, unsigned site) {
+  if (c.debug_delay_ns == 0) return;
+  if (threadIdx.x == 0) {
+    unsigned h = (static_cast<unsigned>(c.rank) * 2654435761u) ^ (blockIdx.x * 40503u) ^ (site * 2246822519u) ^
+                 static_cast<unsigned>(global_timer_ns() >> 5);
+    h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+    const unsigned long long until = global_timer_ns() + h % c.debug_delay_ns;
+    while (global_timer_ns() < until) __nanosleep(200);
+  }
+  __syncthreads();
+}
+
 // Opt-in phase timestamp of one CTA (thread 0 only); a null buffer costs one predicate.
 __device__ __forceinline__ void profile_stamp(unsigned long long* profile, int index) {
   if (profile != nullptr && threadIdx.x == 0)

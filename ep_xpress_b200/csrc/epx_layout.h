@@ -162,6 +162,7 @@ struct RankCtx {
   int topk;
   int num_experts;
   int single_round;               // 0: remote-sum -> bf16 -> + local -> bf16; 1: one rounding
+  unsigned debug_delay_ns;        // debugging: every CTA sleeps a pseudo-random time below this at phase boundaries
   unsigned long long timeout_ns;  // bound of every device-side wait
   const int* expert_rank;         // [num_experts] owner rank
   const int* expert_local;        // [num_experts] index among the owner's experts

@@ -22,6 +22,8 @@ from typing import List, Optional
 import torch
 
 _ALIGN = 4096
+_GUARD_BYTES = 4096        # keeps the slot itself page-aligned
+_GUARD_PATTERN = 0xA5
 
 
 class HeapAllocator:
@@ -90,6 +92,8 @@ class Slot:
     busy: bool = False                 # dispatched, combine not yet enqueued
     released: bool = False
     tag: object = field(default=None, repr=False)
+    bases: Optional[List[int]] = None  # allocation start per local rank when guard bands surround the slot
+    guards: Optional[List[torch.Tensor]] = None   # uint8 views of the guard bands (diagnostics)
 
 
 class TransportCore:
@@ -105,11 +109,14 @@ class TransportCore:
                                     config.combine_rounding == "single", self.device.index,
                                     bool(config.cooperative_launch))
         self.engine.set_combine_streaming({"auto": -1, "off": 0, "on": 1}[config.combine_streaming])
+        if config.debug_delay_ns:
+            self.engine.set_debug_delay(int(config.debug_delay_ns))
         ctrl = self.engine.ctrl_bytes()
         self._allocators = [HeapAllocator(ctrl, heap_bytes) for _ in self.local_ranks]
         self.max_ctas = max(1, min(self.engine.max_ctas(config.max_tokens_per_rank), self.engine.sm_count()))
         self.items_per_cta = native.THREADS // 32   # (token, row segment) work items a CTA should find
         self.launches = 0
+        self._slots: List[Slot] = []
 
     # ---- slots ---------------------------------------------------------------
     def create_slot(self, capacity: int, tokens: int, stream=None) -> Slot:
@@ -117,8 +124,23 @@ class TransportCore:
         stream = stream or torch.cuda.current_stream(self.device)
         fanout = min(self.topk, self.world)
         offsets, views = [], []
+        # Diagnostics: a band of a known byte pattern before and after every slot. Nothing may
+        # ever write there, so `check_guards` turns a stray peer store (a wrong row index, a
+        # stale slot address) into a reported error instead of silent corruption next door.
+        guarded = bool(self.config.diagnostics)
+        bases, guards = [], []
         for local, allocator in enumerate(self._allocators):
-            offset = allocator.allocate(layout["bytes"])
+            if guarded:
+                base = allocator.allocate(layout["bytes"] + 2 * _GUARD_BYTES)
+                offset = base + _GUARD_BYTES
+                for at in (base, offset + layout["bytes"]):
+                    band = self.engine.view(local, at, [_GUARD_BYTES], torch.uint8)
+                    with torch.cuda.stream(stream):
+                        band.fill_(_GUARD_PATTERN)
+                    guards.append(band)
+            else:
+                base = offset = allocator.allocate(layout["bytes"])
+            bases.append(base)
             offsets.append(offset)
             self.engine.slot_reset(local, offset, capacity, tokens, stream.cuda_stream)
 
@@ -138,14 +160,27 @@ class TransportCore:
                 recv_counts=view("recv_cnt", (self.world,), torch.int32),
                 output=view("output", (tokens, self.hidden), torch.bfloat16),
             ))
-        return Slot(capacity, tokens, offsets, views)
+        slot = Slot(capacity, tokens, offsets, views, bases=bases, guards=guards if guarded else None)
+        self._slots.append(slot)
+        return slot
 
     def release_slot(self, slot: Slot) -> None:
         if slot.released:
             return
         slot.released = True
-        for allocator, offset in zip(self._allocators, slot.offsets):
+        if slot in self._slots:
+            self._slots.remove(slot)
+        for allocator, offset in zip(self._allocators, slot.bases or slot.offsets):
             allocator.release(offset)
+
+    def check_guards(self) -> None:
+        """Raise if any guard band around a live slot was written to (diagnostics only)."""
+        for slot in self._slots:
+            for index, band in enumerate(slot.guards or ()):
+                if not bool((band == _GUARD_PATTERN).all()):
+                    where = "before" if index % 2 == 0 else "after"
+                    raise RuntimeError(f"guard band {where} the slot at heap offset {slot.offsets[index // 2]} of local "
+                                       f"rank {index // 2} was overwritten: a store landed outside its slot")
 
     # ---- launches --------------------------------------------------------------
     def pick_ctas(self, tokens: int, budget: Optional[int] = None) -> int:

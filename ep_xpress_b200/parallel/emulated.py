@@ -88,6 +88,12 @@ class EmulatedGroup:
             torch.cuda.synchronize(self.device)
             return [self.core.status(i) for i in range(self.world_size)]
 
+    def check_guards(self) -> None:
+        """Diagnostics: raise if a store landed in the guard band around any live slot."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            self.core.check_guards()
+
     def close(self):
         if self._closed:
             return

@@ -214,6 +214,12 @@ class NVLinkContext(Context):
                 error = RuntimeError(f"{self.config.transport}: {text} (detail 0x{detail:016x})")
                 self._abort(error)
                 raise error
+            if self.config.diagnostics:
+                try:
+                    self._core.check_guards()
+                except RuntimeError as error:
+                    self._abort(error)
+                    raise
 
     def stats(self):
         """Counters of this context (launches, epochs, heap use); synchronises the device."""

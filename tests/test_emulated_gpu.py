@@ -210,3 +210,24 @@ def test_streamed_and_sequential_combine_agree_across_slots():
         for index in (0, 1):
             for rank in range(world):
                 assert torch.equal(bits(outs[(1, index)][rank]), bits(outs[(0, index)][rank]))
+
+
+def test_random_delays_and_guard_bands_leave_results_exact():
+    """Orderings shaken by per-CTA sleeps at every phase boundary; nothing lands outside a slot."""
+    world, hidden, topk, tokens = 4, 512, 4, 150
+    experts = world * 4
+    cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=2.0,
+                 diagnostics=True, debug_delay_ns=20000)
+    emap = workloads.round_robin_expert_map(experts, world)
+    with EmulatedGroup(world, emap, cfg) as group:
+        slots = [group.create_slot(), group.create_slot()]
+        assert all(slot.guards and len(slot.guards) == 2 * world for slot in slots)
+        for seed in range(4):
+            xs = [workloads.gaussian_payload(tokens, hidden, seed=seed, rank=r) for r in range(world)]
+            routes = [workloads.uniform_routing(tokens, experts, topk, seed=seed, rank=r) for r in range(world)]
+            run_round(group, slots[seed % 2], xs, [i for i, _ in routes], [w for _, w in routes], emap, ctas=6)
+        group.check_guards()
+        slots[1].guards[3][17] = 0                                 # what a stray store would do
+        with pytest.raises(RuntimeError, match="guard band after the slot"):
+            group.check_guards()
+        slots[1].guards[3][17] = 0xA5

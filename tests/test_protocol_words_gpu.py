@@ -95,8 +95,26 @@ def test_cpu_played_peer_lets_a_local_dispatch_complete():
 
 def test_stale_generation_never_satisfies_a_wait():
     rank = LoneRank(timeout=0.05)
-    rank.forge_peer_dispatch_words(3)                 # same parity as generation 1, wrong tag
-    assert rank.dispatch(LOCAL)[0] == 3 and usable()
+    for generation in (1, 2):
+        rank.forge_peer_dispatch_words(generation)
+        assert rank.dispatch(LOCAL)[0] == 0
+    # Generation 3 shares its words with generation 1, whose values are still there.
+    status, _, dispatch_epoch, _ = rank.dispatch(LOCAL)
+    assert status == 3 and dispatch_epoch == 2 and usable()
+    rank.close()
+
+
+def test_a_peer_that_is_generations_ahead_is_reported_at_once():
+    rank = LoneRank(timeout=5.0)
+    rank.forge_peer_dispatch_words(3)                 # same parity as generation 1, but from the future
+    begin = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    begin.record()
+    status, detail, _, _ = rank.dispatch(LOCAL)
+    end.record()
+    torch.cuda.synchronize()
+    assert status == 5 and (detail >> 32) & 0xff == 7 and detail & 0xffffffff == 1      # out of step with rank 1
+    assert begin.elapsed_time(end) < 1000 and usable()
     rank.close()
 
 
