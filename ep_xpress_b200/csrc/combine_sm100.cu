@@ -705,7 +705,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   } else {
   // ---- A. push my rows to the ranks that own the tokens ---------------------------
   debug_delay(c, 4);
-  {
+  if (W > 1) {
     const int peers = W - 1;
     const long long blocks = (s_most + kPushBlock - 1) / kPushBlock;
     const long long items = peers > 0 ? blocks * peers * kPushBlock * segs : 0;
@@ -721,26 +721,29 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   profile_stamp(op.profile, 1);
   debug_delay(c, 5);
 
-  // ---- B. signal ------------------------------------------------------------------------
-  if (tid == 0) {
-    __threadfence_system();   // this CTA's peer stores are performed system-wide before it arrives
-    const unsigned prev = atomicAdd(&hdr->cdone_count, 1u);
-    s_last = (prev == gridDim.x - 1) ? 1 : 0;
-    if (s_last) __threadfence();   // acquire side of the arrival counter; the update below releases at sys scope
-  }
-  __syncthreads();
-  if (s_last && tid < W && tid != self) {
-    unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.ready) + self;
-    red_max_release_sys(word, all_pushed);
-  }
+  // A group of one rank has nobody to signal or to wait for.
+  if (W > 1) {
+    // ---- B. signal ------------------------------------------------------------------------
+    if (tid == 0) {
+      __threadfence_system();   // this CTA's peer stores are performed system-wide before it arrives
+      const unsigned prev = atomicAdd(&hdr->cdone_count, 1u);
+      s_last = (prev == gridDim.x - 1) ? 1 : 0;
+      if (s_last) __threadfence();   // acquire side of the arrival counter; the update below releases at sys scope
+    }
+    __syncthreads();
+    if (s_last && tid < W && tid != self) {
+      unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.ready) + self;
+      red_max_release_sys(word, all_pushed);
+    }
 
-  // ---- C. wait for the peers that push to me ----------------------------------------------
-  bool ok = true;
-  if (tid < W && s_need[tid]) {
-    const unsigned long long* word = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready) + tid;
-    ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(word) >= all_pushed; });
+    // ---- C. wait for the peers that push to me ----------------------------------------------
+    bool ok = true;
+    if (tid < W && s_need[tid]) {
+      const unsigned long long* word = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready) + tid;
+      ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(word) >= all_pushed; });
+    }
+    if (!__syncthreads_and(ok)) return;
   }
-  if (!__syncthreads_and(ok)) return;
   profile_stamp(op.profile, 2);
   debug_delay(c, 6);
 

@@ -368,7 +368,9 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   __syncthreads();
   profile_stamp(op.profile, 4);
   if (tid == 0) {
-    __threadfence_system();   // this CTA's peer stores are performed system-wide before it arrives
+    // This CTA's peer stores are performed system-wide before it arrives (a group of one rank
+    // has no peers: device scope is enough there).
+    if (W > 1) __threadfence_system(); else __threadfence();
     const unsigned prev = atomicAdd(&hdr->done_count, 1u);
     s_last = (prev == gridDim.x - 1) ? 1 : 0;
     if (s_last) __threadfence();   // acquire side of the arrival counter; the flag store below releases at sys scope
@@ -420,7 +422,8 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   }
   profile_stamp(op.profile, 6);
   ok = true;
-  if (tid < W && s_ok[self] && value_of(ld_relaxed_sys(my_cnt + tid * W + self)) > 0)
+  // (Not for this rank's own rows: the launch itself completes only when they are written.)
+  if (tid < W && tid != self && s_ok[self] && value_of(ld_relaxed_sys(my_cnt + tid * W + self)) > 0)
     ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return tag_of(ld_acquire_sys(my_done + tid)) == g; });
   __syncthreads_and(ok);
   profile_stamp(op.profile, 7);
