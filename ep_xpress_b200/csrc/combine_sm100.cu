@@ -77,31 +77,29 @@ __device__ __forceinline__ void store_chunk(char* p, const Chunk<kWords>& c) {
   else st_payload4(p, c.w[0]);
 }
 
+// Accumulators hold two FP32 sums per 64-bit register (the two elements of one BF16 pair).
 template <int kWords>
-__device__ __forceinline__ void accumulate(float* acc, const Chunk<kWords>& c) {
+__device__ __forceinline__ void accumulate(unsigned long long* acc, const Chunk<kWords>& c) {
 #pragma unroll
-  for (int i = 0; i < kWords; ++i) {
-    acc[2 * i] = __fadd_rn(acc[2 * i], __uint_as_float(c.w[i] << 16));
-    acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __uint_as_float(c.w[i] & 0xffff0000u));
-  }
+  for (int i = 0; i < kWords; ++i) acc[i] = add_f32x2(acc[i], bf16x2_to_f32x2(c.w[i]));
 }
 
 // Two-step rounding (default) or single rounding of the accumulated sum.
 template <int kWords>
-__device__ __forceinline__ Chunk<kWords> finish(const float* acc, const Chunk<kWords>& local, bool has_local,
-                                                bool single_round) {
+__device__ __forceinline__ Chunk<kWords> finish(const unsigned long long* acc, const Chunk<kWords>& local,
+                                                bool has_local, bool single_round) {
   Chunk<kWords> out;
 #pragma unroll
   for (int i = 0; i < kWords; ++i) {
-    float lo = acc[2 * i], hi = acc[2 * i + 1];
+    unsigned long long sum = acc[i];
+    float lo, hi;
     if (!single_round) {
-      const float llo = has_local ? __uint_as_float(local.w[i] << 16) : 0.f;
-      const float lhi = has_local ? __uint_as_float(local.w[i] & 0xffff0000u) : 0.f;
-      lo = __fadd_rn(bf16_bits_to_float(float_to_bf16_bits(lo)), llo);
-      hi = __fadd_rn(bf16_bits_to_float(float_to_bf16_bits(hi)), lhi);
+      unpack_f32x2(sum, lo, hi);
+      const unsigned long long rounded = bf16x2_to_f32x2(pack_bf16x2(lo, hi));
+      sum = add_f32x2(rounded, has_local ? bf16x2_to_f32x2(local.w[i]) : 0ull);
     }
-    out.w[i] = static_cast<unsigned>(float_to_bf16_bits(lo)) |
-               (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+    unpack_f32x2(sum, lo, hi);
+    out.w[i] = pack_bf16x2(lo, hi);
   }
   return out;
 }
@@ -135,9 +133,9 @@ __device__ __noinline__ void reduce_rows(RowPointers rows, const char* local_ptr
     for (int u = 0; u < kUnroll; ++u) {
       const long long off = base + static_cast<long long>(u) * 32 * kChunk;
       if (off < b1) {
-        float acc[kWords * 2];
+        unsigned long long acc[kWords];
 #pragma unroll
-        for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
+        for (int i = 0; i < kWords; ++i) acc[i] = 0ull;
 #pragma unroll
         for (int b = 0; b < kPeers; ++b)
           if (rp[b] != nullptr) accumulate<kWords>(acc, v[b][u]);
@@ -158,9 +156,9 @@ __device__ __noinline__ void reduce_rows_generic(const char* ptr_a, const char* 
   for (long long batch = b0; batch < b1; batch += 32ll * kChunk) {   // warp-uniform trip count
     const long long off = batch + static_cast<long long>(lane) * kChunk;
     const bool active = off < b1;
-    float acc[kWords * 2];
+    unsigned long long acc[kWords];
 #pragma unroll
-    for (int i = 0; i < kWords * 2; ++i) acc[i] = 0.f;
+    for (int i = 0; i < kWords; ++i) acc[i] = 0ull;
     for (int j0 = 0; j0 < n; j0 += kPeerBatch) {
       Chunk<kWords> v[kPeerBatch];
       bool use[kPeerBatch];
@@ -413,12 +411,12 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       const char* base = ring + static_cast<size_t>(stage) * stage_bytes;
       const int chunks = item.bytes / 16;
       for (int first = gtid; first < chunks; first += kGroupThreads * kChunksPerThread) {
-        float acc[kChunksPerThread][8];
+        unsigned long long acc[kChunksPerThread][4];
         Chunk<4> local[kChunksPerThread];
 #pragma unroll
         for (int u = 0; u < kChunksPerThread; ++u) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+          for (int i = 0; i < 4; ++i) acc[u][i] = 0ull;
         }
         bool has_local = false;
         for (int j = 0; j < item.contributors; ++j) {

@@ -222,5 +222,31 @@ __device__ __forceinline__ float bf16_bits_to_float(unsigned short bits) {
 __device__ __forceinline__ unsigned short float_to_bf16_bits(float v) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
+// Two floats rounded (to nearest even) and packed as one BF16 pair in a single instruction;
+// `lo` becomes the low half, i.e. the element at the lower address.
+__device__ __forceinline__ unsigned pack_bf16x2(float lo, float hi) {
+  unsigned d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+// Pairs of floats in one 64-bit register for the packed FP32 adder of sm_100: the reduce loops
+// are bound by instruction issue, and one add.rn.f32x2 does the work of two FADDs with the same
+// IEEE result per element.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ unsigned long long bf16x2_to_f32x2(unsigned pair) {
+  return pack_f32x2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
+}
 
 }  // namespace epx

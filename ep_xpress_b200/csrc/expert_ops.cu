@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(256) scale_rows_kernel(const unsigned short* _
           for (int q = 0; q < 4; ++q) {
             const float lo = __fmul_rn(__uint_as_float(w[q] << 16), scale);
             const float hi = __fmul_rn(__uint_as_float(w[q] & 0xffff0000u), scale);
-            w[q] = static_cast<unsigned>(float_to_bf16_bits(lo)) | (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+            w[q] = pack_bf16x2(lo, hi);
           }
           *reinterpret_cast<uint4*>(dst + i) = v[u];
         }

@@ -248,7 +248,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             lo = __uint_as_float(first[2 * i]) * scale;
             hi = __uint_as_float(first[2 * i + 1]) * scale;
           }
-          packed[i] = static_cast<unsigned>(float_to_bf16_bits(lo)) | (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+          packed[i] = pack_bf16x2(lo, hi);
         }
         uint4* dst = reinterpret_cast<uint4*>(out_row + chunk * 32);
 #pragma unroll
@@ -451,7 +451,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             lo = __uint_as_float(first[2 * i]) * scale;
             hi = __uint_as_float(first[2 * i + 1]) * scale;
           }
-          packed[i] = static_cast<unsigned>(float_to_bf16_bits(lo)) | (static_cast<unsigned>(float_to_bf16_bits(hi)) << 16);
+          packed[i] = pack_bf16x2(lo, hi);
         }
         uint4* dst = reinterpret_cast<uint4*>(out_row + chunk * 32);
 #pragma unroll
@@ -599,8 +599,7 @@ __global__ void __launch_bounds__(256) moe_slot_sum_kernel(const uint4* __restri
           unsigned out[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            out[i] = static_cast<unsigned>(float_to_bf16_bits(acc[u][2 * i])) |
-                     (static_cast<unsigned>(float_to_bf16_bits(acc[u][2 * i + 1])) << 16);
+            out[i] = pack_bf16x2(acc[u][2 * i], acc[u][2 * i + 1]);
           partial[row * vecs_per_row + at] = make_uint4(out[0], out[1], out[2], out[3]);
         }
       }
