@@ -555,6 +555,9 @@ class NVLinkContext(Context):
             return self._last_profile
 
     def read_combine_profile(self):
+        """The last completed report; never synchronises and never reads device memory."""
+        if self._profile is not None:
+            raise RuntimeError("stop the combine profile at a completed boundary before reading it")
         report = getattr(self, "_last_profile", None)
         if report is None:
             raise RuntimeError("no completed profile is available")

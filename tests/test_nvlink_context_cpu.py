@@ -247,3 +247,14 @@ def test_set_tuning_bounds_the_launch_width(ctx):
     with pytest.raises(ValueError, match="positive"):
         ctx.ep.set_tuning(items_per_cta=0)
     assert ctx.core.max_ctas == 40 and ctx.ep._failed is None      # misuse does not poison the context
+
+
+def test_profile_report_is_only_readable_at_a_completed_boundary(ctx):
+    with pytest.raises(RuntimeError, match="no completed"):
+        ctx.ep.read_combine_profile()
+    ctx.ep._profile = object()                                     # a capture is running
+    with pytest.raises(RuntimeError, match="completed boundary"):
+        ctx.ep.read_combine_profile()
+    ctx.ep._profile = None
+    ctx.ep._last_profile = {"operations": []}
+    assert ctx.ep.read_combine_profile() == {"operations": []}
