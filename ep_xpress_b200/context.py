@@ -30,6 +30,7 @@ ERROR_TEXT = {
     3: "timed out waiting for a peer",
     4: "a peer aborted the operation",
     5: "operation identity (tag or handle) mismatch between ranks",
+    6: "operation epochs are exhausted (2^31 operations ran on this context): re-create it",
 }
 
 

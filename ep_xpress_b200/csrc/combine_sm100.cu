@@ -638,6 +638,10 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
 
   profile_stamp(op.profile, 0);
   const unsigned e = ld_volatile_u32(&hdr->comb_epoch) + 1;
+  if (e > kLastEpoch) {       // epochs never wrap; uniform over the rank's CTAs
+    if (threadIdx.x == 0 && blockIdx.x == 0) report_error(c, kEpochsExhausted, kPhaseCombine, 0xE0, e);
+    return;
+  }
   // Progress words carry (epoch << 32 | rows pushed); "everything" is the largest row count.
   const unsigned long long epoch_base = static_cast<unsigned long long>(e) << 32;
   const unsigned long long all_pushed = epoch_base | 0xffffffffull;

@@ -79,6 +79,12 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
 
   profile_stamp(op.profile, 0);
   const unsigned g = ld_volatile_u32(&hdr->disp_epoch) + 1;
+  // Generations never wrap (the reference stops at 2^31 too, ep_xpress/csrc/host_sm.cu:563-567):
+  // every CTA reads the same header word, so all of them leave here together.
+  if (g > kLastEpoch) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) report_error(c, kEpochsExhausted, kPhaseDispatch, 0xE0, g);
+    return;
+  }
   const int par = static_cast<int>(g & 1u);
   const int dirty_prev = misc[kDirtyRows];
   unsigned long long* const my_cnt = reinterpret_cast<unsigned long long*>(my_heap + cl.cnt) +

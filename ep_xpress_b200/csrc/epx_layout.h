@@ -39,7 +39,9 @@ enum Status : int {
   kTimeout = 3,
   kPeerAbort = 4,
   kIdentityMismatch = 5,
+  kEpochsExhausted = 6,   // 2^31 - 1 operations of one kind ran on this context: re-create it
 };
+constexpr unsigned kLastEpoch = 0x7ffffffeu;   // generation tags compare as signed differences
 
 EPX_HD size_t align_up(size_t value, size_t alignment) {
   return (value + alignment - 1) / alignment * alignment;

@@ -144,3 +144,14 @@ def test_announced_rows_that_never_arrive_time_out_on_the_done_flag():
     status, detail, _, _ = rank.dispatch(LOCAL)
     assert status == 3 and (detail >> 32) & 0xff == 6 and usable()
     rank.close()
+
+
+def test_generations_never_wrap():
+    """At the last usable generation the kernel refuses to run instead of reusing old tags."""
+    rank = LoneRank(timeout=1.0)
+    last = 0x7FFFFFFE
+    rank.core.engine.poke_u64(0, 16, (last << 32) | last)        # disp_epoch and comb_epoch of the header
+    status, detail, dispatch_epoch, combine_epoch = rank.dispatch(LOCAL)
+    assert status == 6 and detail & 0xFFFFFFFF == last + 1
+    assert (dispatch_epoch, combine_epoch) == (last, last) and usable()
+    rank.close()
