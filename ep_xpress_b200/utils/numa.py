@@ -11,6 +11,10 @@ the reference). This module does the same with plain files and system calls:
   land there by first touch) and asks the kernel to prefer the node for its memory;
 * ``pages_by_node`` reports where the pages of an address range actually are.
 
+Containers often hide the PCI tree of sysfs; the driver still knows the topology, so when
+sysfs gives no node the ideal CPU set of the GPU is read from NVML (a read-only query) and the
+process is bound to those CPUs instead.
+
 Everything degrades to a no-op (and says so in the returned record) on machines without NUMA
 information, inside containers that hide it, or where the calls are not permitted.
 """
@@ -112,13 +116,49 @@ def bind_to_node(node: int, sysfs: str = "/sys", *, set_affinity=os.sched_setaff
     return record
 
 
-def bind_to_device(device_index: int, sysfs: str = "/sys") -> Dict[str, object]:
+def nvml_cpu_affinity(address: Optional[str], nvml=None) -> List[int]:
+    """CPUs the driver considers closest to the GPU at PCI ``address`` (empty when unknown)."""
+    if not address:
+        return []
+    try:
+        if nvml is None:
+            import pynvml as nvml
+        nvml.nvmlInit()
+        handle = nvml.nvmlDeviceGetHandleByPciBusId(address.encode() if isinstance(address, str) else address)
+        words = (os.cpu_count() or 64) // 64 + 1
+        mask = nvml.nvmlDeviceGetCpuAffinity(handle, words)
+    except Exception:
+        return []
+    return [word * 64 + bit for word, value in enumerate(mask) for bit in range(64) if (int(value) >> bit) & 1]
+
+
+def bind_to_cpus(cpus, *, set_affinity=os.sched_setaffinity, get_affinity=os.sched_getaffinity) -> Dict[str, object]:
+    """Run on ``cpus`` (within the current affinity mask); memory then follows by first touch."""
+    record: Dict[str, object] = {"node": -1, "bound": False, "cpus": 0, "memory_policy": False, "source": "nvml"}
+    chosen = sorted(set(get_affinity(0)).intersection(cpus))
+    if not chosen:
+        record["reason"] = "no CPU near the device is known, or none is in this process's affinity mask"
+        return record
+    try:
+        set_affinity(0, chosen)
+    except OSError as error:
+        record["reason"] = f"sched_setaffinity failed: {error}"
+        return record
+    record.update(bound=True, cpus=len(chosen))
+    return record
+
+
+def bind_to_device(device_index: int, sysfs: str = "/sys", *, nvml=None) -> Dict[str, object]:
     """Bind the calling process to the NUMA node of CUDA device ``device_index``.
 
     Call it before allocating pinned host memory. Returns a record for the benchmark report:
-    ``{"node", "bound", "cpus", "memory_policy"[, "reason"]}``.
+    ``{"node", "bound", "cpus", "memory_policy"[, "reason"][, "source"]}``.
     """
-    return bind_to_node(device_numa_node(device_index, sysfs), sysfs)
+    address = device_pci_address(device_index)
+    node = node_of_pci_device(address, sysfs)
+    if node >= 0:
+        return bind_to_node(node, sysfs)
+    return bind_to_cpus(nvml_cpu_affinity(address, nvml))
 
 
 def pages_by_node(address: int, maps_path: str = "/proc/self/numa_maps") -> Dict[int, int]:

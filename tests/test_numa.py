@@ -1,6 +1,7 @@
 """Host-memory placement helpers against a fake sysfs tree and fake system calls."""
 
 import os
+from unittest import mock
 
 from ep_xpress_b200.utils import numa
 
@@ -67,3 +68,34 @@ def test_prefer_node_never_raises():
     assert numa.prefer_node(-1) is False
     assert numa.prefer_node(0) in (True, False)        # allowed or refused, depending on the sandbox
     assert isinstance(os.sched_getaffinity(0), set)
+
+
+class FakeNvml:
+    def __init__(self, mask, fail=False):
+        self.mask, self.fail, self.asked = mask, fail, None
+
+    def nvmlInit(self):
+        if self.fail:
+            raise RuntimeError("no driver")
+
+    def nvmlDeviceGetHandleByPciBusId(self, address):
+        self.asked = address
+        return "handle"
+
+    def nvmlDeviceGetCpuAffinity(self, handle, words):
+        return (self.mask + [0] * words)[:words]
+
+
+def test_driver_topology_is_the_fallback_when_sysfs_is_hidden():
+    nvml = FakeNvml([0b1111 << 4, 0b1])                       # CPUs 4..7 and 64
+    with mock.patch.object(os, "cpu_count", lambda: 128):       # two mask words
+        assert numa.nvml_cpu_affinity("0000:1b:00.0", nvml) == [4, 5, 6, 7, 64]
+    assert nvml.asked == b"0000:1b:00.0"
+    assert numa.nvml_cpu_affinity(None, nvml) == []
+    assert numa.nvml_cpu_affinity("0000:1b:00.0", FakeNvml([], fail=True)) == []
+    calls = []
+    record = numa.bind_to_cpus([4, 5, 6, 7, 64], set_affinity=lambda pid, cpus: calls.append(list(cpus)),
+                               get_affinity=lambda pid: set(range(0, 8)))
+    assert calls == [[4, 5, 6, 7]] and record["bound"] and record["cpus"] == 4 and record["source"] == "nvml"
+    nothing = numa.bind_to_cpus([], set_affinity=lambda *a: calls.append("never"), get_affinity=lambda pid: {0})
+    assert not nothing["bound"] and "never" not in calls
