@@ -82,7 +82,7 @@ class SlotViews:
     output: torch.Tensor       # bf16  [tokens, hidden]
 
 
-@dataclass(repr=False)
+@dataclass(repr=False, eq=False)      # identity semantics: slots are looked up in lists
 class Slot:
     capacity: int
     tokens: int
