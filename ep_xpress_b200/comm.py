@@ -39,6 +39,13 @@ class ControlPlane:
     def barrier(self):
         self.all_gather_object(None)
 
+    def exchange(self, send, recv):
+        """Variable-size all-to-all on the current stream: ``send[r]`` goes to rank r,
+        ``recv[r]`` is filled by rank r. Contiguous tensors of any dtype; the sizes must match
+        pairwise, which the caller arranges with a fixed-size exchange of counts first. Only the
+        multi-node transport moves payload this way."""
+        raise NotImplementedError
+
 
 class GroupControlPlane(ControlPlane):
     """Control plane over an existing torch.distributed group of any backend."""
@@ -56,9 +63,25 @@ class GroupControlPlane(ControlPlane):
         dist.all_gather_object(gathered, value, group=self.group)
         return gathered
 
+    def exchange(self, send, recv):
+        recv[self.rank].copy_(send[self.rank])
+        ranks = dist.get_process_group_ranks(self.group)
+        operations = []
+        for peer in range(self.world_size):
+            if peer == self.rank:
+                continue
+            if send[peer].numel():
+                operations.append(dist.P2POp(dist.isend, send[peer], ranks[peer], group=self.group))
+            if recv[peer].numel():
+                operations.append(dist.P2POp(dist.irecv, recv[peer], ranks[peer], group=self.group))
+        if operations:
+            for work in dist.batch_isend_irecv(operations):
+                work.wait()
+
 
 class _NcclApi:
-    """The four NCCL entry points used, resolved from the owner's library only."""
+    """The NCCL entry points used, resolved from the owner's library only: three queries and
+    ncclAllGather for the bootstrap, grouped ncclSend/ncclRecv for the multi-node transport."""
 
     def __init__(self, library_path):
         self._dso = ctypes.CDLL(str(library_path))
@@ -86,6 +109,30 @@ class _NcclApi:
 
     def all_gather_bytes(self, comm, send, recv, count, stream):
         self._ok(self._all_gather(send, recv, count, _NCCL_UINT8, comm, stream))
+
+    def _point_to_point(self):
+        if not hasattr(self, "_send"):
+            void_p, c_int = ctypes.c_void_p, ctypes.c_int
+            for attribute, name in (("_send", "ncclSend"), ("_recv", "ncclRecv")):
+                fn = getattr(self._dso, name)
+                fn.argtypes, fn.restype = [void_p, ctypes.c_size_t, c_int, c_int, void_p, void_p], c_int
+                setattr(self, attribute, fn)
+            for attribute, name in (("_group_start", "ncclGroupStart"), ("_group_end", "ncclGroupEnd")):
+                fn = getattr(self._dso, name)
+                fn.argtypes, fn.restype = [], c_int
+                setattr(self, attribute, fn)
+
+    def exchange_bytes(self, comm, sends, recvs, stream):
+        """``sends`` / ``recvs``: (pointer, bytes, peer) triples, one NCCL group for all of them."""
+        self._point_to_point()
+        self._ok(self._group_start())
+        try:
+            for pointer, count, peer in sends:
+                self._ok(self._send(pointer, count, _NCCL_UINT8, peer, comm, stream))
+            for pointer, count, peer in recvs:
+                self._ok(self._recv(pointer, count, _NCCL_UINT8, peer, comm, stream))
+        finally:
+            self._ok(self._group_end())
 
 
 class NCCLCommHandle(ControlPlane):
@@ -167,6 +214,20 @@ class NCCLCommHandle(ControlPlane):
             staged[:len(blob)] = torch.frombuffer(bytearray(blob), dtype=torch.uint8)
             rows = self._gather(staged.to(self.device)).cpu()
         return [pickle.loads(rows[r, :sizes[r]].numpy().tobytes()) for r in range(self.world_size)]
+
+    def exchange(self, send, recv):
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device)
+            recv[self.rank].copy_(send[self.rank])
+            sends = [(t.data_ptr(), t.numel() * t.element_size(), peer) for peer, t in enumerate(send)
+                     if peer != self.rank and t.numel()]
+            recvs = [(t.data_ptr(), t.numel() * t.element_size(), peer) for peer, t in enumerate(recv)
+                     if peer != self.rank and t.numel()]
+            for tensor in list(send) + list(recv):
+                if not tensor.is_contiguous() or tensor.device != self.device:
+                    raise ValueError("exchange needs contiguous tensors on the communicator's device")
+            if sends or recvs:
+                self._api.exchange_bytes(self._pointer, sends, recvs, stream.cuda_stream)
 
     def barrier(self):
         """Teardown rendezvous, outside the token data path."""

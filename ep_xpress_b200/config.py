@@ -61,11 +61,18 @@ class Config:
     # --- NVLink transport -------------------------------------------------
     gpu_pool_budget_bytes: int = 16 << 30     # bound of the peer-mapped heap of one rank
     workspace_pool_bytes: int = 0             # heap reserve for create_workspace; 0 = two more slots
-    combine_rounding: str = "two_step"        # "two_step" (single-node reference) or "single" (multi-node reference)
+    combine_rounding: str = "auto"            # "two_step" (single-node reference), "single" (multi-node reference); auto: by transport
     zero_padding: bool = True                 # keep activation rows above valid_count at zero
     cooperative_launch: bool = True           # driver-guaranteed co-residency of the transport CTAs
     debug_delay_ns: int = 0                   # debugging: random sleeps below this bound at kernel phase boundaries
     combine_streaming: str = "auto"           # reduce while peers still push: "on"; "off"/"auto": push, then reduce
+
+    @property
+    def single_rounding(self) -> bool:
+        """One rounding over all ranks (the multi-node formula) instead of remote-sum, round, add local, round."""
+        if self.combine_rounding == "auto":
+            return self.internode_transport == "gin"
+        return self.combine_rounding == "single"
 
     @property
     def device_transport(self) -> bool:
@@ -117,8 +124,8 @@ class Config:
             raise ValueError("workload must be auto, prefill, or decode")
         if self.transport not in _TRANSPORTS:
             raise NotImplementedError("transport must be nvlink, host_sm or host_ce")
-        if self.combine_rounding not in ("two_step", "single"):
-            raise ValueError("combine_rounding must be two_step or single")
+        if self.combine_rounding not in ("auto", "two_step", "single"):
+            raise ValueError("combine_rounding must be auto, two_step or single")
         if not _is_int(self.debug_delay_ns) or not 0 <= self.debug_delay_ns <= 1_000_000:
             raise ValueError("debug_delay_ns must be an integer in [0, 1000000]")
         if self.combine_streaming not in ("auto", "on", "off"):

@@ -127,8 +127,8 @@ class Context:
             if not isinstance(config, Config):
                 raise TypeError("config must be an ep_xpress_b200.Config")
             if config.internode_transport == "gin":
-                raise NotImplementedError(
-                    "the GIN multi-node transport needs a second node; this library targets one NVLink domain")
+                from .parallel.multinode import MultiNodeContext
+                return object.__new__(MultiNodeContext)
             if config.device_transport:
                 from .parallel.nvlink import NVLinkContext
                 return object.__new__(NVLinkContext)

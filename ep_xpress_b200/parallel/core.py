@@ -106,7 +106,7 @@ class TransportCore:
         self.hidden, self.topk = config.hidden_size, config.topk
         self.engine = native.Engine(world, self.local_ranks, self.hidden, self.topk, list(expert_to_rank),
                                     [list(map(int, row)) for row in heaps], float(config.timeout_seconds),
-                                    config.combine_rounding == "single", self.device.index,
+                                    config.single_rounding, self.device.index,
                                     bool(config.cooperative_launch))
         self.engine.set_combine_streaming({"auto": -1, "off": 0, "on": 1}[config.combine_streaming])
         if config.debug_delay_ns:

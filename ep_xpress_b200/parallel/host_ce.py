@@ -318,7 +318,7 @@ class HostCEContext(Context):
             token_order[dest] = tokens[torch.argsort(rows[tokens])]
         received, metrics = self._exchange("combine", operation, partial_cpu, send_masks, recv_plan)
         tokens_here = plan.token_counts[self.rank]
-        single = cfg.combine_rounding == "single"
+        single = cfg.single_rounding
         remote = torch.zeros((tokens_here, cfg.hidden_size), dtype=torch.float32)
         local = torch.zeros((tokens_here, cfg.hidden_size), dtype=torch.float32)
         for dest in range(self.world_size):                    # ascending rank order

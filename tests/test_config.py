@@ -66,11 +66,14 @@ def test_host_ce_allows_odd_hidden_and_reports_host_pool():
     assert Config(hidden_size=64, topk=2, max_tokens_per_rank=8).pool_bytes(4) == 0
 
 
-def test_gin_is_gated_at_context_creation():
+def test_gin_selects_the_multinode_context_and_single_rounding():
     from ep_xpress_b200 import Context
     cfg = Config(hidden_size=64, topk=2, max_tokens_per_rank=8, transport="host_sm", internode_transport="gin")
-    with pytest.raises(NotImplementedError, match="second node"):
-        Context(None, [0], cfg)
+    assert cfg.single_rounding and not Config(hidden_size=64, topk=2, max_tokens_per_rank=8).single_rounding
+    assert not Config(hidden_size=64, topk=2, max_tokens_per_rank=8, transport="host_sm", internode_transport="gin",
+                      combine_rounding="two_step").single_rounding
+    with pytest.raises(TypeError, match="NCCLCommHandle"):
+        Context(None, [0], cfg)                                     # the multi-node context checks its communicator
 
 
 def test_multinode_sizing_helpers_follow_the_record_layout():
