@@ -55,3 +55,31 @@ def test_invalid_rank_from_the_library_is_rejected():
     with mock.patch.object(comm_module, "_NcclApi", Broken):
         with pytest.raises(ValueError, match="invalid NCCL communicator"):
             NCCLCommHandle.borrow(99, owner=object(), library_path="x")
+
+
+class FakeFunction:
+    def __init__(self, log, name, result=0):
+        self.log, self.name, self.result = log, name, result
+        self.argtypes, self.restype = None, None
+
+    def __call__(self, *args):
+        self.log.append((self.name,) + args)
+        return self.result
+
+
+def test_point_to_point_exchange_is_one_nccl_group():
+    log = []
+    api = object.__new__(comm_module._NcclApi)
+    api._dso = type("Dso", (), {name: FakeFunction(log, name) for name in
+                                ("ncclSend", "ncclRecv", "ncclGroupStart", "ncclGroupEnd")})()
+    api._error_string = lambda code: b"boom"
+    api.exchange_bytes(77, sends=[(1000, 16, 2), (2000, 32, 3)], recvs=[(3000, 8, 2)], stream=5)
+    assert [entry[0] for entry in log] == ["ncclGroupStart", "ncclSend", "ncclSend", "ncclRecv", "ncclGroupEnd"]
+    assert log[1] == ("ncclSend", 1000, 16, 1, 2, 77, 5)          # bytes as ncclUint8, to peer 2
+    assert log[3] == ("ncclRecv", 3000, 8, 1, 2, 77, 5)
+    # a failing call still closes the group, then raises
+    log.clear()
+    api._dso.ncclRecv.result = 3
+    with pytest.raises(RuntimeError, match="boom"):
+        api.exchange_bytes(77, sends=[], recvs=[(3000, 8, 2)], stream=5)
+    assert log[-1][0] == "ncclGroupEnd"
