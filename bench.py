@@ -1,4 +1,5 @@
-"""Headline benchmark: one MoE layer's expert-parallel communication step.
+"""Headline benchmark: one MoE layer's expert-parallel communication step (the quantity the
+reference's benchmarks/communication.py:137-276 measures: dispatch + synthetic expert + combine).
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \

@@ -1,4 +1,5 @@
-"""Full MoE layer: dispatch -> tcgen05 grouped SwiGLU experts -> combine.
+"""Full MoE layer: dispatch -> tcgen05 grouped SwiGLU experts -> combine (the reference measures
+this level only inside a serving framework, docs/model-performance.md of the reference).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29503 -m benchmarks.moe_layer --tokens 128 4096 [--baseline]

@@ -1,3 +1,6 @@
+// Registry of this process's peer-mapped heaps: allocation, CUDA IPC export/open, and bounds
+// checks of every range a launch is given. Plays the role of the reference's overlap-checked
+// registry of cudaHostRegister'ed ranges (ep_xpress/csrc/bindings.cpp:39-99) for device memory.
 #include "heap.h"
 
 #include <cuda_runtime.h>

@@ -1,4 +1,6 @@
 // Python bindings of the grouped SwiGLU expert runner.
+// (Python face of the expert runner; counterpart of fused_experts_valid_count,
+// ep_xpress/adapters/sglang_valid.py:233-255.)
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>

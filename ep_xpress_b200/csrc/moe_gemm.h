@@ -1,4 +1,10 @@
 // Host API of the grouped SwiGLU expert runner (plain C++, no torch types).
+//
+// The stages replace what the reference borrows from its serving framework and patches for a
+// device-resident row count: route alignment (ep_xpress/adapters/sglang_valid.py:13-161), the
+// grouped GEMMs with SiLU-and-mul in between (sglang_valid.py:233-255 and the act_and_mul patch,
+// ep_xpress/adapters/sglang/sglang-v0.5.21.patch:281-330) and the slot-order FP32 sum with one
+// BF16 rounding (sglang_valid.py:206-222).
 #pragma once
 #include <cuda_runtime.h>
 

@@ -1,4 +1,11 @@
-"""A full expert-parallel MoE layer: dispatch -> grouped SwiGLU experts -> combine."""
+"""A full expert-parallel MoE layer: dispatch -> grouped SwiGLU experts -> combine.
+
+The reference leaves the experts to its serving framework and only adapts that framework's
+fused-experts call to the device-resident row count
+(ep_xpress/adapters/sglang_valid.py:233-255, ``fused_experts_valid_count``); here the layer is
+part of the library, with the same contract: rows at or above ``valid_count`` and slots with
+id -1 cost nothing and contribute nothing.
+"""
 
 from __future__ import annotations
 
