@@ -13,6 +13,7 @@ host_sm.py:809-830).
 
 from __future__ import annotations
 
+import contextlib
 import hashlib
 import json
 import socket
@@ -72,6 +73,7 @@ class Workspace:
         self.count = views.count
         self.output = views.output[:local_tokens]
         self.expected_ranks = views.mask[:local_tokens]
+        self.dest_rows = views.dest_rows[:local_tokens]
         self._generation = 0
         self._busy = False
         self._consumers = []
@@ -414,7 +416,7 @@ class NVLinkContext(Context):
                     "dispatch", self._counter, tag, x.shape[0], capacity, ctas)
                 if profile is None and capturing:
                     profile = self._decode_slice("dispatch", ctas)
-                with torch.cuda.stream(execution), torch.no_grad():
+                with self._on(execution, stream, same_stream):
                     if not same_stream:
                         for tensor in (x, ids, weights):
                             tensor.record_stream(execution)
@@ -426,16 +428,34 @@ class NVLinkContext(Context):
             slot.busy = True
             slot.generation += 1
             views = slot.views[0]
-            route = _DeviceRoute(slot, views.inverse[:capacity], views.count, channels, ctas,
-                                 views.mask[:x.shape[0]], views.dest_rows[:x.shape[0]], workspace, capacity,
-                                 fused_combine)
-            handle = RouteHandle(self._id, self._counter, route, x.shape[0], capacity, tag)
-            batch = DispatchBatch(views.hidden[:capacity], views.local_ids[:capacity], views.weights[:capacity],
-                                  handle, views.count)
+            if workspace is not None:
+                # A workspace has exactly this shape: its views were cut once, at creation
+                # (slicing six tensors costs more host time than the rest of the call).
+                route = _DeviceRoute(slot, workspace.inverse, views.count, channels, ctas, workspace.expected_ranks,
+                                     workspace.dest_rows, workspace, capacity, fused_combine)
+                handle = RouteHandle(self._id, self._counter, route, x.shape[0], capacity, tag)
+                batch = DispatchBatch(workspace.hidden, workspace.local_ids, workspace.weights, handle, views.count)
+            else:
+                route = _DeviceRoute(slot, views.inverse[:capacity], views.count, channels, ctas,
+                                     views.mask[:x.shape[0]], views.dest_rows[:x.shape[0]], workspace, capacity,
+                                     fused_combine)
+                handle = RouteHandle(self._id, self._counter, route, x.shape[0], capacity, tag)
+                batch = DispatchBatch(views.hidden[:capacity], views.local_ids[:capacity], views.weights[:capacity],
+                                      handle, views.count)
             if same_stream:
                 return batch
             return self._finish(batch, workspace, metrics={"ctas": ctas, "active_channels": channels,
                                                            "recv_capacity": capacity})
+
+    @staticmethod
+    def _on(execution, requested, same_stream):
+        """Make ``execution`` the current stream for the torch allocations and copies of an
+        operation - unless it already is (a direct call on the caller's current stream), where
+        entering the context would only cost host time. Inputs are inference tensors and the
+        kernels are launched outside autograd, so no grad mode is touched."""
+        if same_stream and requested is None:
+            return contextlib.nullcontext()
+        return torch.cuda.stream(execution)
 
     def _finish(self, value, workspace=None, tensors=(), metrics=None):
         completed = torch.cuda.Event()
@@ -498,7 +518,7 @@ class NVLinkContext(Context):
                 self._begin(execution, capturing=capturing)
                 if not same_stream:
                     execution.wait_stream(producer)
-                with torch.cuda.stream(execution), torch.no_grad():
+                with self._on(execution, stream, same_stream):
                     source = partial if partial.is_contiguous() else partial.contiguous()
                     if not same_stream:
                         source.record_stream(execution)
