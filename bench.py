@@ -34,7 +34,6 @@ import json
 import os
 import statistics
 import sys
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)

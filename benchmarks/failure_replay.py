@@ -16,7 +16,6 @@ import os
 import sys
 import time
 
-import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))

@@ -23,7 +23,7 @@ from dataclasses import asdict, dataclass
 
 import torch
 
-from ..comm import ControlPlane, NCCLCommHandle
+from ..comm import ControlPlane
 from ..config import Config
 from ..context import ERROR_TEXT, Context, DispatchBatch, Pending, RouteHandle
 from .core import Slot, TransportCore

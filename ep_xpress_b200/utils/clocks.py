@@ -4,7 +4,6 @@ from __future__ import annotations
 
 import statistics
 import threading
-import time
 
 _REASONS = {
     "sw_power_cap": 0x4,
