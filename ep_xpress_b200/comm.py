@@ -148,43 +148,46 @@ class NCCLCommHandle(ControlPlane):
 
     @classmethod
     def borrow(cls, pointer, *, owner, library_path, group=None):
-        """Wrap an existing communicator using its owner's NCCL library.
+        """Wrap a communicator that somebody else created, resolving NCCL from THEIR library.
 
-        ``group``, when given, must describe the same ordered ranks. The
-        communicator must be in NCCL's normal blocking mode.
+        ``owner`` is whatever keeps the communicator alive (a process group, a framework object);
+        the handle holds a reference to it and never destroys anything. ``group``, when given,
+        must be the torch.distributed group with the same ordered ranks. The communicator has to
+        be in NCCL's blocking mode.
         """
-        if isinstance(pointer, ctypes.c_void_p):
-            pointer = pointer.value
-        if isinstance(pointer, bool) or not isinstance(pointer, int) or pointer <= 0:
-            raise ValueError("a non-null NCCL communicator pointer is required")
+        address = pointer.value if isinstance(pointer, ctypes.c_void_p) else pointer
+        if type(address) is not int or address <= 0:
+            raise ValueError("borrow() needs the non-null address of an ncclComm_t")
         if owner is None:
-            raise ValueError("a borrowed communicator requires a lifetime owner")
-        self = object.__new__(cls)
-        self._owner = owner
-        self._pointer = pointer
-        self._api = _NcclApi(library_path)
-        self.group = group
-        self.rank = self._api.integer("ncclCommUserRank", pointer)
-        self.world_size = self._api.integer("ncclCommCount", pointer)
-        self.device = torch.device("cuda", self._api.integer("ncclCommCuDevice", pointer))
-        if not 0 <= self.rank < self.world_size:
-            raise ValueError("invalid NCCL communicator rank or size")
+            raise ValueError("borrow() needs a lifetime owner: the object that keeps the communicator alive")
+        handle = object.__new__(cls)
+        handle._owner, handle._pointer, handle.group = owner, address, group
+        handle._api = api = _NcclApi(library_path)
+        rank, size = api.integer("ncclCommUserRank", address), api.integer("ncclCommCount", address)
+        if size < 1 or rank < 0 or rank >= size:
+            raise ValueError(f"invalid NCCL communicator: rank {rank} of {size}")
+        handle.rank, handle.world_size = rank, size
+        handle.device = torch.device("cuda", api.integer("ncclCommCuDevice", address))
         if group is not None:
-            self.validate_group(group)
-        return self
+            handle.validate_group(group)
+        return handle
 
     def get(self):
         """The borrowed raw pointer; no collective, no CUDA call."""
         return self._pointer
 
     def validate_group(self, group):
+        """``group`` must describe the ranks of this communicator, in the same order."""
         if not dist.is_initialized():
-            raise RuntimeError("initialize the supplied process group first")
-        if (dist.get_rank(group), dist.get_world_size(group)) != (self.rank, self.world_size):
-            raise ValueError("NCCL communicator and process group ranks do not match")
-        if self.group is not None and self.group is not group and \
-                dist.get_process_group_ranks(group) != dist.get_process_group_ranks(self.group):
-            raise ValueError("NCCL communicator and process group membership do not match")
+            raise RuntimeError("the process group given to the handle is not initialised")
+        described = (dist.get_rank(group), dist.get_world_size(group))
+        if described != (self.rank, self.world_size):
+            raise ValueError(f"the process group says rank {described[0]} of {described[1]}, the communicator "
+                             f"rank {self.rank} of {self.world_size}")
+        known = self.group
+        if known is not None and known is not group:
+            if dist.get_process_group_ranks(group) != dist.get_process_group_ranks(known):
+                raise ValueError("the process group has other members than the communicator's own group")
 
     def _gather(self, payload: torch.Tensor) -> torch.Tensor:
         # Both buffers are allocated on the current stream, so the upload above
@@ -243,41 +246,50 @@ _live_handles = weakref.WeakValueDictionary()
 _warmed = weakref.WeakKeyDictionary()
 
 
-def get_nccl_comm_handle(group=None, device=None):
-    """Borrow the communicator of a PyTorch NCCL process group.
+def _cuda_device(device):
+    """``None`` / index / ``"cuda"`` / ``"cuda:N"`` -> a fully indexed CUDA device."""
+    if device is None:
+        return torch.device("cuda", torch.cuda.current_device())
+    chosen = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+    if chosen.type != "cuda":
+        raise ValueError(f"an NCCL communicator lives on a CUDA device, not on {chosen}")
+    return chosen if chosen.index is not None else torch.device("cuda", torch.cuda.current_device())
 
-    Collective on first use per (group, device): it makes PyTorch create its
-    lazy communicator with one tiny all-reduce, then reads ``_comm_ptr()``.
-    Call it before CUDA Graph capture.
+
+def get_nccl_comm_handle(group=None, device=None):
+    """Borrow the communicator PyTorch built for an NCCL process group.
+
+    PyTorch creates that communicator lazily, so the first call per (group, device) runs one
+    tiny all-reduce - a collective: call it on every rank, and before any CUDA Graph capture.
+    Later calls return the cached handle without communicating, also after the handle object
+    was garbage-collected on some ranks only.
     """
     if not dist.is_initialized():
         raise RuntimeError("initialize the NCCL process group first")
-    group = dist.group.WORLD if group is None else group
-    if str(dist.get_backend(group)) != "nccl":
-        raise ValueError("get_nccl_comm_handle requires an NCCL process group")
-    wanted = torch.cuda.current_device() if device is None else device
-    wanted = torch.device("cuda", wanted) if isinstance(wanted, int) else torch.device(wanted)
-    if wanted.type != "cuda":
-        raise ValueError("NCCL communicator device must be CUDA")
-    device = torch.device("cuda", torch.cuda.current_device() if wanted.index is None else wanted.index)
-    key = (group, device)
-    cached = _live_handles.get(key)
-    if cached is not None:
-        return cached
+    group = group if group is not None else dist.group.WORLD
+    backend_name = str(dist.get_backend(group))
+    if backend_name != "nccl":
+        raise ValueError(f"the group's backend is {backend_name}; only an NCCL group has a communicator to borrow")
+    device = _cuda_device(device)
+    handle = _live_handles.get((group, device))
+    if handle is not None:
+        return handle
     backend = group._get_backend(device)
-    if not callable(getattr(backend, "_comm_ptr", None)):
-        raise RuntimeError("PyTorch does not expose _comm_ptr(); obtain an NCCLCommHandle.borrow() "
-                           "from the framework before constructing Context")
+    pointer_of = getattr(backend, "_comm_ptr", None)
+    if not callable(pointer_of):
+        raise RuntimeError("this PyTorch build has no ProcessGroupNCCL._comm_ptr(); get the raw communicator from "
+                           "your framework and pass it to NCCLCommHandle.borrow()")
     with torch.cuda.device(device):
         if torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("obtain the NCCL communicator before CUDA Graph capture")
-        if device not in _warmed.get(group, ()):
+            raise RuntimeError("get_nccl_comm_handle() communicates: call it before CUDA Graph capture starts")
+        warmed = _warmed.setdefault(group, set())
+        if device not in warmed:
             dist.all_reduce(torch.zeros(1, device=device), group=group)
             torch.cuda.current_stream(device).synchronize()
-            _warmed.setdefault(group, set()).add(device)
-        library = Path(torch.__file__).resolve().parent / "lib" / "libtorch_cuda.so"
-        handle = NCCLCommHandle.borrow(backend._comm_ptr(), owner=group, group=group, library_path=library)
+            warmed.add(device)
+        torch_nccl = Path(torch.__file__).resolve().parent / "lib" / "libtorch_cuda.so"
+        handle = NCCLCommHandle.borrow(pointer_of(), owner=group, group=group, library_path=torch_nccl)
     if handle.device != device:
-        raise ValueError("the process group's NCCL communicator is bound to another CUDA device")
-    _live_handles[key] = handle
+        raise ValueError(f"the group's communicator belongs to {handle.device}, not to {device}")
+    _live_handles[(group, device)] = handle
     return handle

@@ -131,12 +131,17 @@ class Config:
         if self.combine_streaming not in ("auto", "on", "off"):
             raise ValueError("combine_streaming must be auto, on or off")
         if device:
-            if self.hidden_size % 2 or self.hidden_size > (1 << 31) - 1:
-                raise ValueError("host_sm requires an even hidden size that fits int32")
-            if self.topk > 256 or self.slots > 64 or self.chunk_rows > 65536:
-                raise ValueError("host_sm supports topk <= 256, slots <= 64 and chunk_rows <= 65536")
-            if self.timeout_seconds > 3600 or self.max_tokens_per_rank > (1 << 31) - 1:
-                raise ValueError("host_sm timeout must be <= 3600 seconds and token capacity must fit int32")
+            # Limits of the device kernels: rows are moved as BF16 pairs, row indices and byte
+            # offsets are 32-bit in places, waits are timed in 64-bit nanoseconds.
+            int32_max = (1 << 31) - 1
+            limits = (("topk <= 256", self.topk <= 256), ("slots <= 64", self.slots <= 64),
+                      ("chunk_rows <= 65536", self.chunk_rows <= 65536),
+                      ("an even hidden size below 2^31", self.hidden_size % 2 == 0 and self.hidden_size <= int32_max),
+                      ("timeout_seconds <= 3600", self.timeout_seconds <= 3600),
+                      ("max_tokens_per_rank below 2^31", self.max_tokens_per_rank <= int32_max))
+            broken = [rule for rule, holds in limits if not holds]
+            if broken:
+                raise ValueError("the device transports need " + ", ".join(broken))
         if self.combine_backend != "gpu":
             raise NotImplementedError("this release implements GPU combine only")
         if self.graph_mode != "eager":

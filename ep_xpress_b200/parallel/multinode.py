@@ -148,14 +148,20 @@ class MultiNodeContext(Context):
         self._failed = error
         return error
 
-    def _tensor(self, value, dtype, shape, name):
-        if not isinstance(value, torch.Tensor) or value.device != self.device:
-            raise ValueError(name + " must be a tensor on the context device")
-        if value.dtype != dtype or tuple(value.shape) != tuple(shape):
-            raise ValueError(name + " has invalid shape or dtype")
-        if value.requires_grad:
-            raise ValueError("EP-Xpress accepts inference tensors only")
-        return value.contiguous()
+    def _input(self, what, value, dtype, *shape):
+        """A contiguous inference tensor of exactly this dtype and shape on the context device."""
+        problem = None
+        if not isinstance(value, torch.Tensor):
+            problem = "is not a tensor"
+        elif value.device != self.device:
+            problem = f"lives on {value.device}, the context on {self.device}"
+        elif value.dtype != dtype or value.shape != torch.Size(shape):
+            problem = f"is {value.dtype} {tuple(value.shape)}, expected {dtype} {shape}"
+        elif value.requires_grad:
+            problem = "requires grad; only inference tensors are accepted"
+        if problem:
+            raise ValueError(f"{what} {problem}")
+        return value if value.is_contiguous() else value.contiguous()
 
     def _exchange_counts(self, row: torch.Tensor) -> torch.Tensor:
         """Everybody's row of int64 values: the result is the [world, len(row)] matrix."""
@@ -166,12 +172,13 @@ class MultiNodeContext(Context):
 
     # ---------------------------------------------------------------- workspaces
     def create_workspace(self, recv_capacity, local_tokens, *, fused_combine=False):
-        for value, limit in ((recv_capacity, self.world_size * self.config.max_tokens_per_rank),
-                             (local_tokens, self.config.max_tokens_per_rank)):
-            if isinstance(value, bool) or not isinstance(value, int) or not 0 <= value <= limit:
-                raise ValueError("invalid workspace capacity")
+        bounds = {"recv_capacity": (recv_capacity, self.world_size * self.config.max_tokens_per_rank),
+                  "local_tokens": (local_tokens, self.config.max_tokens_per_rank)}
+        for name, (value, limit) in bounds.items():
+            if type(value) is not int or value < 0 or value > limit:
+                raise ValueError(f"invalid workspace capacity: {name} must be an integer in [0, {limit}]")
         if self.device.type == "cuda" and torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("allocate workspaces before capture")
+            raise RuntimeError("workspaces are allocated outside CUDA Graph capture")
         return MultiNodeWorkspace(self, recv_capacity, local_tokens, fused_combine)
 
     # ------------------------------------------------------------------ dispatch
@@ -196,11 +203,11 @@ class MultiNodeContext(Context):
             if (not isinstance(workspace, MultiNodeWorkspace) or workspace.context_id != self._id or
                     workspace.recv_capacity != capacity or workspace.local_tokens != n or workspace.busy):
                 raise ValueError("workspace ownership, capacity or lifetime mismatch")
-            hidden = self._tensor(x, torch.bfloat16, (n, cfg.hidden_size), "hidden")
+            hidden = self._input("hidden", x, torch.bfloat16, n, cfg.hidden_size)
             if not isinstance(topk_ids, torch.Tensor) or topk_ids.dtype not in (torch.int32, torch.int64):
                 raise ValueError("topk_ids must be int32 or int64")
-            ids = self._tensor(topk_ids, topk_ids.dtype, (n, cfg.topk), "topk_ids").to(torch.int64)
-            weights = self._tensor(topk_weights, torch.float32, (n, cfg.topk), "topk_weights")
+            ids = self._input("topk_ids", topk_ids, topk_ids.dtype, n, cfg.topk).to(torch.int64)
+            weights = self._input("topk_weights", topk_weights, torch.float32, n, cfg.topk)
 
             # ---- route: destination columns, validation ------------------------------------
             experts = len(self.expert_to_rank)

@@ -350,12 +350,15 @@ class NVLinkContext(Context):
 
     # ------------------------------------------------------------------ dispatch
     def _validate_dispatch(self, x, ids, weights):
-        if not all(isinstance(t, torch.Tensor) for t in (x, ids, weights)):
-            raise ValueError("dispatch inputs must be tensors")
-        if x.ndim != 2 or x.shape[0] > self.config.max_tokens_per_rank:
-            raise ValueError("x must be [tokens, hidden] within the configured token capacity")
+        """Host-side checks only: shapes, dtypes and devices are checked again by the engine."""
+        for name, tensor in (("x", x), ("topk_ids", ids), ("topk_weights", weights)):
+            if not isinstance(tensor, torch.Tensor):
+                raise ValueError(f"dispatch inputs must be tensors ({name} is {type(tensor).__name__})")
+        limit = self.config.max_tokens_per_rank
+        if x.ndim != 2 or x.shape[0] > limit:
+            raise ValueError(f"x must be [tokens, hidden] within the configured token capacity of {limit}")
         if x.requires_grad or weights.requires_grad:
-            raise ValueError("dispatch accepts inference tensors only")
+            raise ValueError("dispatch accepts inference tensors only (requires_grad is set)")
 
     def dispatch_on_stream(self, x, topk_ids, topk_weights, tag=None, stream=None, recv_capacity=None,
                            active_channels=None, workspace=None, fused_combine=False):
@@ -380,11 +383,13 @@ class NVLinkContext(Context):
             if workspace is not None:
                 if not isinstance(workspace, Workspace) or workspace._context_id != self._id:
                     raise ValueError("workspace belongs to another context")
-                if (workspace.recv_capacity, workspace.local_tokens, workspace.fused_combine) != (
-                        capacity, x.shape[0], fused_combine):
-                    raise ValueError("workspace shape or fused combine mode does not match dispatch")
+                wanted = (capacity, x.shape[0], fused_combine)
+                if wanted != (workspace.recv_capacity, workspace.local_tokens, workspace.fused_combine):
+                    raise ValueError(f"workspace shape or fused combine mode does not match dispatch: the dispatch "
+                                     f"needs (capacity, tokens, fused) = {wanted}")
                 if workspace._busy:
-                    raise RuntimeError("wait on the previous workspace combine before reusing it")
+                    raise RuntimeError("this workspace still holds a dispatch without its combine: wait on the "
+                                       "previous workspace combine before reusing it")
             channels = self.effective_channels if active_channels is None else active_channels
             if isinstance(channels, bool) or not isinstance(channels, int) or \
                     not 1 <= channels <= self.effective_channels:
@@ -495,16 +500,17 @@ class NVLinkContext(Context):
     def _combine(self, partial, handle, tag, stream, weights_applied, *, same_stream):
         with self._lock, torch.cuda.device(self.device):
             self._check_usable()
-            if weights_applied is not True:
-                raise ValueError("combine accepts already-weighted rank partials only")
-            if not isinstance(handle, RouteHandle) or handle._context_id != self._id:
+            mine = isinstance(handle, RouteHandle) and handle._context_id == self._id
+            if not mine:
                 raise ValueError("handle belongs to another context")
             if handle._consumed:
                 raise ValueError("handle has already been consumed by combine")
+            if weights_applied is not True:
+                raise ValueError("combine accepts already-weighted rank partials only")
             if not isinstance(partial, torch.Tensor) or partial.requires_grad:
                 raise ValueError("partial must be an inference tensor")
-            if partial.ndim != 2 or partial.shape[1] != self.config.hidden_size or \
-                    partial.dtype != torch.bfloat16 or partial.shape[0] > handle.received_count:
+            rows_ok = partial.ndim == 2 and partial.shape[0] <= handle.received_count
+            if not rows_ok or partial.shape[1] != self.config.hidden_size or partial.dtype != torch.bfloat16:
                 raise ValueError("partial must be BF16 [rows <= capacity, hidden]")
             if not same_stream and self._pending >= self.config.max_pending_operations:
                 raise RuntimeError("too many pending operations; wait on earlier tickets first")

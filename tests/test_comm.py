@@ -83,3 +83,46 @@ def test_point_to_point_exchange_is_one_nccl_group():
     with pytest.raises(RuntimeError, match="boom"):
         api.exchange_bytes(77, sends=[], recvs=[(3000, 8, 2)], stream=5)
     assert log[-1][0] == "ncclGroupEnd"
+
+
+def test_get_handle_warms_up_once_and_caches(monkeypatch):
+    import contextlib
+    import torch
+    import torch.distributed as dist
+
+    class Backend:
+        def _comm_ptr(self):
+            return 4321
+
+    class Group:
+        def _get_backend(self, device):
+            return Backend()
+
+    group, reductions = Group(), []
+    monkeypatch.setattr(comm_module, "_NcclApi", FakeApi)
+    monkeypatch.setattr(dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(dist, "get_backend", lambda g: "nccl")
+    monkeypatch.setattr(dist, "get_rank", lambda g=None: 1)
+    monkeypatch.setattr(dist, "get_world_size", lambda g=None: 4)
+    monkeypatch.setattr(dist, "all_reduce", lambda tensor, group=None: reductions.append(group))
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    monkeypatch.setattr(torch.cuda, "device", lambda d: contextlib.nullcontext())
+    monkeypatch.setattr(torch.cuda, "is_current_stream_capturing", lambda: False)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda d=None: mock.Mock())
+    monkeypatch.setattr(torch, "zeros", lambda *shape, device=None: None)
+    handle = comm_module.get_nccl_comm_handle(group)
+    assert (handle.rank, handle.world_size, handle.get(), str(handle.device)) == (1, 4, 4321, "cuda:0")
+    assert handle._owner is group and reductions == [group]
+    assert comm_module.get_nccl_comm_handle(group, device="cuda") is handle and reductions == [group]
+    del handle                                               # collected here, maybe not on other ranks:
+    again = comm_module.get_nccl_comm_handle(group, 0)       # a new handle, but no second collective
+    assert again.get() == 4321 and reductions == [group]
+    with pytest.raises(ValueError, match="CUDA device"):
+        comm_module.get_nccl_comm_handle(group, "cpu")
+    monkeypatch.setattr(dist, "get_backend", lambda g: "gloo")
+    with pytest.raises(ValueError, match="only an NCCL group"):
+        comm_module.get_nccl_comm_handle(Group())
+    monkeypatch.setattr(dist, "get_backend", lambda g: "nccl")
+    monkeypatch.setattr(dist, "get_rank", lambda g=None: 0)
+    with pytest.raises(ValueError, match="process group says rank 0 of 4"):
+        comm_module.get_nccl_comm_handle(Group())
