@@ -25,6 +25,15 @@ rotate over four pre-staged batches and one step touches several hundred MB, far
 more than the 126 MB L2. The ``e2e`` block repeats the measurement with the
 step's inputs copied from pinned host memory every step (prefetched on a copy
 stream) and a checksum plus ``valid_count`` read back to the host every step.
+With CUDA graphs (the decode shape) a step is ONE replay of a graph that holds
+the input copy, dispatch, expert and combine; the per-phase times then come
+from the library's sample ring (earliest CTA start to latest CTA end of every
+replayed kernel on the GPU's timer), per sample the maximum over ranks.
+
+Before anything is timed, one step's results are checked on every rank: the
+received rows bit for bit against the senders' inputs, the output bit for bit
+against the rank-order FP32 formula; the device status is read after warm-up
+and after each timed region (``"checked"`` / ``"status"`` in the JSON line).
 """
 
 from __future__ import annotations
@@ -62,6 +71,7 @@ def parse_args():
     parser.add_argument("--tokens", type=int, default=None, help="override tokens per rank")
     parser.add_argument("--routing", choices=("uniform", "zipf"), default="uniform")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--no-verify", action="store_true", help="skip the bit-exact check of one step")
     parser.add_argument("--combine-streaming", choices=("auto", "on", "off"), default="auto",
                         help="ours: reduce while peers still push (auto: large batches only)")
     parser.add_argument("--cpu-numa", choices=("auto", "off"), default="auto",
@@ -118,66 +128,70 @@ class OursArm:
         from ep_xpress_b200.models import IdentityMoELayer
         from ep_xpress_b200.utils import workloads
         self.comm = get_nccl_comm_handle(dist.group.WORLD)
+        self.expert_map = workloads.contiguous_expert_map(shape["experts"], world)
         cfg = Config(hidden_size=shape["hidden"], topk=shape["topk"], max_tokens_per_rank=tokens,
-                     timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30,
+                     timeout_seconds=30.0, decode_max_tokens=tokens if tokens <= 256 else 0,
                      cooperative_launch=not plain_launch, combine_streaming=combine_streaming)
-        self.context = Context(self.comm, workloads.contiguous_expert_map(shape["experts"], world), cfg)
+        self.context = Context(self.comm, self.expert_map, cfg)
         self.layer = IdentityMoELayer(self.context)
+        self.graphs = None
 
-    def enable_graph(self, example):
-        """Capture dispatch, expert and combine as three CUDA graphs on the layer's workspace."""
+    def enable_graph(self, batches, samples):
+        """One CUDA graph per pre-staged batch: copy of the batch into the static inputs, dispatch,
+        expert and combine; plus one graph without the copy for inputs that arrive from the host."""
         import torch
         from ep_xpress_b200.ops import scale_rows
         ep, ws = self.context, self.layer.workspace
         ep.enable_cuda_graph()
-        self.static = [torch.empty_like(t) for t in example]
+        self.static = [torch.empty_like(t) for t in batches[0]]
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for dst, src in zip(self.static, example):
+            for dst, src in zip(self.static, batches[0]):
                 dst.copy_(src)
             self.layer.forward(*self.static, stream=side)            # warm the workspace eagerly
         side.synchronize()
+        ep.prepare_decode_profile(max_samples_per_channel=samples, stage="layer")
         ep.prepare_graph_capture()
         state = {}
 
-        def dispatch():
-            state["batch"] = ep.dispatch_on_stream(*self.static, stream=side, workspace=ws)
-
-        def expert():
-            state["partial"] = scale_rows(ep, state["batch"], stream=side)
-
-        def combine():
-            state["out"] = ep.combine_on_stream(state["partial"], state["batch"].handle, stream=side)
+        def layer():
+            batch = ep.dispatch_on_stream(*self.static, stream=side, workspace=ws)
+            partial = scale_rows(ep, batch, stream=side)
+            state["out"] = ep.combine_on_stream(partial, batch.handle, stream=side)
+            state["batch"] = batch
 
         self.graphs = []
-        for phase in (dispatch, expert, combine):
+        for batch in list(batches) + [None]:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                phase()
+                if batch is not None:
+                    for dst, src in zip(self.static, batch):
+                        dst.copy_(src, non_blocking=True)
+                layer()
             self.graphs.append(graph)
         self.graph_state = state
         torch.cuda.current_stream().wait_stream(side)
 
-    def step(self, x, ids, weights, timing=None):
-        if getattr(self, "graphs", None) is None:
+    def step(self, x, ids, weights, timing=None, resident=None):
+        """``resident``: index of the pre-staged batch (graph mode replays the graph that copies it)."""
+        if self.graphs is None:
             return self.layer.forward(x, ids, weights, timing=timing)
         import torch
         stream = torch.cuda.current_stream()
-        for dst, src in zip(self.static, (x, ids, weights)):
-            dst.copy_(src, non_blocking=True)
+        if resident is None:
+            for dst, src in zip(self.static, (x, ids, weights)):
+                dst.copy_(src, non_blocking=True)
         self.context.prepare_graph_replay(stream)
-        marks = [mark(stream)] if timing is not None else None
-        for graph in self.graphs:
-            graph.replay()
-            if marks is not None:
-                marks.append(mark(stream))
-        if marks is not None:
-            timing.append(marks)
+        self.graphs[-1 if resident is None else resident].replay()
         return self.graph_state["out"], self.graph_state["batch"].valid_count
 
     def launches_per_step(self):
         return 3
+
+    def check(self):
+        self.context.check()
+        return 0
 
     def close(self):
         self.context.close()
@@ -204,7 +218,7 @@ class ReferenceArm:
         self.workspace = self.context.create_workspace(world * tokens, tokens)
         self.torch = torch
 
-    def step(self, x, ids, weights, timing=None):
+    def step(self, x, ids, weights, timing=None, resident=None):
         torch = self.torch
         ep = self.context
         stream = torch.cuda.current_stream()
@@ -223,6 +237,10 @@ class ReferenceArm:
         return out, batch.valid_count
 
     def launches_per_step(self):
+        return 0
+
+    def check(self):
+        self.context.check()
         return 0
 
     def close(self):
@@ -255,6 +273,48 @@ def fenced(world):
     torch.cuda.synchronize()
 
 
+def verify_step(arm, shape, tokens, world, rank, routing, device_batch):
+    """One untimed step on batch 0, checked on this rank: received rows bit for bit against the
+    senders' inputs, output bit for bit against the rank-order FP32 formula. Raises on a mismatch."""
+    import torch
+    from ep_xpress_b200.utils import routing as oracle
+    from ep_xpress_b200.utils import workloads
+    x, ids, weights = device_batch
+    out, valid = arm.step(x, ids, weights, resident=0)
+    torch.cuda.synchronize()
+    report = {"combine_tokens": int(x.shape[0])}
+    want = oracle.identity_layer_oracle(x, ids, weights, arm.expert_map, rank, world)
+    if not torch.equal(out.view(torch.int16), want.view(torch.int16)):
+        bad = int((out.view(torch.int16) != want.view(torch.int16)).any(dim=1).sum())
+        raise SystemExit(f"rank {rank}: combine output differs from the rank-order FP32 formula on {bad} tokens")
+    batch = arm.graph_state["batch"] if arm.graphs is not None else None
+    if batch is None:                                  # eager: run the dispatch once more to look at the rows
+        batch = arm.context.dispatch_on_stream(x, ids, weights, workspace=arm.layer.workspace)
+        arm.context.combine_on_stream(arm.context.partial_buffer(batch.handle), batch.handle)
+        torch.cuda.synchronize()
+    received = int(batch.valid_count.item())
+    owner = torch.tensor(arm.expert_map)
+    expected_rows, sources = 0, []
+    for peer in range(world):
+        if routing == "zipf":
+            peer_ids, _ = workloads.zipf_routing(tokens, shape["experts"], shape["topk"], seed=0, rank=peer)
+        else:
+            peer_ids, _ = workloads.uniform_routing(tokens, shape["experts"], shape["topk"], seed=0, rank=peer,
+                                                    weights=shape["weights"])
+        expected_rows += int((owner[peer_ids.clamp(min=0)].eq(rank) & (peer_ids >= 0)).any(dim=1).sum())
+        sources.append(workloads.gaussian_payload(tokens, shape["hidden"], seed=0, rank=peer))
+    if received != expected_rows:
+        raise SystemExit(f"rank {rank}: received {received} rows, the routes say {expected_rows}")
+    inverse = batch.handle.inverse_map[:received]
+    everything = torch.stack(sources).cuda()
+    rows = everything[inverse[:, 0], inverse[:, 1]]
+    if not torch.equal(batch.hidden[:received].view(torch.int16), rows.view(torch.int16)):
+        raise SystemExit(f"rank {rank}: received activation rows differ from the senders' inputs")
+    report["dispatch_rows"] = received
+    del everything, rows
+    return report
+
+
 def run(args):
     import torch
     from ep_xpress_b200.utils.clocks import ClockSampler
@@ -272,28 +332,47 @@ def run(args):
                                                                       args.combine_streaming)
     use_graph = args.impl == "ours" and (args.graph == "on" or (args.graph == "auto" and args.config == "decode"))
     if use_graph:
-        arm.enable_graph(device[0])
+        arm.enable_graph(device, samples=max(args.steps, 16))
     stream = torch.cuda.current_stream()
 
-    # ---- device-timed: inputs resident, rotated ---------------------------------
+    # ---- correctness of one step, then warm-up ------------------------------------
+    checked = None
+    if args.impl == "ours" and not args.no_verify:
+        checked = verify_step(arm, shape, tokens, world, rank, args.routing, device[0])
     for i in range(args.warmup):
-        arm.step(*device[i % sets])
+        arm.step(*device[i % sets], resident=i % sets)
+    status = arm.check()
     fenced(world)
+
+    # ---- device-timed: inputs resident, rotated ---------------------------------
     timing = []
     clocks = ClockSampler(local, interval_s=0.002)
     clocks.__enter__()
+    if use_graph:
+        arm.context.start_decode_profile()
+        fenced(world)
     begin = mark(stream)
     for i in range(args.steps):
-        arm.step(*device[i % sets], timing=timing)
+        arm.step(*device[i % sets], timing=timing, resident=i % sets)
     end = mark(stream)
     fenced(world)
     clocks.pause()
     total_ms = gather_max([begin.elapsed_time(end)], world)[0]
-    dispatch_us = gather_max([m[0].elapsed_time(m[1]) * 1e3 for m in timing], world)
-    combine_us = gather_max([m[2].elapsed_time(m[3]) * 1e3 for m in timing], world)
+    if use_graph:
+        samples = arm.context.stop_decode_profile()["stages"]
+        if min(samples[name]["samples"] for name in samples) < args.steps:
+            raise SystemExit("the sample ring recorded fewer operations than steps were timed")
+        dispatch_us = gather_max([ns / 1e3 for ns in samples["dispatch"]["elapsed_ns"][:args.steps]], world)
+        combine_us = gather_max([ns / 1e3 for ns in samples["combine"]["elapsed_ns"][:args.steps]], world)
+        phase_timing = "library sample ring: earliest CTA start to latest CTA end of every replayed kernel"
+    else:
+        dispatch_us = gather_max([m[0].elapsed_time(m[1]) * 1e3 for m in timing], world)
+        combine_us = gather_max([m[2].elapsed_time(m[3]) * 1e3 for m in timing], world)
+        phase_timing = "CUDA events around every phase"
     both_us = [d + c for d, c in zip(dispatch_us, combine_us)]
     ms_per_step = total_ms / args.steps
     value = world * tokens / (ms_per_step * 1e-3)
+    status = max(status, arm.check())
 
     # ---- end to end: H2D of every step's inputs, D2H of its result -----------------
     e2e = None
@@ -342,9 +421,10 @@ def run(args):
         e2e_ms = gather_max([begin.elapsed_time(end)], world)[0] / args.steps
         e2e = {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 8}
+        status = max(status, arm.check())
 
     clocks.__exit__(None, None, None)
-    if args.profile_out and args.impl == "ours":
+    if args.profile_out and args.impl == "ours" and not use_graph:
         arm.context.start_combine_profile(16)
         for i in range(4):
             arm.step(*device[i % sets])
@@ -353,6 +433,7 @@ def run(args):
             json.dump(report, handle)
         fenced(world)
     published = PUBLISHED_TOKENS_PER_S.get((args.config, world)) if args.tokens is None else None
+    ordered = sorted(both_us)
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -361,10 +442,15 @@ def run(args):
         "config": {"model": shape["model"], "global_batch": world * tokens, "seq_len": tokens,
                    "tokens_per_rank": tokens, "hidden": shape["hidden"], "experts": shape["experts"],
                    "topk": shape["topk"], "routing": args.routing, "parallelism": f"ep{world}",
-                   "cuda_graph": bool(use_graph), "cpu_numa": placement,
-                   "l2": "inputs rotate over 4 batches; a step touches far more than the 126 MB L2"},
+                   "cuda_graph": bool(use_graph), "cpu_numa": placement, "phase_timing": phase_timing,
+                   "l2": "inputs rotate over 4 batches; a step touches far more than the 126 MB L2"
+                         if tokens >= 1024 else
+                         "inputs rotate over 4 batches; the rows of a step come from a peer's memory or were "
+                         "written by the previous kernel, a small batch fits the 126 MB L2 by nature"},
         "dispatch_us_p50": statistics.median(dispatch_us), "combine_us_p50": statistics.median(combine_us),
         "dispatch_combine_us_p50": statistics.median(both_us),
+        "dispatch_combine_us_p95": ordered[min(len(ordered) - 1, int(0.95 * len(ordered)))],
+        "checked": checked is not None, "verified": checked, "status": status,
         "clocks": clocks.summary(), "e2e": e2e,
         "gpu_launches": arm.launches_per_step() * args.steps,
     }

@@ -37,13 +37,16 @@ _POLICY = {
     "EPX_DECODE_TOKENS_PER_CHANNEL": ("tokens_per_channel_decode", int),
 }
 
+# Read by other parts of the library, not by this module: accepted here so that setting them does
+# not make the configuration fail ("EPX_NODE_ID": node label of the multi-node context).
+_FOREIGN = ("EPX_NODE_ID",)
+
 PRESETS = {
     # decode-heavy serving: small bounded batches, many retained per-layer workspaces
     "b200_decode": {"EPX_TRANSPORT": "nvlink", "EPX_DECODE_MAX_TOKENS": "256", "EPX_SLOTS": "2",
                     "EPX_WORKSPACE_POOL_BYTES": str(8 << 30), "EPX_TIMEOUT_SECONDS": "30"},
     # prefill-heavy: large slots, default workspace reserve
-    "b200_prefill": {"EPX_TRANSPORT": "nvlink", "EPX_SLOTS": "2", "EPX_TIMEOUT_SECONDS": "60",
-                     "EPX_GPU_POOL_BUDGET_BYTES": str(64 << 30)},
+    "b200_prefill": {"EPX_TRANSPORT": "nvlink", "EPX_SLOTS": "2", "EPX_TIMEOUT_SECONDS": "60"},
     # the host-staged oracle path, for debugging a deployment without NVLink
     "host_oracle": {"EPX_TRANSPORT": "host_ce", "EPX_TIMEOUT_SECONDS": "120"},
 }
@@ -71,7 +74,8 @@ def config_from_env(hidden_size, topk, max_tokens_per_rank, env=None, preset=Non
         if preset not in PRESETS:
             raise ValueError(f"unknown preset {preset!r}; choose from {sorted(PRESETS)}")
         values.update(PRESETS[preset])
-    unknown = [k for k in env if k.startswith("EPX_") and k not in _FIELDS and k not in _POLICY and k != "EPX_PRESET"]
+    unknown = [k for k in env if k.startswith("EPX_") and k not in _FIELDS and k not in _POLICY
+               and k not in _FOREIGN and k != "EPX_PRESET"]
     if unknown:
         raise ValueError(f"unknown configuration variables: {sorted(unknown)}")
     values.update({k: v for k, v in env.items() if k in _FIELDS})

@@ -23,6 +23,7 @@ _TRANSPORTS = ("nvlink", "host_sm", "host_ce")
 _CTRL_HEADER_BYTES = 256
 _SLOT_ALIGN = 256
 _ROUTE_TILE = 512
+_FLAG_LINE = 128          # arrival words behind every staging row (csrc/epx_layout.h)
 
 
 def _round_up(value: int, alignment: int) -> int:
@@ -77,6 +78,22 @@ class Config:
     @property
     def device_transport(self) -> bool:
         return self.transport in DEVICE_TRANSPORTS
+
+    def inert_fields(self) -> tuple:
+        """Fields that were given a non-default value but change nothing on the chosen transport.
+
+        The reference's host-staged device transport needs these knobs (frame sizes, warp
+        specialisation of its pair combine, single-frame dispatch, a trap on errors, the host
+        loop's poll interval); the NVLink transport has no frames to size and selects its kernel
+        variants by shape. They stay accepted so that existing call sites keep working; a context
+        warns once when it is constructed with any of them set.
+        """
+        if not self.device_transport:
+            return ()
+        defaults = {"chunk_bytes": 2 << 20, "combine_frame_rows": 0, "combine_warp_specialization": False,
+                    "decode_single_frame": False, "workload": "auto", "poll_interval_seconds": 0.0001,
+                    "host_pool_budget_bytes": 512 << 20}
+        return tuple(name for name, default in defaults.items() if getattr(self, name) != default)
 
     def __post_init__(self):
         device = self.transport in DEVICE_TRANSPORTS
@@ -201,10 +218,33 @@ class Config:
         fanout = min(k, w)
         tiles = -(-tokens // _ROUTE_TILE)
         parts = (capacity * h * 2, capacity * k * 8, capacity * k * 4, capacity * 16, capacity * 4,
-                 tokens * fanout * h * 2, capacity * h * 2,
+                 tokens * fanout * (h * 2 + _FLAG_LINE), capacity * h * 2,
                  tokens * 8, tokens * fanout * 4, tokens * fanout * 4, (tiles + 1) * w * 4, w * 8, w * 4, w * 4, w * 4, 64 * 4,
                  tokens * h * 2)
         return _round_up(sum(_round_up(p, _SLOT_ALIGN) for p in parts), 4096)
+
+    def nvlink_slot_breakdown(self, world_size, capacity=None, tokens=None) -> dict:
+        """Bytes of every plane of one operation slot, by name (the same arithmetic as
+        :meth:`nvlink_slot_bytes`). ``hidden``/``ids``/``weights``/``inverse``/``ret`` are what peers
+        store a dispatch into (``capacity`` rows), ``staging`` is where expert ranks push the rows
+        of this rank's ``tokens`` (one row and one arrival line per (token, destination)),
+        ``partial`` is the default output plane of the expert runner, ``output`` the combine
+        result of a workspace, ``route_state`` the rank-local bookkeeping."""
+        _check_world(world_size)
+        capacity = world_size * self.max_tokens_per_rank if capacity is None else capacity
+        tokens = self.max_tokens_per_rank if tokens is None else tokens
+        h, k, w = self.hidden_size, self.topk, world_size
+        fanout = min(k, w)
+        tiles = -(-tokens // _ROUTE_TILE)
+        up = lambda value: _round_up(value, _SLOT_ALIGN)      # noqa: E731
+        parts = {"hidden": up(capacity * h * 2), "ids": up(capacity * k * 8), "weights": up(capacity * k * 4),
+                 "inverse": up(capacity * 16), "ret": up(capacity * 4),
+                 "staging": up(tokens * fanout * (h * 2 + _FLAG_LINE)), "partial": up(capacity * h * 2),
+                 "route_state": (up(tokens * 8) + 2 * up(tokens * fanout * 4) + up((tiles + 1) * w * 4) + up(w * 8)
+                                 + 3 * up(w * 4) + up(64 * 4)),
+                 "output": up(tokens * h * 2)}
+        parts["total"] = _round_up(sum(parts.values()), 4096)
+        return parts
 
     def heap_bytes(self, world_size) -> int:
         """Peer-mapped HBM one rank allocates at bootstrap."""

@@ -18,19 +18,23 @@
 // + j, j-th destination rank ascending) and are added in that order.
 //
 // One launch replaces the reference's zero-fill, pair transport and reduce
-// launches (host_sm.cu:559-590, :1212-1468, :592-607). Protocol:
-//   A. push    work items (received row, row segment) claimed from a local counter:
-//              rows whose source is a peer are stored to that peer's staging plane
-//              at the return slot the dispatch recorded next to the row;
-//   B. signal  the last CTA publishes its progress word (epoch << 32 | rows pushed, here
-//              "all") to every peer after a system fence, as a max update;
-//   C. wait    bounded, for that word of exactly the peers this rank sent rows to;
-//   D. reduce  work items (token, segment): staging rows and the local partial row
-//              are read from this GPU's own memory and reduced in rank order;
-//   E. retire  the last CTA advances the device epoch.
-// A streamed variant (opt-in) runs A and D side by side: a few warps push and publish
-// progress chunk by chunk while the others reduce the tokens whose rows have arrived.
-// No trailing handshake is needed: a staging plane is only rewritten by the combine
+// launches (host_sm.cu:559-590, :1212-1468, :592-607) and, like its mailbox kernel
+// (host_sm.cu:1952-2511), receives and reduces in the same kernel. Default protocol
+// ("mailbox", groups of two or more ranks, 16-byte rows, fan-out up to eight):
+//   push     two pusher warps per CTA claim received rows whose token lives on a peer.
+//            A row travels partial -> shared memory -> the owner's staging row as bulk
+//            asynchronous copies (TMA, no tensor map); when the copies of a batch have
+//            completed, the pusher stores the combine epoch into the arrival word that
+//            sits right behind the staging row (release, system scope). No CTA-wide
+//            fence, no counter, no "all rows are out" message.
+//   reduce   at the same time the other warps of every CTA walk the rank's own tokens:
+//            a producer warp polls the arrival words of exactly the rows a token is
+//            owed (local memory), copies them into a shared-memory stage, and four
+//            consumer warps add them in rank order and store the result.
+// The sequential protocol (push everything, fence, one progress word per peer, wait,
+// reduce) is kept for rows that are not 16-byte aligned, wider fan-outs, and as a
+// selectable fallback. A group of one rank only reduces.
+// No trailing handshake is needed: a staging row is only rewritten by the combine
 // of a later dispatch on the same slot, which cannot complete before this rank has
 // entered that dispatch, i.e. finished this reduce.
 #include "epx_device.cuh"
@@ -189,25 +193,32 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 
 // ---- reduce phase, bulk-copy variant -------------------------------------------------------
 // (rows 16-byte aligned, at most kPeerBatch contributors per token)
-// The CTA is four independent pipelines. Each has one producer warp, four consumer warps and
-// a private ring of shared-memory stages. The producer walks its share of the CTA's
-// (token, row segment) items; lane j issues ONE bulk copy (TMA) of contributor j's segment
-// into the stage and all copies of an item complete on the stage's "full" mbarrier. The
-// consumers add the staged chunks in ascending rank order, store the result and release the
-// stage through its "empty" mbarrier. Data in flight lives in shared memory, so the phase
+// The reducing warps of a CTA form independent pipelines. Each has one producer warp, four
+// consumer warps and a private ring of shared-memory stages. The producer walks its share of
+// the CTA's (token, row segment) items; lane j issues ONE bulk copy (TMA) of contributor j's
+// segment into the stage and all copies of an item complete on the stage's "full" mbarrier.
+// The consumers add the staged chunks in ascending rank order, store the result and release
+// the stage through its "empty" mbarrier. Data in flight lives in shared memory, so the phase
 // needs few registers; a producer's per-item bookkeeping is a serial instruction stream of
-// about a microsecond, which is why there are four of them. Route look-ups (mask, row
+// about a microsecond, which is why there are several of them. Route look-ups (mask, row
 // indices) are loaded for 32 items at once and one batch ahead.
 constexpr int kGroupWarps = 4;                    // consumer warps of one pipeline
 constexpr int kGroupThreads = kGroupWarps * 32;
 constexpr int kMaxGroups = 4;
-constexpr int kBulkThreads = kThreads + 32 * kMaxGroups;   // 20 warps in either role layout
-constexpr int kStreamGroups = 3;                  // streamed launches: 3 pipelines (15 warps) ...
-constexpr int kPushWarps = kBulkThreads / 32 - kStreamGroups * (kGroupWarps + 1);   // ... + 5 push warps
+constexpr int kBulkThreads = kThreads + 32 * kMaxGroups;   // sequential protocol: 4 pipelines = 20 warps
+constexpr size_t kBulkSmemBytes = 192 * 1024;              // ... sharing 192 KB of stage rings
 constexpr int kMaxGroupStages = 3;
 constexpr int kChunksPerThread = 4;
-constexpr int kSegMaxBytes = 8192;                // largest row segment of one item
-constexpr size_t kBulkSmemBytes = 192 * 1024;
+constexpr int kSegMaxBytes = 16384;               // largest row segment of one item
+
+// Mailbox protocol: 2 pipelines (10 warps) and 2 pusher warps per CTA.
+constexpr int kMailGroups = 2;
+constexpr int kPushers = 2;
+constexpr int kMailThreads = (kMailGroups * (kGroupWarps + 1) + kPushers) * 32;
+constexpr size_t kMailReduceSmem = 128 * 1024;    // stage rings of the two pipelines
+constexpr int kPushStages = 3;                    // bulk copies one pusher keeps in flight
+constexpr int kPushStageBytes = 14336;
+constexpr size_t kMailSmemBytes = kMailReduceSmem + static_cast<size_t>(kPushers) * kPushStages * kPushStageBytes;
 
 // Segment size: as large as possible while every group still gets two stages of `fan`
 // contributor slots (one being filled while the other is reduced).
@@ -233,6 +244,24 @@ struct StageItem {
 __device__ __forceinline__ void mbarrier_arrive(unsigned long long* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar)) : "memory");
 }
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Shared -> global copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) by the
+// copy engine of this SM; the destination may be a peer's memory. Completion is tracked by the
+// issuing thread's bulk async-groups (commit / wait below). One copy per call, no fan-out.
+__device__ __forceinline__ void bulk_store_from_smem(void* dst, const void* src, unsigned bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_address(src)),
+               "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Every bulk copy this thread committed has read its source AND its writes are complete.
+__device__ __forceinline__ void bulk_wait_all_complete() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 struct BulkReduceArgs {
   const unsigned long long* mask_arr;
@@ -241,6 +270,7 @@ struct BulkReduceArgs {
   const char* staging;
   char* out;
   long long row_bytes;
+  long long stride;       // distance between two staging rows
   int tokens;
   int fan;
   int self;
@@ -248,24 +278,22 @@ struct BulkReduceArgs {
   bool single_round;
   unsigned long long timeout_ns;
   unsigned long long* profile;
-  // streamed launches only: progress words of the peers and what this epoch's words start with
+  // mailbox launches only
   const RankCtx* ctx;
-  const unsigned long long* progress;
-  unsigned long long epoch_base;
+  unsigned epoch;
 };
 
 // Barriers and item slots are indexed [group][stage]. Returns false when a bounded wait gave up.
 // Called by the first kGroups * (kGroupWarps + 1) warps of the CTA: consumers first, then one
-// producer warp per group. kStreamed: the peers are still pushing while this runs, so a
-// producer checks, before it copies a token's rows, that every remote contributor has
-// published progress beyond the row it owes (cached per peer; re-read only when short), and
-// the CTAs take items round-robin so that each of them owns tokens from every part of the
-// batch, the early ones included.
-template <int kGroups, bool kStreamed>
+// producer warp per group. kMailbox: the peers are still pushing while this runs, so before a
+// producer copies a token's rows, lane j waits (bounded) for the arrival word behind the staging
+// row of remote contributor j to carry this combine's epoch, and the CTAs take items round-robin
+// so that each of them owns tokens from every part of the batch.
+template <int kGroups, bool kMailbox, size_t kReduceSmem>
 __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem, unsigned long long* full_all,
                                             unsigned long long* empty_all, StageItem* items_all) {
   constexpr int kConsumerWarps = kGroups * kGroupWarps;
-  constexpr size_t kGroupSmemBytes = kBulkSmemBytes / kGroups;
+  constexpr size_t kGroupSmemBytes = kReduceSmem / kGroups;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool producer = warp >= kConsumerWarps;
   const int group = producer ? warp - kConsumerWarps : warp / kGroupWarps;
@@ -280,19 +308,18 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   unsigned long long* const empty = empty_all + group * kMaxGroupStages;
   StageItem* const slots = items_all + group * kMaxGroupStages;
   // Items of this CTA are a contiguous range (local memory only: a static split is balanced),
-  // or every gridDim.x-th item when streamed; the groups take them round-robin.
-  const int lo = kStreamed ? static_cast<int>(blockIdx.x)
-                           : static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
+  // or every gridDim.x-th item in mailbox launches; the groups take them round-robin.
+  const int lo = kMailbox ? static_cast<int>(blockIdx.x)
+                          : static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
   const int hi = static_cast<int>(static_cast<long long>(items) * (blockIdx.x + 1) / gridDim.x);
-  const int stride = kStreamed ? static_cast<int>(gridDim.x) : 1;
-  const int cta_items = kStreamed ? (items > lo ? (items - lo + stride - 1) / stride : 0)
-                                  : hi - static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
+  const int stride = kMailbox ? static_cast<int>(gridDim.x) : 1;
+  const int cta_items = kMailbox ? (items > lo ? (items - lo + stride - 1) / stride : 0)
+                                 : hi - static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
   const int mine = cta_items > group ? (cta_items - group + kGroups - 1) / kGroups : 0;
   long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
   bool ok = true;
   if (producer) {
     auto item_of = [&](int k) { return lo + (group + k * kGroups) * stride; };
-    unsigned long long seen_lo = 0, seen_hi = 0;           // progress word of peer `lane` / `lane + 32`
     // Lane L loads the mask of item L of the batch, lane 8q + j the row of contributor j of
     // item 4r + q.
     auto load_batch = [&](int base, unsigned long long& mask, int (&rows)[8]) {
@@ -338,29 +365,22 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             is_self = d == a.self;
             if (row >= 0 && !(is_self && row >= a.partial_rows))
               src = is_self ? a.partial + static_cast<long long>(row) * a.row_bytes
-                            : a.staging + (static_cast<long long>(t) * a.fan + lane) * a.row_bytes;
+                            : a.staging + (static_cast<long long>(t) * a.fan + lane) * a.stride;
           }
-          if (kStreamed) {
-            // Contributor `lane` is rank d and owes row `row` of d's receive buffer.
-            const int d = lane < n ? nth_set_bit(m, lane) : 0;
+          if (kMailbox) {
+            // Contributor `lane` is a peer: its row is in once the word behind it carries this epoch.
             const bool remote = src != nullptr && !is_self;
-            const unsigned long long target = a.epoch_base + static_cast<unsigned long long>(row < 0 ? 0 : row) + 1ull;
-            const unsigned long long lo_word = __shfl_sync(0xffffffffu, seen_lo, d & 31);
-            const unsigned long long hi_word = __shfl_sync(0xffffffffu, seen_hi, d & 31);
-            const bool behind = remote && (d < 32 ? lo_word : hi_word) < target;
-            if (__any_sync(0xffffffffu, behind)) {
-              bool fine = true;
-              if (behind)
-                fine = bounded_wait(*a.ctx, kPhaseCombine, 5, [&] { return ld_acquire_sys(a.progress + d) >= target; });
-              if (!__all_sync(0xffffffffu, fine)) {
-                ok = false;
-                continue;
-              }
-              const int world = a.ctx->world;
-              seen_lo = lane < world ? ld_acquire_sys(a.progress + lane) : 0ull;
-              seen_hi = lane + 32 < world ? ld_acquire_sys(a.progress + lane + 32) : 0ull;
-              fence_proxy_async();      // the rows were written by generic stores; the copies below are async-proxy reads
+            bool fine = true;
+            if (remote) {
+              const unsigned* word = reinterpret_cast<const unsigned*>(src + a.row_bytes);
+              if (ld_acquire_sys_u32(word) != a.epoch)
+                fine = bounded_wait(*a.ctx, kPhaseCombine, 5, [&] { return ld_acquire_sys_u32(word) == a.epoch; });
             }
+            if (!__all_sync(0xffffffffu, fine)) {
+              ok = false;
+              continue;
+            }
+            fence_proxy_async();      // the rows were written by a peer; the copies below read them through the async proxy
           }
           const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
           const unsigned self_vote = __ballot_sync(0xffffffffu, is_self);
@@ -470,31 +490,38 @@ struct PushArgs {
   const char* partial;
   const int* ret;
   long long row_bytes;
+  long long stride;         // distance between two staging rows
   long long seg_bytes;
   int segs;
-  long long chunk_bytes;    // streamed push: progress is published about this often
   int most;                 // most rows received from one peer
   int valid;
   int self;
   int world;
 };
 
+// Resolves push item `q` (segments already divided out) to the received row it stands for and
+// the rank that owns its token; false when the item is a hole of the interleaved order.
+__device__ __forceinline__ bool push_target(const PushArgs& p, long long q, long long* row, int* source) {
+  const int peers = p.world - 1;
+  const int in_block = static_cast<int>(q % kPushBlock);
+  const long long q2 = q / kPushBlock;
+  *source = (p.self + 1 + static_cast<int>(q2 % peers)) % p.world;
+  const long long from_source = (q2 / peers) * kPushBlock + in_block;
+  if (from_source >= p.rows_from[*source]) return false;
+  *row = p.first_row[*source] + from_source;
+  return *row < p.valid;
+}
+
 template <int kWords, int kUnroll>
 __device__ __forceinline__ void push_item(const PushArgs& p, long long item, int lane) {
   constexpr int kChunk = kWords * 4;
-  const int peers = p.world - 1;
   const int seg = static_cast<int>(item % p.segs);
-  const long long q = item / p.segs;
-  const int in_block = static_cast<int>(q % kPushBlock);
-  const long long q2 = q / kPushBlock;
-  const int source = (p.self + 1 + static_cast<int>(q2 % peers)) % p.world;
-  const long long from_source = (q2 / peers) * kPushBlock + in_block;
-  if (from_source >= p.rows_from[source]) return;
-  const long long row = p.first_row[source] + from_source;
-  if (row >= p.valid) return;
+  long long row;
+  int source;
+  if (!push_target(p, item / p.segs, &row, &source)) return;
   const long long back = p.ret[row];
   const char* src = p.partial + row * p.row_bytes;
-  char* dst = p.stage[source] + back * p.row_bytes;
+  char* dst = p.stage[source] + back * p.stride;
   const long long b0 = seg * p.seg_bytes;
   const long long b1 = min(p.row_bytes, b0 + p.seg_bytes);
   for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
@@ -512,99 +539,74 @@ __device__ __forceinline__ void push_item(const PushArgs& p, long long item, int
   }
 }
 
-// ---- streamed push ------------------------------------------------------------------------------
-// Run by the last kPushWarps warps of every CTA while the other warps already reduce. The item
-// order is cut into up to kMaxPushChunks chunks of whole blocks, and after each chunk the rank
-// tells every peer how many of that peer's rows have certainly arrived (as a row index in this
-// rank's receive buffer, the coordinate the peer recorded at dispatch).
-//
-// "Certainly arrived" needs a system-scope fence behind the stores, and under a saturated link
-// such a fence takes tens of microseconds (the posted writes queued ahead of it have to drain).
-// The warps that store therefore never fence: a warp whose next claimed item lies beyond chunk
-// c only counts itself out of c in shared memory. The CTA's herald warp waits for that count,
-// runs the fence (cumulative over the stores it has observed through the count), counts the CTA
-// out of the chunk in the rank's header, and the herald of the last CTA publishes - with a max
-// update, so that a delayed publication can never take progress back.
-struct PushPlan {
-  long long blocks;      // blocks of kPushBlock rows per peer
-  long long per_block;   // work items of one block over all peers
-  long long items;
-  int chunks;
-};
-
-__device__ __forceinline__ PushPlan plan_push(const PushArgs& p) {
-  PushPlan plan;
+// ---- mailbox push ---------------------------------------------------------------------------
+// Run by ONE thread of each pusher warp. Rows are claimed from the rank's counter and moved in
+// batches of kPushStages pieces (a row of up to kPushStageBytes is one piece): all loads of a
+// batch are issued, each store follows its load, and once every copy of the batch has
+// completed the arrival words of the rows that ended in it are released. The copies run in the
+// SM's copy engine; the thread only issues and waits, so two pushers per CTA keep far more
+// bytes in flight than the link needs.
+__device__ __forceinline__ bool mailbox_push(const PushArgs& p, const RankCtx& c, CtrlHeader* hdr, char* stages,
+                                             unsigned long long* full, unsigned epoch) {
   const int peers = p.world - 1;
-  plan.blocks = peers > 0 ? (p.most + kPushBlock - 1) / kPushBlock : 0;
-  plan.per_block = static_cast<long long>(peers) * kPushBlock * p.segs;
-  plan.items = plan.blocks * plan.per_block;
-  long long wanted = plan.blocks * kPushBlock * peers * p.row_bytes / (p.chunk_bytes > 0 ? p.chunk_bytes : 1);
-  if (wanted > kMaxPushChunks) wanted = kMaxPushChunks;
-  if (wanted > plan.blocks) wanted = plan.blocks;
-  plan.chunks = wanted < 1 ? 1 : static_cast<int>(wanted);
-  return plan;
-}
-
-template <int kWords>
-__device__ __forceinline__ void push_streamed(const PushArgs& p, CtrlHeader* hdr, int* left_behind, int lane) {
-  const PushPlan plan = plan_push(p);
-  int current = 0;                                     // chunk this warp may still store into
-  unsigned next_claim = lane == 0 ? atomicAdd(&hdr->cwork_push, 1u) : 0u;
-  while (true) {
-    const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
-    int item_chunk = plan.chunks;
-    if (item < plan.items) {
-      const long long block = item / plan.per_block;
-      item_chunk = current;
-      while (item_chunk + 1 < plan.chunks && plan.blocks * (item_chunk + 1) / plan.chunks <= block) ++item_chunk;
-    }
-    if (current < item_chunk) {
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        for (; current < item_chunk; ++current) atomicAdd(left_behind + current, 1);
+  const long long blocks = (p.most + kPushBlock - 1) / kPushBlock;
+  const long long items = blocks * peers * kPushBlock;
+  const int pieces = static_cast<int>((p.row_bytes + kPushStageBytes - 1) / kPushStageBytes);
+  const int piece_bytes = static_cast<int>(align_up((p.row_bytes + pieces - 1) / pieces, 16));
+  unsigned parity = 0;
+  const char* src_row = nullptr;     // row being moved: source, destination, next piece
+  char* dst_row = nullptr;
+  int piece = pieces;                // == pieces: no row in hand
+  bool more = true;
+  while (more) {
+    unsigned* words[kPushStages];
+    char* dst[kPushStages];
+    int bytes[kPushStages];
+    int count = 0;
+    while (count < kPushStages) {
+      if (piece == pieces) {
+        const long long item = atomicAdd(&hdr->cwork_push, 1u);
+        if (item >= items) { more = false; break; }
+        long long row;
+        int source;
+        if (!push_target(p, item, &row, &source)) continue;
+        src_row = p.partial + row * p.row_bytes;
+        dst_row = p.stage[source] + static_cast<long long>(p.ret[row]) * p.stride;
+        piece = 0;
       }
-      current = item_chunk;
+      const long long b0 = static_cast<long long>(piece) * piece_bytes;
+      bytes[count] = static_cast<int>(min(p.row_bytes, b0 + piece_bytes) - b0);
+      dst[count] = dst_row + b0;
+      ++piece;
+      words[count] = piece == pieces ? reinterpret_cast<unsigned*>(dst_row + p.row_bytes) : nullptr;
+      char* stage = stages + static_cast<size_t>(count) * kPushStageBytes;
+      mbarrier_arrive_expect_tx(full + count, static_cast<unsigned>(bytes[count]));
+      bulk_load_to_smem(stage, src_row + b0, static_cast<unsigned>(bytes[count]), full + count);
+      ++count;
     }
-    if (item >= plan.items) break;
-    if (lane == 0) next_claim = atomicAdd(&hdr->cwork_push, 1u);   // in flight while this item is copied
-    push_item<kWords, 8>(p, item, lane);
+    if (count == 0) break;
+    for (int i = 0; i < count; ++i) {
+      if (!mbarrier_wait_bounded(full + i, parity, c.timeout_ns)) return false;
+      bulk_store_from_smem(dst[i], stages + static_cast<size_t>(i) * kPushStageBytes, static_cast<unsigned>(bytes[i]));
+    }
+    bulk_commit_group();
+    bulk_wait_all_complete();
+    fence_proxy_async();               // the copies wrote through the async proxy; the words below are ordinary stores
+    for (int i = 0; i < count; ++i)
+      if (words[i] != nullptr) st_release_sys_u32(words[i], epoch);
+    // A stage whose barrier was not used in this batch keeps its phase: only full batches flip
+    // every barrier, and a short batch is always the last one.
+    parity ^= 1u;
   }
+  return true;
 }
 
-__device__ __forceinline__ void herald_streamed(const PushArgs& p, const RankCtx& c, CtrlHeader* hdr,
-                                                size_t ready_offset, unsigned epoch, const int* left_behind, int lane) {
-  const PushPlan plan = plan_push(p);
-  const volatile int* counts = left_behind;
-  for (int chunk = 0; chunk < plan.chunks; ++chunk) {
-    unsigned before = 0;
-    bool ok = true;
-    if (lane == 0) {
-      ok = bounded_wait(c, kPhaseCombine, 6, [&] { return counts[chunk] >= kPushWarps - 1; });
-      if (ok) {
-        __threadfence_system();                          // every store the CTA made into this chunk has landed
-        before = atomicAdd(&hdr->cpush_done[chunk], 1u);
-        if (before == gridDim.x - 1) __threadfence();    // acquire side of the count
-      }
-    }
-    if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) return;
-    before = __shfl_sync(0xffffffffu, before, 0);
-    if (before != gridDim.x - 1) continue;
-    const long long pushed = plan.blocks * (chunk + 1) / plan.chunks * kPushBlock;   // rows per peer, at least
-    for (int d = lane; d < p.world; d += 32) {
-      if (d == p.self) continue;
-      const long long rows = p.rows_from[d] < pushed ? p.rows_from[d] : pushed;
-      const unsigned long long progress = chunk == plan.chunks - 1
-          ? 0xffffffffull : static_cast<unsigned long long>(p.first_row[d] + rows);
-      unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[d] + ready_offset) + p.self;
-      red_max_release_sys(word, (static_cast<unsigned long long>(epoch) << 32) | progress);
-    }
-  }
-}
+enum CombineMode : int { kModeRegister = 0, kModeBulk = 1, kModeMailbox = 2 };
 
-template <bool kVec16, bool kBulk, bool kStreamed>
+template <bool kVec16, int kMode>
 __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_smem) {
-  static_assert(kBulk || !kStreamed, "streaming needs the bulk-copy reduce");
+  static_assert(kVec16 || kMode == kModeRegister, "the bulk-copy paths need 16-byte rows");
+  constexpr bool kBulk = kMode != kModeRegister;
   constexpr int kWords = kVec16 ? 4 : 1;
   constexpr int kChunk = kWords * 4;
   constexpr int kUnroll = 4;
@@ -626,14 +628,15 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   const char* const staging = slot + sl.staging;
   const int fan = route_fanout(K, W);
   const long long row_bytes = static_cast<long long>(H) * 2;
+  const long long stride = static_cast<long long>(staging_stride(H));
 
   __shared__ char* s_stage[64];
   __shared__ int s_need[64];
   __shared__ int s_rows_from[64], s_first_row[64];
   __shared__ int s_most;
-  __shared__ int s_left_behind[kMaxPushChunks];   // streamed: push warps that are done with chunk c
   __shared__ int s_last;
   __shared__ unsigned long long s_full[kMaxGroups * kMaxGroupStages], s_empty[kMaxGroups * kMaxGroupStages];
+  __shared__ unsigned long long s_push_full[kPushers * kPushStages];
   __shared__ StageItem s_items[kMaxGroups * kMaxGroupStages];
 
   profile_stamp(op.profile, 0);
@@ -642,9 +645,10 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     if (threadIdx.x == 0 && blockIdx.x == 0) report_error(c, kEpochsExhausted, kPhaseCombine, 0xE0, e);
     return;
   }
-  // Progress words carry (epoch << 32 | rows pushed); "everything" is the largest row count.
-  const unsigned long long epoch_base = static_cast<unsigned long long>(e) << 32;
-  const unsigned long long all_pushed = epoch_base | 0xffffffffull;
+  const unsigned sample = sample_begin(op.samples, e, op.sample_capacity);
+  // Progress words of the sequential protocol carry (epoch << 32 | rows pushed); "everything"
+  // is the largest row count.
+  const unsigned long long all_pushed = (static_cast<unsigned long long>(e) << 32) | 0xffffffffull;
   if (tid < W) {
     const unsigned long long off = reinterpret_cast<const unsigned long long*>(slot + sl.peer_off)[tid];
     const int cap = reinterpret_cast<const int*>(slot + sl.peer_cap)[tid];
@@ -652,7 +656,6 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     s_stage[tid] = c.heap[tid] + off + pl.staging;
     s_need[tid] = (tid != self && reinterpret_cast<const int*>(slot + sl.send_cnt)[tid] > 0) ? 1 : 0;
   }
-  if (tid >= 96 && tid < 96 + kMaxPushChunks) s_left_behind[tid - 96] = 0;
   if (tid == 64) {
     int at = 0, most = 0;
     for (int r = 0; r < W; ++r) {
@@ -669,9 +672,14 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       mbarrier_init(s_full + tid, 1);
       mbarrier_init(s_empty + tid, kGroupWarps);
     }
+    if (tid >= 96 && tid < 96 + kPushers * kPushStages) mbarrier_init(s_push_full + (tid - 96), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
+  // Every received row owes its owner a partial row: a shorter `partial` cannot be combined.
+  // The rows that exist are still pushed; the owners of the others end with a peer-abort status.
+  if (misc[kValidCount] > op.partial_rows && tid == 0 && blockIdx.x == 0)
+    report_error(c, kCapacityExceeded, kPhaseCombine, 7, static_cast<unsigned>(op.partial_rows));
   const int valid = min(misc[kValidCount], op.partial_rows);
   const int segs = op.segments;
   const long long seg_bytes = align_up((row_bytes + segs - 1) / segs, 32 * kChunk * kUnroll);
@@ -679,29 +687,32 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
 
   PushArgs push;
   push.rows_from = s_rows_from; push.first_row = s_first_row; push.stage = s_stage;
-  push.partial = partial; push.ret = ret; push.row_bytes = row_bytes; push.seg_bytes = seg_bytes;
-  push.chunk_bytes = op.push_chunk_bytes; push.segs = segs; push.most = s_most; push.valid = valid; push.self = self; push.world = W;
+  push.partial = partial; push.ret = ret; push.row_bytes = row_bytes; push.stride = stride; push.seg_bytes = seg_bytes;
+  push.segs = segs; push.most = s_most; push.valid = valid; push.self = self; push.world = W;
   BulkReduceArgs reduce;
   reduce.mask_arr = mask_arr; reduce.send_rows = send_rows; reduce.partial = partial; reduce.staging = staging;
-  reduce.out = reinterpret_cast<char*>(op.out); reduce.row_bytes = row_bytes;
+  reduce.out = reinterpret_cast<char*>(op.out); reduce.row_bytes = row_bytes; reduce.stride = stride;
   reduce.tokens = T; reduce.fan = fan; reduce.self = self; reduce.partial_rows = op.partial_rows;
   reduce.single_round = single_round; reduce.timeout_ns = c.timeout_ns; reduce.profile = op.profile;
   reduce.ctx = &c;
-  reduce.progress = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready);
-  reduce.epoch_base = epoch_base;
+  reduce.epoch = e;
 
-  if (kStreamed) {
+  if (kMode == kModeMailbox) {
     // ---- push and reduce side by side ----------------------------------------------------
-    constexpr int kReduceWarps = kStreamGroups * (kGroupWarps + 1);
-    if ((tid >> 5) == kBulkThreads / 32 - 1) {
-      herald_streamed(push, c, hdr, cl.ready, e, s_left_behind, lane);
-    } else if ((tid >> 5) >= kReduceWarps) {
-      push_streamed<kWords>(push, hdr, s_left_behind, lane);
-      if (op.profile != nullptr && tid == kReduceWarps * 32)
-        op.profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + 1] = global_timer_ns();
+    constexpr int kReduceWarps = kMailGroups * (kGroupWarps + 1);
+    const int warp = tid >> 5;
+    debug_delay(c, 4);
+    if (warp >= kReduceWarps) {
+      if (lane == 0) {
+        const int pusher = warp - kReduceWarps;
+        char* stages = dynamic_smem + kMailReduceSmem + static_cast<size_t>(pusher) * kPushStages * kPushStageBytes;
+        if (!mailbox_push(push, c, hdr, stages, s_push_full + pusher * kPushStages, e))
+          report_error(c, kTimeout, kPhaseCombine, 6, 0);
+        if (op.profile != nullptr && pusher == 0)
+          op.profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + 1] = global_timer_ns();
+      }
     } else {
-      profile_stamp(op.profile, 2);
-      if (!bulk_reduce<kStreamGroups, true>(reduce, dynamic_smem, s_full, s_empty, s_items))
+      if (!bulk_reduce<kMailGroups, true, kMailReduceSmem>(reduce, dynamic_smem, s_full, s_empty, s_items))
         report_error(c, kTimeout, kPhaseCombine, 4, 0);
     }
   } else {
@@ -752,7 +763,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   // ---- D. rank-order reduce from local memory -----------------------------------------------
   if (kBulk) {
     fence_proxy_async();      // the rows were written by generic stores; the reduce reads them through the async proxy
-    if (!bulk_reduce<kMaxGroups, false>(reduce, dynamic_smem, s_full, s_empty, s_items))
+    if (!bulk_reduce<kMaxGroups, false, kBulkSmemBytes>(reduce, dynamic_smem, s_full, s_empty, s_items))
       report_error(c, kTimeout, kPhaseCombine, 4, 0);
   } else {
     const long long items = static_cast<long long>(T) * segs;
@@ -780,7 +791,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
           is_self = (d == self);
           if (row >= 0 && !(is_self && row >= op.partial_rows))
             ptr_a = is_self ? partial + static_cast<long long>(row) * row_bytes
-                            : staging + (static_cast<long long>(t) * fan + lane) * row_bytes;
+                            : staging + (static_cast<long long>(t) * fan + lane) * stride;
         }
         const unsigned vote_a = __ballot_sync(0xffffffffu, is_self);
         is_self = false;
@@ -790,7 +801,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
           is_self = (d == self);
           if (row >= 0 && !(is_self && row >= op.partial_rows))
             ptr_b = is_self ? partial + static_cast<long long>(row) * row_bytes
-                            : staging + (static_cast<long long>(t) * fan + lane + 32) * row_bytes;
+                            : staging + (static_cast<long long>(t) * fan + lane + 32) * stride;
         }
         const unsigned vote_b = __ballot_sync(0xffffffffu, is_self);
         if (vote_a) self_index = __ffs(vote_a) - 1;
@@ -819,11 +830,13 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     }
   }
 
-  }   // !kStreamed
+  }   // sequential protocol
 
   // ---- E. retire the epoch ---------------------------------------------------------------
   __syncthreads();
+  if (kMode == kModeMailbox) profile_stamp(op.profile, 2);
   profile_stamp(op.profile, 3);
+  sample_end(op.samples, sample);
   if (tid == 0) {
     const unsigned prev = atomicAdd(&hdr->cfin_count, 1u);
     if (prev == gridDim.x - 1) {
@@ -831,18 +844,17 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       hdr->cfin_count = 0;
       hdr->cwork_push = 0;
       hdr->cwork_reduce = 0;
-      for (int chunk = 0; chunk < kMaxPushChunks; ++chunk) hdr->cpush_done[chunk] = 0;
       hdr->comb_epoch = e;
       __threadfence();
     }
   }
 }
 
-template <bool kVec16, bool kBulk, bool kStreamed>
-__global__ void __launch_bounds__(kBulk ? kBulkThreads : kThreads, 1)
+template <bool kVec16, int kMode>
+__global__ void __launch_bounds__(kMode == kModeMailbox ? kMailThreads : (kMode == kModeBulk ? kBulkThreads : kThreads), 1)
 combine_kernel(const __grid_constant__ CombineArgs args) {
   extern __shared__ __align__(128) char combine_smem[];
-  combine_body<kVec16, kBulk, kStreamed>(args.op[blockIdx.y], combine_smem);
+  combine_body<kVec16, kMode>(args.op[blockIdx.y], combine_smem);
 }
 
 struct CombineVariant {
@@ -851,21 +863,21 @@ struct CombineVariant {
   size_t dynamic_smem;
 };
 
-// The bulk-copy reduce needs 16-byte rows and at most kPeerBatch contributors per token;
-// streaming (push and reduce side by side) exists for the bulk-copy reduce only.
-cudaError_t pick_combine(bool vec16, int fanout, bool streamed, CombineVariant* out) {
+// The bulk-copy reduce needs 16-byte rows and at most kPeerBatch contributors per token; the
+// mailbox protocol exists for the bulk-copy reduce and for groups of two or more ranks.
+cudaError_t pick_combine(bool vec16, int fanout, bool mailbox, CombineVariant* out) {
   if (vec16 && fanout <= kPeerBatch) {
-    if (streamed) {
-      *out = {reinterpret_cast<const void*>(combine_kernel<true, true, true>), kBulkThreads, kBulkSmemBytes};
-      return cudaFuncSetAttribute(combine_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(kBulkSmemBytes));
+    if (mailbox) {
+      *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeMailbox>), kMailThreads, kMailSmemBytes};
+      return cudaFuncSetAttribute(combine_kernel<true, kModeMailbox>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(kMailSmemBytes));
     }
-    *out = {reinterpret_cast<const void*>(combine_kernel<true, true, false>), kBulkThreads, kBulkSmemBytes};
-    return cudaFuncSetAttribute(combine_kernel<true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeBulk>), kBulkThreads, kBulkSmemBytes};
+    return cudaFuncSetAttribute(combine_kernel<true, kModeBulk>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(kBulkSmemBytes));
   }
-  if (vec16) *out = {reinterpret_cast<const void*>(combine_kernel<true, false, false>), kThreads, 0};
-  else *out = {reinterpret_cast<const void*>(combine_kernel<false, false, false>), kThreads, 0};
+  if (vec16) *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeRegister>), kThreads, 0};
+  else *out = {reinterpret_cast<const void*>(combine_kernel<false, kModeRegister>), kThreads, 0};
   return cudaSuccess;
 }
 
@@ -878,9 +890,9 @@ cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas) {
   err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
   if (err != cudaSuccess) return err;
   int fewest = 1 << 30;
-  for (int streamed = 0; streamed < 2; ++streamed) {
+  for (int mailbox = 0; mailbox < 2; ++mailbox) {
     CombineVariant variant;
-    err = pick_combine(vec16, fanout, streamed != 0, &variant);
+    err = pick_combine(vec16, fanout, mailbox != 0, &variant);
     if (err != cudaSuccess) return err;
     err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, variant.kernel, variant.threads, variant.dynamic_smem);
     if (err != cudaSuccess) return err;
@@ -890,13 +902,13 @@ cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas) {
   return cudaSuccess;
 }
 
-bool combine_can_stream(bool vec16, int fanout) { return vec16 && fanout <= kPeerBatch; }
+bool combine_can_mailbox(bool vec16, int fanout, int world) { return vec16 && fanout <= kPeerBatch && world > 1; }
 
-cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout,
-                           bool streamed, bool cooperative, cudaStream_t stream) {
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout, int world,
+                           bool mailbox, bool cooperative, cudaStream_t stream) {
   void* params[] = {const_cast<CombineArgs*>(&args)};
   CombineVariant variant;
-  cudaError_t err = pick_combine(vec16, fanout, streamed && combine_can_stream(vec16, fanout), &variant);
+  cudaError_t err = pick_combine(vec16, fanout, mailbox && combine_can_mailbox(vec16, fanout, world), &variant);
   if (err != cudaSuccess) return err;
   const dim3 grid(ctas_per_rank, ranks, 1), block(variant.threads, 1, 1);
   if (!cooperative) return cudaLaunchKernel(variant.kernel, grid, block, params, variant.dynamic_smem, stream);

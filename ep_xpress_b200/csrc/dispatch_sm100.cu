@@ -17,9 +17,13 @@
 //                offset[self->d] = sum_{s<self} count[s->d] and valid_count[d];
 //                rows therefore land in (source rank, token) order, the order of
 //                the reference's CPU planner (ep_xpress/routing.py:140-158);
-//   4. payload   one warp per (token, row segment) loads the row once and stores
-//                it to every destination together with translated local expert
-//                ids, weights and the (source, token) inverse entry;
+//   4. payload   four mover warps per CTA claim tokens; a row is read ONCE into shared
+//                memory by a bulk asynchronous copy (TMA, no tensor map) and stored
+//                from there to every destination rank's plane by bulk copies, local
+//                and peer alike - the first loads are already in flight while the
+//                counts are awaited. The other warps write the translated local
+//                expert ids, the weights and the (source, token) inverse entry.
+//                Rows that are not 16-byte aligned take a register path;
 //   5. signal    the last CTA publishes "done" to every peer after a system fence;
 //   6. receive   padding rows are reset, valid_count is written, and the launch
 //                ends once every sender with rows for this rank has signalled.
@@ -33,6 +37,20 @@ namespace {
 constexpr unsigned kPhaseDispatch = 1;
 constexpr int kWarps = kThreads / 32;
 constexpr int kRegK = 8;   // top-k up to which a token's ids and weights are routed from registers
+constexpr int kMovers = 4;              // warps of a CTA that move payload with bulk copies
+constexpr int kMoveStages = 3;          // row pieces one mover keeps in shared memory
+constexpr int kMoveStageBytes = 14336;  // largest piece (a whole DeepSeek-V3 row)
+constexpr size_t kMoveRingBytes = static_cast<size_t>(kMovers) * kMoveStages * kMoveStageBytes;
+
+__device__ __forceinline__ void bulk_store_from_smem(void* dst, const void* src, unsigned bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_address(src)),
+               "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// The bulk copies this thread committed have finished READING shared memory (the stage may be refilled).
+__device__ __forceinline__ void bulk_wait_all_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have read their source AND their writes are complete.
+__device__ __forceinline__ void bulk_wait_all_complete() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 struct PeerPlanes {
   char* hidden;
@@ -76,6 +94,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   __shared__ char* s_heap[64];
   __shared__ PeerPlanes s_planes[64];
   __shared__ int s_last;
+  __shared__ unsigned long long s_mfull[kMovers * kMoveStages];
 
   profile_stamp(op.profile, 0);
   const unsigned g = ld_volatile_u32(&hdr->disp_epoch) + 1;
@@ -86,6 +105,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     return;
   }
   const int par = static_cast<int>(g & 1u);
+  const unsigned sample = sample_begin(op.samples, g, op.sample_capacity);
   const int dirty_prev = misc[kDirtyRows];
   unsigned long long* const my_cnt = reinterpret_cast<unsigned long long*>(my_heap + cl.cnt) +
                                      static_cast<size_t>(par) * W * W;
@@ -94,6 +114,11 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   unsigned long long* const my_done = reinterpret_cast<unsigned long long*>(my_heap + cl.done) +
                                       static_cast<size_t>(par) * W;
   if (tid < W) s_heap[tid] = c.heap[tid];
+  if (kVec16 && tid >= 64 && tid < 64 + kMovers * kMoveStages) {
+    mbarrier_init(s_mfull + (tid - 64), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
 
   // Credit + address: does not depend on routing, so it leaves first.
   if (blockIdx.x == 0 && tid < W) {
@@ -109,7 +134,9 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   // A batch of at most one tile (decode) is routed by EVERY CTA redundantly: all CTAs write
   // identical values and each reads back only what its own threads wrote before a CTA
   // barrier, so the rank-wide barrier and its round trip through L2 are skipped.
-  const bool solo = ntiles <= 1;
+  // (Fan-outs above eight spill positions to the dest_rows plane in two steps, which CTAs that
+  // run ahead of one another would overwrite with stale values: those take the barrier.)
+  const bool solo = ntiles <= 1 && fan <= 8;
   for (int tile = solo ? 0 : blockIdx.x; tile < ntiles; tile += solo ? 1 : gridDim.x) {
     const int t = tile * kRouteTile + tid;
     unsigned long long m = 0;
@@ -221,6 +248,53 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     }
   }
 
+  // ---- 4a. payload, first loads --------------------------------------------------------
+  // Movers (warps 0..kMovers-1 of every CTA) claim row pieces from the rank's counter. Which
+  // rows to read only depends on this rank's routing, so the first batch of loads is issued
+  // here and is in flight while the counts of the other ranks are awaited below.
+  const long long row_bytes = static_cast<long long>(H) * 2;
+  const int pieces = static_cast<int>((row_bytes + kMoveStageBytes - 1) / kMoveStageBytes);
+  const int piece_bytes = static_cast<int>(align_up((row_bytes + pieces - 1) / pieces, 16));
+  const long long move_items = static_cast<long long>(T) * pieces;
+  const bool mover = kVec16 && warp < kMovers;
+  char* const ring = reinterpret_cast<char*>(tile_base) + op.ring_offset +
+                     static_cast<size_t>(warp < kMovers ? warp : 0) * kMoveStages * kMoveStageBytes;
+  unsigned long long* const mfull = s_mfull + (warp < kMovers ? warp : 0) * kMoveStages;
+  // Small batches are spread one piece per claim; large ones fill every stage of a mover.
+  const long long per_mover = move_items / (static_cast<long long>(gridDim.x) * kMovers);
+  const unsigned claim = per_mover < 1 ? 1u : (per_mover > kMoveStages ? kMoveStages : static_cast<unsigned>(per_mover));
+  int b_tok[kMoveStages], b_bytes[kMoveStages];
+  long long b_b0[kMoveStages];
+  unsigned long long b_mask[kMoveStages];
+  unsigned mparity = 0;        // bit i: phase parity of stage i's barrier
+  bool more = mover;
+  auto claim_and_load = [&]() {
+    unsigned base = 0;
+    if (lane == 0) base = atomicAdd(&hdr->work_next, claim);
+    base = __shfl_sync(0xffffffffu, base, 0);
+#pragma unroll
+    for (int i = 0; i < kMoveStages; ++i) {
+      const long long item = static_cast<long long>(base) + i;
+      b_mask[i] = 0ull;
+      if (i < static_cast<int>(claim) && item < move_items) {
+        const int t = static_cast<int>(item / pieces);
+        const long long b0 = (item - static_cast<long long>(t) * pieces) * piece_bytes;
+        b_tok[i] = t;
+        b_b0[i] = b0;
+        b_bytes[i] = static_cast<int>(min(row_bytes, b0 + piece_bytes) - b0);
+        b_mask[i] = mask_arr[t];
+        if (b_mask[i] != 0ull && lane == 0) {
+          mbarrier_arrive_expect_tx(mfull + i, static_cast<unsigned>(b_bytes[i]));
+          bulk_load_to_smem(ring + static_cast<size_t>(i) * kMoveStageBytes,
+                            reinterpret_cast<const char*>(op.x) + static_cast<long long>(t) * row_bytes + b0,
+                            static_cast<unsigned>(b_bytes[i]), mfull + i);
+        }
+      }
+    }
+    more = static_cast<long long>(base) + claim < move_items;
+  };
+  if (mover) claim_and_load();
+
   // ---- 3. wait for every rank's counts and addresses ---------------------------
   // A word of a LATER generation in this parity's place means the group is out of step (a rank
   // ran more dispatches than this one): that is reported at once instead of timing out.
@@ -239,7 +313,16 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   }
   for (int i = tid; i < W * 4 && ok; i += kThreads)
     ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(my_addr + i)) == g; });
-  if (!__syncthreads_and(ok)) return;
+  if (!__syncthreads_and(ok)) {
+    // Giving up: the loads already issued still target this CTA's shared memory, so they are
+    // waited for (bounded) before the CTA may exit.
+    if (mover) {
+#pragma unroll
+      for (int i = 0; i < kMoveStages; ++i)
+        if (b_mask[i] != 0ull) mbarrier_wait_bounded(mfull + i, (mparity >> i) & 1u, c.timeout_ns);
+    }
+    return;
+  }
   profile_stamp(op.profile, 3);
   debug_delay(c, 2);
 
@@ -279,7 +362,90 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   __syncthreads();
 
   // ---- 4. payload --------------------------------------------------------------
-  const long long row_bytes = static_cast<long long>(H) * 2;
+  if (kVec16) {
+    if (mover) {
+      // Stores of the batch whose loads are in flight, then the next claim. Lane j issues the
+      // copy to the j-th destination; every lane tracks its own copies (bulk async-groups are
+      // per thread) and all of them have read the stage before it is refilled.
+      bool moving = true;
+      while (moving) {
+#pragma unroll
+        for (int i = 0; i < kMoveStages; ++i) {
+          const unsigned long long m = b_mask[i];
+          if (m == 0ull || !moving) continue;                       // warp-uniform
+          if (!__all_sync(0xffffffffu, mbarrier_wait_bounded(mfull + i, (mparity >> i) & 1u, c.timeout_ns))) {
+            if (lane == 0) report_error(c, kTimeout, kPhaseDispatch, 8, static_cast<unsigned>(b_tok[i]));
+            moving = false;
+            continue;
+          }
+          mparity ^= 1u << i;
+          fence_proxy_async();
+          const int t = b_tok[i], n = __popcll(m), tile = t / kRouteTile;
+          for (int j = lane; j < n; j += 32) {
+            const int d = nth_set_bit(m, j);
+            if (!s_ok[d]) continue;
+            const long long row = static_cast<long long>(s_off[d]) + tile_base[tile * W + d] +
+                                  dest_rows[static_cast<long long>(t) * fan + j];
+            bulk_store_from_smem(s_planes[d].hidden + row * row_bytes + b_b0[i],
+                                 ring + static_cast<size_t>(i) * kMoveStageBytes, static_cast<unsigned>(b_bytes[i]));
+          }
+        }
+        bulk_commit_group();
+        bulk_wait_all_read();
+        if (!more || !moving) break;
+        claim_and_load();
+      }
+      bulk_wait_all_complete();
+      fence_proxy_async();     // the rows went out through the async proxy; the signal below is an ordinary store
+    } else {
+      // Row metadata: translated local expert ids, weights, inverse entry and return slot of
+      // every (token, destination), and this rank's record of where each row went.
+      const int meta_warps = kWarps - kMovers;
+      const int first = static_cast<int>(blockIdx.x) * meta_warps + (warp - kMovers);
+      const int step = static_cast<int>(gridDim.x) * meta_warps;
+      for (int t = first; t < T; t += step) {
+        const unsigned long long m = mask_arr[t];
+        if (m == 0ull) continue;
+        const int n = __popcll(m), tile = t / kRouteTile;
+        for (int k0 = 0; k0 < K; k0 += 32) {
+          const int k = k0 + lane;
+          long long local = -1;
+          int owner = -1;
+          float w = 0.f;
+          if (k < K) {
+            const long long id = load_id<IdT>(op.ids, static_cast<long long>(t) * K + k);
+            if (id >= 0) {
+              w = op.weights[static_cast<long long>(t) * K + k];
+              owner = c.expert_rank[id];
+              local = c.expert_local[id];
+            }
+          }
+          unsigned long long rest = m;
+          for (int j = 0; j < n; ++j, rest &= rest - 1) {
+            const int d = __ffsll(static_cast<long long>(rest)) - 1;
+            if (!s_ok[d]) continue;
+            const long long row = static_cast<long long>(s_off[d]) + tile_base[tile * W + d] +
+                                  dest_rows[static_cast<long long>(t) * fan + j];
+            if (k < K) {
+              reinterpret_cast<long long*>(s_planes[d].ids)[row * K + k] = owner == d ? local : -1;
+              reinterpret_cast<float*>(s_planes[d].weights)[row * K + k] = w;
+            }
+            if (k == 0) {
+              long long* inv = reinterpret_cast<long long*>(s_planes[d].inverse) + row * 2;
+              inv[0] = self;
+              inv[1] = t;
+              reinterpret_cast<int*>(s_planes[d].ret)[row] = t * fan + j;
+            }
+          }
+        }
+        for (int j = lane; j < n; j += 32) {
+          const int d = nth_set_bit(m, j);
+          send_rows[static_cast<long long>(t) * fan + j] =
+              s_ok[d] ? s_off[d] + tile_base[tile * W + d] + dest_rows[static_cast<long long>(t) * fan + j] : -1;
+        }
+      }
+    }
+  } else {
   constexpr int kChunk = kVec16 ? 16 : 4;
   constexpr int kUnroll = 4;
   const int segs = op.segments;
@@ -368,6 +534,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     }
   }
 
+  }   // register path
   // ---- 5. signal -----------------------------------------------------------------
   const int valid = s_ok[self] ? s_total[self] : 0;
   debug_delay(c, 3);
@@ -433,11 +600,12 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return tag_of(ld_acquire_sys(my_done + tid)) == g; });
   __syncthreads_and(ok);
   profile_stamp(op.profile, 7);
+  sample_end(op.samples, sample);
 }
 
 template <typename IdT, bool kVec16>
 __global__ void __launch_bounds__(kThreads, 1) dispatch_kernel(const __grid_constant__ DispatchArgs args) {
-  extern __shared__ int tile_base[];
+  extern __shared__ __align__(128) int tile_base[];
   dispatch_body<IdT, kVec16>(args.op[blockIdx.y], tile_base);
 }
 
@@ -450,8 +618,12 @@ DispatchKernel pick_kernel(bool ids64, bool vec16) {
 
 }  // namespace
 
-size_t dispatch_dynamic_smem(int max_tokens, int world) {
-  return static_cast<size_t>(route_tiles(max_tokens) + 1) * world * sizeof(int);
+size_t dispatch_ring_offset(int max_tokens, int world) {
+  return align_up(static_cast<size_t>(route_tiles(max_tokens) + 1) * world * sizeof(int), 128);
+}
+
+size_t dispatch_dynamic_smem(int max_tokens, int world, bool vec16) {
+  return dispatch_ring_offset(max_tokens, world) + (vec16 ? kMoveRingBytes : 0);
 }
 
 cudaError_t dispatch_max_ctas(bool ids64, bool vec16, size_t dynamic_smem, int* ctas) {

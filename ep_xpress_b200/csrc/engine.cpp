@@ -17,6 +17,7 @@
 
 #include "epx_launch.h"
 #include "heap.h"
+#include "host_helpers.h"
 
 namespace py = pybind11;
 
@@ -98,10 +99,6 @@ class Engine {
     if (tables_ != nullptr) cudaFree(tables_);
   }
 
-  // 1: push and reduce side by side wherever the bulk-copy reduce applies; 0 or -1: one after
-  // the other. (-1, "auto", is reserved for a size rule; on B200 the sequential order measured
-  // faster at every size tried, because a system-scope fence does not complete while the same SM
-  // keeps storing to a peer, so progress cannot be published before the push is over.)
   // Debugging: every CTA sleeps a pseudo-random time below `ns` at each phase boundary, which
   // shakes the interleaving of ranks and CTAs without changing any result.
   void set_debug_delay(int64_t ns) {
@@ -112,11 +109,13 @@ class Engine {
     cuda_check(cudaMemcpy(ctx_, host_ctx_.data(), sizeof(RankCtx) * host_ctx_.size(), cudaMemcpyHostToDevice),
                "upload rank contexts");
   }
-  // `chunk_bytes`: how much a rank pushes between two progress publications (0 keeps the value).
-  void set_combine_streaming(int mode, int64_t chunk_bytes) {
-    streaming_ = mode;
-    if (chunk_bytes > 0) push_chunk_bytes_ = chunk_bytes;
-  }
+  // 0: the sequential combine protocol (push, signal, wait, reduce) everywhere; anything else:
+  // the mailbox protocol (push and reduce side by side, one arrival word per row) wherever it
+  // applies. Every rank of a group must make the same choice.
+  void set_combine_streaming(int mode) { streaming_ = mode; }
+  // Whether the mailbox combine protocol applies to this group's shape (16-byte rows, fan-out
+  // up to eight, two or more ranks); tensors that are not 16-byte aligned still fall back.
+  bool can_mailbox() const { return combine_can_mailbox(hidden_ % 8 == 0, route_fanout(topk_, world_), world_); }
   int sm_count() const { return sms_; }
   std::vector<int> experts_per_rank() const { return experts_per_rank_; }
   size_t ctrl_bytes() const { return ctrl_layout(world_).bytes; }
@@ -134,11 +133,11 @@ class Engine {
   // Largest per-rank CTA count a cooperative launch of every variant may use.
   int max_ctas(int64_t max_tokens) const {
     c10::cuda::CUDAGuard guard(device_);
-    const size_t smem = dispatch_dynamic_smem(static_cast<int>(max_tokens), world_);
     int best = 1 << 30;
     for (int ids64 = 0; ids64 < 2; ++ids64)
       for (int vec = 0; vec < 2; ++vec) {
         int ctas = 0;
+        const size_t smem = dispatch_dynamic_smem(static_cast<int>(max_tokens), world_, vec != 0);
         cuda_check(dispatch_max_ctas(ids64, vec, smem, &ctas), "dispatch occupancy query");
         best = std::min(best, ctas);
       }
@@ -174,7 +173,8 @@ class Engine {
                 const std::vector<at::Tensor>& weights, const std::vector<int64_t>& slot_off,
                 const std::vector<int64_t>& capacity, const std::vector<int64_t>& slot_capacity,
                 const std::vector<int64_t>& slot_tokens, uint64_t identity, int ctas, bool zero_padding,
-                int64_t stream, const std::optional<at::Tensor>& profile) const {
+                int64_t stream, const std::optional<at::Tensor>& profile,
+                const std::optional<at::Tensor>& samples) const {
     const size_t n = local_ranks_.size();
     TORCH_CHECK(x.size() == n && ids.size() == n && weights.size() == n && slot_off.size() == n &&
                 capacity.size() == n && slot_capacity.size() == n && slot_tokens.size() == n,
@@ -223,14 +223,18 @@ class Engine {
       op.zero_padding = zero_padding ? 1 : 0;
     }
     TORCH_CHECK(route_tiles(static_cast<int>(max_tokens)) <= kMaxRouteTiles, "too many tokens for one dispatch");
-    const size_t smem = dispatch_dynamic_smem(static_cast<int>(max_tokens), world_);
+    const size_t smem = dispatch_dynamic_smem(static_cast<int>(max_tokens), world_, vec16);
     ctas = std::max(1, ctas);
     const int segments = pick_segments(max_tokens, ctas);
     for (size_t i = 0; i < n; ++i) {
       args.op[i].segments = segments;
       args.op[i].vec16 = vec16 ? 1 : 0;
+      args.op[i].ring_offset = static_cast<int>(dispatch_ring_offset(static_cast<int>(max_tokens), world_));
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
+    attach_samples(samples, n, [&](size_t i, unsigned long long* ring, int capacity) {
+      args.op[i].samples = ring; args.op[i].sample_capacity = capacity;
+    });
     cuda_check(launch_dispatch(args, static_cast<int>(n), ctas, ids64, vec16, smem, cooperative_, stream_of(stream)),
                "dispatch launch");
   }
@@ -238,7 +242,7 @@ class Engine {
   void combine(const std::vector<std::optional<at::Tensor>>& partial, const std::vector<at::Tensor>& out,
                const std::vector<int64_t>& slot_off, const std::vector<int64_t>& slot_capacity,
                const std::vector<int64_t>& slot_tokens, uint64_t identity, int ctas, int64_t stream,
-               const std::optional<at::Tensor>& profile) const {
+               const std::optional<at::Tensor>& profile, int mailbox, const std::optional<at::Tensor>& samples) const {
     const size_t n = local_ranks_.size();
     TORCH_CHECK(partial.size() == n && out.size() == n && slot_off.size() == n && slot_capacity.size() == n &&
                 slot_tokens.size() == n, "combine needs one entry per local rank");
@@ -285,12 +289,13 @@ class Engine {
     for (size_t i = 0; i < n; ++i) {
       args.op[i].segments = segments;
       args.op[i].vec16 = vec16 ? 1 : 0;
-      args.op[i].push_chunk_bytes = push_chunk_bytes_;
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
+    attach_samples(samples, n, [&](size_t i, unsigned long long* ring, int capacity) {
+      args.op[i].samples = ring; args.op[i].sample_capacity = capacity;
+    });
     const int fanout = route_fanout(topk_, world_);
-    const bool streamed = world_ > 1 && streaming_ > 0;
-    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, fanout, streamed, cooperative_,
+    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, fanout, world_, mailbox < 0 ? streaming_ != 0 : mailbox != 0, cooperative_,
                               stream_of(stream)), "combine launch");
   }
 
@@ -384,13 +389,25 @@ class Engine {
       assign(i, reinterpret_cast<unsigned long long*>(p.data_ptr<int64_t>()) + i * ctas * kProfileStamps);
   }
 
+  // samples: int64 [ranks, 1 + capacity, kSampleWords] on the context device, or nothing.
+  template <typename Assign>
+  void attach_samples(const std::optional<at::Tensor>& samples, size_t ranks, Assign assign) const {
+    if (!samples.has_value()) return;
+    const at::Tensor& t = *samples;
+    TORCH_CHECK(t.is_cuda() && t.get_device() == device_ && t.scalar_type() == at::kLong && t.is_contiguous() &&
+                t.dim() == 3 && t.size(0) == static_cast<int64_t>(ranks) && t.size(1) >= 2 && t.size(2) == kSampleWords,
+                "samples must be a contiguous int64 CUDA tensor [ranks, 1 + capacity, 4]");
+    for (size_t i = 0; i < ranks; ++i)
+      assign(i, reinterpret_cast<unsigned long long*>(t.data_ptr<int64_t>()) + i * t.size(1) * kSampleWords,
+             static_cast<int>(t.size(1) - 1));
+  }
+
   int world_;
   std::vector<int> local_ranks_;
   int hidden_, topk_, device_;
   bool cooperative_ = true;
   std::vector<RankCtx> host_ctx_;
   int streaming_ = -1;
-  int64_t push_chunk_bytes_ = 16ll << 20;
   int sms_ = 0;
   std::vector<int> experts_per_rank_;
   std::vector<char*> own_heap_;
@@ -408,6 +425,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.attr("MAX_EMULATED_RANKS") = kMaxEmulatedRanks;
   m.attr("THREADS") = kThreads;
   m.attr("PROFILE_STAMPS") = kProfileStamps;
+  m.attr("SAMPLE_WORDS") = kSampleWords;
   m.def("heap_allocate", [](size_t bytes) { return reinterpret_cast<int64_t>(HeapRegistry::instance().allocate(bytes)); });
   m.def("heap_export", [](int64_t base) { return py::bytes(HeapRegistry::instance().export_handle(reinterpret_cast<void*>(base))); });
   m.def("heap_open", [](const std::string& handle, size_t bytes) {
@@ -419,6 +437,44 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("slot_bytes", [](int64_t capacity, int64_t tokens, int hidden, int topk, int world) {
     return slot_layout(capacity, tokens, hidden, topk, world).bytes;
   });
+  // ---- helpers of the host-staged transport (host_helpers.cu) ----
+  m.def("register_host", [](int64_t address, size_t bytes) { register_host_range(reinterpret_cast<void*>(address), bytes); });
+  m.def("unregister_host", [](int64_t address) { unregister_host_range(reinterpret_cast<void*>(address)); });
+  m.def("registered_host_ranges", [] { return registered_host_ranges(); });
+  m.def("copy_d2h_async", [](const at::Tensor& source, int64_t host_address, int64_t stream) {
+    TORCH_CHECK(source.is_cuda() && source.is_contiguous(), "the source must be a contiguous CUDA tensor");
+    c10::cuda::CUDAGuard guard(source.device());
+    cuda_check(copy_device_to_registered_host(source.data_ptr(), reinterpret_cast<void*>(host_address),
+                                              static_cast<size_t>(source.numel()) * source.element_size(),
+                                              stream_of(stream)), "device-to-host copy");
+  });
+  m.def("add_partial", [](at::Tensor& accum, const at::Tensor& partial, const at::Tensor& index, at::Tensor& status,
+                          int64_t stream) {
+    TORCH_CHECK(accum.is_cuda() && accum.scalar_type() == at::kFloat && accum.dim() == 2 && accum.is_contiguous(),
+                "accum must be a contiguous FP32 CUDA tensor [tokens, hidden]");
+    TORCH_CHECK(partial.is_cuda() && partial.scalar_type() == at::kBFloat16 && partial.dim() == 2 &&
+                partial.is_contiguous() && partial.size(1) == accum.size(1),
+                "partial must be a contiguous BF16 CUDA tensor [rows, hidden]");
+    TORCH_CHECK(index.is_cuda() && index.scalar_type() == at::kLong && index.is_contiguous() &&
+                index.numel() == partial.size(0), "index must be a contiguous int64 CUDA tensor [rows]");
+    TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() == 1, "status must be int32[1]");
+    c10::cuda::CUDAGuard guard(accum.device());
+    cuda_check(launch_add_partial(accum.data_ptr<float>(), partial.data_ptr(),
+                                  reinterpret_cast<const long long*>(index.data_ptr<int64_t>()), partial.size(0),
+                                  accum.size(0), static_cast<int>(accum.size(1)), status.data_ptr<int>(),
+                                  stream_of(stream)), "add_partial launch");
+  });
+  m.def("finish_combine", [](const at::Tensor& remote, const at::Tensor& local, at::Tensor& out, bool single_round,
+                             int64_t stream) {
+    TORCH_CHECK(remote.is_cuda() && remote.scalar_type() == at::kFloat && remote.is_contiguous() &&
+                local.is_cuda() && local.scalar_type() == at::kFloat && local.is_contiguous() &&
+                local.numel() == remote.numel(), "remote and local must be contiguous FP32 CUDA tensors of one shape");
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.is_contiguous() &&
+                out.numel() == remote.numel(), "out must be a contiguous BF16 CUDA tensor of the same shape");
+    c10::cuda::CUDAGuard guard(remote.device());
+    cuda_check(launch_finish_combine(remote.data_ptr<float>(), local.data_ptr<float>(), out.data_ptr(), remote.numel(),
+                                     single_round, stream_of(stream)), "finish_combine launch");
+  });
   py::class_<Engine>(m, "Engine")
       .def(py::init<int, std::vector<int>, int, int, std::vector<int>, std::vector<std::vector<int64_t>>, double, bool, int, bool>(),
            py::arg("world"), py::arg("local_ranks"), py::arg("hidden"), py::arg("topk"), py::arg("expert_to_rank"),
@@ -426,7 +482,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("cooperative") = true)
       .def("sm_count", &Engine::sm_count)
       .def("set_debug_delay", &Engine::set_debug_delay)
-      .def("set_combine_streaming", &Engine::set_combine_streaming, py::arg("mode"), py::arg("chunk_bytes") = 0)
+      .def("set_combine_streaming", &Engine::set_combine_streaming, py::arg("mode"))
       .def("experts_per_rank", &Engine::experts_per_rank)
       .def("ctrl_bytes", &Engine::ctrl_bytes)
       .def("ctrl_offsets", &Engine::ctrl_offsets)
@@ -436,10 +492,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("slot_reset", &Engine::slot_reset)
       .def("dispatch", &Engine::dispatch, py::arg("x"), py::arg("ids"), py::arg("weights"), py::arg("slot_off"),
            py::arg("capacity"), py::arg("slot_capacity"), py::arg("slot_tokens"), py::arg("identity"),
-           py::arg("ctas"), py::arg("zero_padding"), py::arg("stream"), py::arg("profile") = py::none())
+           py::arg("ctas"), py::arg("zero_padding"), py::arg("stream"), py::arg("profile") = py::none(),
+           py::arg("samples") = py::none())
       .def("combine", &Engine::combine, py::arg("partial"), py::arg("out"), py::arg("slot_off"),
            py::arg("slot_capacity"), py::arg("slot_tokens"), py::arg("identity"), py::arg("ctas"), py::arg("stream"),
-           py::arg("profile") = py::none())
+           py::arg("profile") = py::none(), py::arg("mailbox") = -1, py::arg("samples") = py::none())
+      .def("combine_can_mailbox", &Engine::can_mailbox)
       .def("scale_rows", &Engine::scale_rows)
       .def("status", &Engine::status)
       .def("poke_u64", &Engine::poke_u64)

@@ -216,6 +216,28 @@ __device__ __forceinline__ void profile_stamp(unsigned long long* profile, int i
     profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + index] = global_timer_ns();
 }
 
+// Sample ring of graph-replayed operations (layout: kSampleWords in epx_layout.h). Returns the
+// sample index of the operation with `generation`, or ~0u when nothing is to be recorded;
+// thread 0 of every CTA offers its start time. An operation beyond the ring's capacity only
+// counts itself as dropped (once, by CTA 0).
+__device__ __forceinline__ unsigned sample_begin(unsigned long long* ring, unsigned generation, int capacity) {
+  if (ring == nullptr || threadIdx.x != 0) return ~0u;
+  if (ld_relaxed_sys(ring + 2) == 0ull) return ~0u;
+  const unsigned index = generation - static_cast<unsigned>(ld_relaxed_sys(ring + 1));
+  if (index < static_cast<unsigned>(capacity)) {
+    atomicMin(ring + static_cast<size_t>(1 + index) * kSampleWords, global_timer_ns());
+    return index;
+  }
+  if (blockIdx.x == 0 && static_cast<int>(index) >= capacity) atomicAdd(ring, 1ull);
+  return ~0u;
+}
+__device__ __forceinline__ void sample_end(unsigned long long* ring, unsigned index) {
+  if (index == ~0u) return;
+  unsigned long long* row = ring + static_cast<size_t>(1 + index) * kSampleWords;
+  atomicMax(row + 1, global_timer_ns());
+  atomicAdd(row + 2, 1ull);
+}
+
 __device__ __forceinline__ float bf16_bits_to_float(unsigned short bits) {
   return __uint_as_float(static_cast<unsigned>(bits) << 16);
 }

@@ -5,9 +5,11 @@
 
 namespace epx {
 
-// Dynamic shared memory of the dispatch kernel for a slot laid out for
-// `max_tokens` local tokens.
-size_t dispatch_dynamic_smem(int max_tokens, int world);
+// Dynamic shared memory of the dispatch kernel for a launch of at most `max_tokens` local
+// tokens: the per-tile prefix table, then (16-byte rows only) the movers' stage rings, which
+// start at `dispatch_ring_offset`.
+size_t dispatch_ring_offset(int max_tokens, int world);
+size_t dispatch_dynamic_smem(int max_tokens, int world, bool vec16);
 
 // Largest number of CTAs of each kernel that can be resident at once on the
 // current device; a cooperative launch may not exceed it. (The reference
@@ -22,16 +24,14 @@ cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas);
 // other kernel holding the SMs forever).
 cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
                             size_t dynamic_smem, bool cooperative, cudaStream_t stream);
-// `streamed`: push and reduce run side by side in every CTA (a few warps push while the others
-// already reduce the tokens whose rows have arrived) instead of one after the other. Opt-in:
-// on B200 the sequential order measured faster (2 GPUs, 4096 tokens: 154 us against 161 us),
-// because progress can only be published behind a system-scope fence and that fence does not
-// complete while the same SM keeps storing to a peer. It is ignored where the bulk-copy reduce
-// does not apply (`combine_can_stream`). Every rank may choose on its own: the progress words
-// that peers exchange are the same in both modes.
-bool combine_can_stream(bool vec16, int fanout);
-cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout,
-                           bool streamed, bool cooperative, cudaStream_t stream);
+// `mailbox`: push and reduce run side by side in every CTA (pusher warps move rows with bulk
+// copies and release one arrival word per row; the other warps reduce a token as soon as the
+// rows it is owed are in) instead of one after the other. It applies to 16-byte rows, fan-outs
+// up to eight and groups of two or more ranks (`combine_can_mailbox`); elsewhere, and when not
+// asked for, the sequential protocol runs. All ranks of a group must choose the same protocol.
+bool combine_can_mailbox(bool vec16, int fanout, int world);
+cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout, int world,
+                           bool mailbox, bool cooperative, cudaStream_t stream);
 
 // Synthetic expert used by the validation harness and the communication
 // benchmark: partial[row] = bf16(hidden[row] * sum_k weights[row,k] * factor[local_ids[row,k]])

@@ -30,6 +30,8 @@ constexpr int kRouteTile = kThreads; // tokens routed per CTA iteration
 constexpr int kSlotAlign = 256;      // every sub-buffer starts on a 256-byte boundary
 constexpr int kMaxRouteTiles = 8192; // bound of the per-CTA prefix table
 constexpr int kProfileStamps = 8;    // phase timestamps one CTA records when profiling
+constexpr int kFlagLine = 128;       // arrival words that follow every staging row (one u32 per row segment)
+constexpr int kMaxRowSegments = kFlagLine / 4;
 
 // Sticky status codes (same meaning as ep_xpress/host_sm.py:32-38).
 enum Status : int {
@@ -64,10 +66,8 @@ struct CtrlHeader {
   unsigned cwork_push;      // combine: next unclaimed (row, segment) item of the push phase
   unsigned cwork_reduce;    // combine: next unclaimed (token, segment) item of the reduce phase
   unsigned reserved0;
-  unsigned cpush_done[8];   // combine, streamed push: push warps that left chunk c behind them
-  unsigned long long reserved[21];
+  unsigned long long reserved[25];
 };
-constexpr int kMaxPushChunks = 8;
 static_assert(sizeof(CtrlHeader) == 256, "control header is one 256-byte block");
 
 struct CtrlLayout {
@@ -105,7 +105,8 @@ struct SlotLayout {
   size_t weights;    // f32   [capacity, topk]
   size_t inverse;    // int64 [capacity, 2]
   size_t ret;        // i32   [capacity]           where the row's result goes back: token * fanout + j
-  size_t staging;    // bf16  [tokens * fanout, hidden]  partial rows pushed back by the expert ranks
+  size_t staging;    // [tokens * fanout] x (bf16 [hidden] + kFlagLine bytes of arrival words): partial rows
+                     // pushed back by the expert ranks, each followed by the combine epoch per row segment
   // rank-local
   size_t partial;    // bf16  [capacity, hidden]   default output plane of the expert runner
   size_t mask;       // u64   [tokens]             destination-rank set per token
@@ -125,6 +126,8 @@ enum MiscWord : int { kValidCount = 0, kDirtyRows = 1, kSendTotal = 2 };
 
 EPX_HD int route_fanout(int topk, int world) { return topk < world ? topk : world; }
 EPX_HD int route_tiles(int tokens) { return (tokens + kRouteTile - 1) / kRouteTile; }
+// Distance between two staging rows: the BF16 row plus its line of arrival words.
+EPX_HD size_t staging_stride(int hidden) { return static_cast<size_t>(hidden) * 2 + kFlagLine; }
 
 EPX_HD SlotLayout slot_layout(long long capacity, long long tokens, int hidden, int topk, int world) {
   SlotLayout l;
@@ -138,7 +141,7 @@ EPX_HD SlotLayout slot_layout(long long capacity, long long tokens, int hidden, 
   l.weights = take(c * k * 4);
   l.inverse = take(c * 16);
   l.ret = take(c * 4);
-  l.staging = take(t * static_cast<size_t>(route_fanout(topk, world)) * h * 2);
+  l.staging = take(t * static_cast<size_t>(route_fanout(topk, world)) * staging_stride(hidden));
   l.partial = take(c * h * 2);
   l.mask = take(t * 8);
   l.dest_rows = take(t * static_cast<size_t>(route_fanout(topk, world)) * 4);
@@ -179,6 +182,8 @@ struct DispatchOp {
   unsigned long long slot_off;
   unsigned long long identity;  // diagnostics: hash of (phase, tag); 0 when off
   unsigned long long* profile;  // null, or [ctas, kProfileStamps] globaltimer stamps of this launch
+  unsigned long long* samples;  // null, or a sample ring (kSampleWords below) that replays keep filling
+  int sample_capacity;
   int tokens;
   int capacity;           // row bound of this operation (<= slot_capacity)
   int slot_capacity;      // capacity the slot was laid out for
@@ -187,6 +192,7 @@ struct DispatchOp {
   int segments;           // pieces a row is split into for the payload phase
   int vec16;              // rows are 16-byte aligned and hidden % 8 == 0
   int zero_padding;       // zero hidden rows in [valid, previous valid)
+  int ring_offset;        // dynamic shared memory: where the movers' stage rings start (after the tile prefix table)
 };
 
 struct CombineOp {
@@ -196,14 +202,23 @@ struct CombineOp {
   unsigned long long slot_off;
   unsigned long long identity;
   unsigned long long* profile;  // null, or [ctas, kProfileStamps] globaltimer stamps of this launch
+  unsigned long long* samples;  // null, or a sample ring (kSampleWords below) that replays keep filling
+  int sample_capacity;
   int tokens;
   int slot_capacity;
   int slot_tokens;
   int segments;
   int vec16;
-  int partial_rows;       // rows of `partial`; rows at or above it are not pushed
-  long long push_chunk_bytes;  // streamed launches: bytes pushed between two progress publications
+  int partial_rows;       // rows of `partial`; fewer than the received rows is an error
 };
+
+// Bounded timing record of operations that run from CUDA graphs (every replay is a new
+// operation, the storage is fixed at capture): u64 [1 + capacity][kSampleWords]. Row 0 is the
+// header {operations that found the ring full, generation that maps to sample 0, enabled, -},
+// written by the host at quiescent points only; row 1 + i belongs to the operation whose
+// generation is base + i and holds {earliest CTA start, latest CTA end, CTAs that finished, -}
+// on the GPU's global timer (ns). The host presets starts to ~0 and ends to 0.
+constexpr int kSampleWords = 4;
 
 struct DispatchArgs { DispatchOp op[kMaxEmulatedRanks]; };
 struct CombineArgs { CombineOp op[kMaxEmulatedRanks]; };

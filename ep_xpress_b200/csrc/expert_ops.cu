@@ -95,6 +95,11 @@ __global__ void __launch_bounds__(256) slot_reset_kernel(char* slot, SlotLayout 
   for (long long i = me; i < capacity * topk; i += threads) { ids[i] = -1; w[i] = 0.f; }
   long long* inv = reinterpret_cast<long long*>(slot + l.inverse);
   for (long long i = me; i < capacity * 2; i += threads) inv[i] = -1;
+  // Arrival words behind the staging rows must never equal a combine epoch by accident (a
+  // re-used heap range holds old payload): the whole plane starts at zero.
+  uint4* stage = reinterpret_cast<uint4*>(slot + l.staging);
+  const long long stage_vecs = static_cast<long long>(l.partial - l.staging) / 16;
+  for (long long i = me; i < stage_vecs; i += threads) stage[i] = make_uint4(0u, 0u, 0u, 0u);
   unsigned* local = reinterpret_cast<unsigned*>(slot + l.mask);
   const long long local_words = static_cast<long long>(l.output - l.mask) / 4;
   for (long long i = me; i < local_words; i += threads) local[i] = 0u;

@@ -5,6 +5,7 @@
 // resolved once per device with cudaGetSymbolAddress and carved up below.
 #include "moe_noalloc.h"
 
+#include <cstdint>
 #include <mutex>
 
 #include "moe_gemm.h"
@@ -66,6 +67,24 @@ cudaError_t device_state(DeviceState** out) {
 
 extern "C" unsigned long long epx_moe_noalloc_scratch_bytes(void) { return kScratchBytes; }
 
+extern "C" int epx_moe_noalloc_last_status(cudaStream_t stream, int* status, int* cuda_error) {
+  if (cuda_error != nullptr) *cuda_error = 0;
+  if (status == nullptr) return EPX_NOALLOC_BAD_ARGUMENT;
+  auto fail = [&](cudaError_t err) {
+    if (cuda_error != nullptr) *cuda_error = static_cast<int>(err);
+    return EPX_NOALLOC_CUDA_ERROR;
+  };
+  DeviceState* state = nullptr;
+  cudaError_t err = device_state(&state);
+  if (err != cudaSuccess) return fail(err);
+  const int* error_flag = reinterpret_cast<const int*>(state->scratch + kOffCounters) + 2;
+  err = cudaMemcpyAsync(status, error_flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (err != cudaSuccess) return fail(err);
+  err = cudaStreamSynchronize(stream);
+  if (err != cudaSuccess) return fail(err);
+  return EPX_NOALLOC_OK;
+}
+
 extern "C" int epx_moe_forward_noalloc(const void* hidden, const long long* local_ids, const float* weights,
                                        const int* valid_count, const void* w13, const void* w2, void* partial,
                                        int rows, int topk, int experts, int hidden_size, int inter_size,
@@ -75,11 +94,15 @@ extern "C" int epx_moe_forward_noalloc(const void* hidden, const long long* loca
       w2 == nullptr || partial == nullptr || rows < 0 || topk <= 0 || experts <= 0 || hidden_size <= 0 ||
       inter_size <= 0 || hidden_size % 256 != 0 || inter_size % 128 != 0)
     return EPX_NOALLOC_BAD_ARGUMENT;
+  // A misaligned pointer would fault inside a kernel (16-byte vector accesses, TMA): reject it here.
+  auto aligned = [](const void* p, uintptr_t to) { return reinterpret_cast<uintptr_t>(p) % to == 0; };
+  if (!aligned(hidden, 16) || !aligned(partial, 16) || !aligned(w13, 16) || !aligned(w2, 16) ||
+      !aligned(local_ids, 8) || !aligned(weights, 4) || !aligned(valid_count, 4))
+    return EPX_NOALLOC_BAD_ARGUMENT;
   const epx::MoeSizes sizes = epx::moe_sizes(rows, topk, experts);
   if (sizes.max_sorted_rows > kSortedRows || static_cast<long long>(rows) * topk > kMaxPairs ||
       hidden_size > kMaxHidden || inter_size > kMaxInter)
     return EPX_NOALLOC_TOO_LARGE;
-  if (rows == 0) return EPX_NOALLOC_OK;
 
   auto fail = [&](cudaError_t err) {
     if (cuda_error != nullptr) *cuda_error = static_cast<int>(err);
@@ -103,6 +126,7 @@ extern "C" int epx_moe_forward_noalloc(const void* hidden, const long long* loca
   // (sorted_row, sorted_scale and entry_pos are rewritten in full by the align step.)
   err = cudaMemsetAsync(counters, 0, 256, stream);
   if (err != cudaSuccess) return fail(err);
+  if (rows == 0) return EPX_NOALLOC_OK;
   const long long sorted_rows = sizes.max_sorted_rows;   // <= kSortedRows, a multiple of 128
   err = epx::launch_moe_align(local_ids, weights, valid_count, rows, topk, experts, sorted_rows, sizes.max_tiles,
                               sorted_row, sorted_scale, entry_pos, tile_expert, counters, error_flag,

@@ -45,12 +45,26 @@ enum {
 //   w13         bf16  [experts, 2 * inter_size, hidden_size]  device (gate rows, then up rows)
 //   w2          bf16  [experts, hidden_size, inter_size]      device
 //   partial     bf16  [rows, hidden_size]      device, output
-// hidden_size must be a multiple of 256 and inter_size of 128. Returns an EPX_NOALLOC_* code;
-// `cuda_error`, when not null, receives the cudaError_t behind EPX_NOALLOC_CUDA_ERROR.
+// hidden_size must be a multiple of 256 and inter_size of 128. Alignment (checked on the host,
+// nothing is launched when it fails, EPX_NOALLOC_BAD_ARGUMENT): hidden, partial, w13 and w2 on
+// 16 bytes (rows are moved as 16-byte vectors and fed to TMA), local_ids on 8, weights and
+// valid_count on 4. Returns an EPX_NOALLOC_* code; `cuda_error`, when not null, receives the
+// cudaError_t behind EPX_NOALLOC_CUDA_ERROR. EPX_NOALLOC_OK means "enqueued": what the kernels
+// found while running is read with epx_moe_noalloc_last_status.
 int epx_moe_forward_noalloc(const void* hidden, const long long* local_ids, const float* weights,
                             const int* valid_count, const void* w13, const void* w2, void* partial, int rows,
                             int topk, int experts, int hidden_size, int inter_size, cudaStream_t stream,
                             int* cuda_error);
+
+// Status word that the kernels of the MOST RECENT epx_moe_forward_noalloc call on the current
+// device left in the static workspace: 0 = fine, 1 = a bounded wait inside a GEMM gave up (the
+// output is incomplete), 2 = more local (row, slot) pairs than the workspace holds (pairs were
+// dropped). The word is cleared at the start of every call and shared like the rest of the
+// array, so read it before the next call is enqueued. Allocates nothing: the word is copied
+// from the array to `*status` on `stream` and the stream is synchronised before returning.
+// Returns an EPX_NOALLOC_* code (BAD_ARGUMENT for a null `status`, CUDA_ERROR with the
+// cudaError_t in `*cuda_error`); before any forward call on the device the status is 0.
+int epx_moe_noalloc_last_status(cudaStream_t stream, int* status, int* cuda_error);
 
 // Size of the library's static workspace in bytes (for documentation and tests).
 unsigned long long epx_moe_noalloc_scratch_bytes(void);

@@ -114,7 +114,7 @@ class TransportCore:
         ctrl = self.engine.ctrl_bytes()
         self._allocators = [HeapAllocator(ctrl, heap_bytes) for _ in self.local_ranks]
         self.max_ctas = max(1, min(self.engine.max_ctas(config.max_tokens_per_rank), self.engine.sm_count()))
-        self.items_per_cta = native.THREADS // 32   # (token, row segment) work items a CTA should find
+        self.items_per_cta = 4            # rows a CTA of the dispatch kernel should find (one per mover warp)
         self.launches = 0
         self._slots: List[Slot] = []
 
@@ -184,30 +184,40 @@ class TransportCore:
 
     # ---- launches --------------------------------------------------------------
     def pick_ctas(self, tokens: int, budget: Optional[int] = None) -> int:
-        """CTAs per rank: enough warps for every (token, 2 KiB row segment), within the budget."""
+        """CTAs per rank of a dispatch: one mover warp per row piece until the budget is reached."""
         budget = self.max_ctas if budget is None else max(1, min(budget, self.max_ctas))
-        segments = max(1, self.hidden * 2 // 2048)
-        wanted = -(-max(tokens, 1) * segments // max(1, self.items_per_cta))
+        pieces = -(-self.hidden * 2 // 14336)
+        wanted = -(-max(tokens, 1) * pieces // max(1, self.items_per_cta))
+        return max(1, min(budget, wanted))
+
+    def pick_combine_ctas(self, tokens: int, capacity: int, budget: Optional[int] = None) -> int:
+        """CTAs per rank of a combine: a CTA pushes about six received rows per round trip and
+        reduces four (token, row segment) items at a time."""
+        budget = self.max_ctas if budget is None else max(1, min(budget, self.max_ctas))
+        wanted = max(-(-max(capacity, 1) // 6), max(tokens, 1))
         return max(1, min(budget, wanted))
 
     def dispatch(self, slot: Slot, xs, ids, weights, capacities, *, identity=0, ctas=None, stream=None,
-                 profile=None):
+                 profile=None, samples=None):
         stream = stream or torch.cuda.current_stream(self.device)
         tokens = max(x.shape[0] for x in xs)
         ctas = self.pick_ctas(tokens) if ctas is None else ctas
         n = len(self.local_ranks)
         self.engine.dispatch(list(xs), list(ids), list(weights), slot.offsets, list(capacities),
                              [slot.capacity] * n, [slot.tokens] * n, identity, ctas,
-                             bool(self.config.zero_padding), stream.cuda_stream, profile)
+                             bool(self.config.zero_padding), stream.cuda_stream, profile, samples)
         self.launches += 1
 
-    def combine(self, slot: Slot, partials, outs, *, identity=0, ctas=None, stream=None, profile=None):
+    def combine(self, slot: Slot, partials, outs, *, identity=0, ctas=None, stream=None, profile=None,
+                mailbox=None, samples=None):
+        """``mailbox``: None = the context's default protocol, True/False = this operation's."""
         stream = stream or torch.cuda.current_stream(self.device)
         tokens = max(out.shape[0] for out in outs)
-        ctas = self.pick_ctas(tokens) if ctas is None else ctas
+        ctas = self.pick_combine_ctas(tokens, slot.capacity) if ctas is None else ctas
         n = len(self.local_ranks)
         self.engine.combine(list(partials), list(outs), slot.offsets, [slot.capacity] * n, [slot.tokens] * n,
-                            identity, ctas, stream.cuda_stream, profile)
+                            identity, ctas, stream.cuda_stream, profile, -1 if mailbox is None else int(bool(mailbox)),
+                            samples)
         self.launches += 1
 
     def scale_rows(self, hidden, local_ids, weights, valid_count, factors, partial, stream=None):

@@ -67,14 +67,15 @@ class EmulatedGroup:
         return [EmulatedBatch(v.hidden[:c], v.local_ids[:c], v.weights[:c], v.inverse[:c], v.count, v.partial[:c])
                 for v, c in zip(slot.views, capacities)]
 
-    def combine(self, slot: Slot, partials, token_counts, *, outs=None, ctas=None, identity=0, stream=None):
+    def combine(self, slot: Slot, partials, token_counts, *, outs=None, ctas=None, identity=0, stream=None,
+                mailbox=None):
         with torch.cuda.device(self.device):
             if outs is None:
                 outs = [torch.empty((n, self.config.hidden_size), dtype=torch.bfloat16, device=self.device)
                         for n in token_counts]
             if ctas is None:
-                ctas = self.core.pick_ctas(max(token_counts))
-            self.core.combine(slot, partials, outs, identity=identity, ctas=ctas, stream=stream)
+                ctas = self.core.pick_combine_ctas(max(token_counts), slot.capacity)
+            self.core.combine(slot, partials, outs, identity=identity, ctas=ctas, stream=stream, mailbox=mailbox)
         return outs
 
     def scale_rows(self, batch: EmulatedBatch, factors=None, out=None, stream=None):

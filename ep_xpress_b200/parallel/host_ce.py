@@ -319,6 +319,9 @@ class HostCEContext(Context):
         received, metrics = self._exchange("combine", operation, partial_cpu, send_masks, recv_plan)
         tokens_here = plan.token_counts[self.rank]
         single = cfg.single_rounding
+        if partial.is_cuda:
+            return CompletedTicket(self._reduce_on_gpu(partial, plan, received, token_order, tokens_here, single),
+                                   metrics)
         remote = torch.zeros((tokens_here, cfg.hidden_size), dtype=torch.float32)
         local = torch.zeros((tokens_here, cfg.hidden_size), dtype=torch.float32)
         for dest in range(self.world_size):                    # ascending rank order
@@ -339,6 +342,34 @@ class HostCEContext(Context):
         else:
             out = (remote.to(torch.bfloat16).to(torch.float32) + local).to(torch.bfloat16)
         return CompletedTicket(out.to(self.device), metrics)
+
+    def _reduce_on_gpu(self, partial, plan, received, token_order, tokens_here, single):
+        """Combine arithmetic on the GPU with the native helper kernels (the reference's host_ce
+        does the same with its add_partial / finish_combine kernels, ep_xpress/context.py:375-408):
+        every peer's rows are uploaded and accumulated into an FP32 plane in ascending rank
+        order, then rounded, joined with the local rows and rounded again."""
+        native, cfg, device = self._native, self.config, partial.device
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream(device).cuda_stream
+            remote = torch.zeros((tokens_here, cfg.hidden_size), dtype=torch.float32, device=device)
+            local = torch.zeros((tokens_here, cfg.hidden_size), dtype=torch.float32, device=device)
+            status = torch.zeros(1, dtype=torch.int32, device=device)
+            out = torch.empty((tokens_here, cfg.hidden_size), dtype=torch.bfloat16, device=device)
+            for dest in range(self.world_size):                # ascending rank order
+                if dest == self.rank:
+                    rows = plan.dest_rows[self.rank][:, dest]
+                    sel = (rows >= 0).nonzero().flatten()
+                    if not sel.numel():
+                        continue
+                    values = partial.detach()[rows[sel].to(device)].contiguous()
+                    native.add_partial(remote if single else local, values, sel.to(device), status, stream)
+                elif dest in received:
+                    got = torch.cat(received[dest]).contiguous().view(torch.bfloat16).reshape(-1, cfg.hidden_size)
+                    native.add_partial(remote, got.to(device), token_order[dest].to(device), status, stream)
+            native.finish_combine(remote, local, out, single, stream)
+            if int(status.item()):
+                raise RuntimeError("host_ce: a combine row index lies outside this rank's tokens")
+        return out
 
     # ---------------------------------------------------------------- teardown
     def _release(self):

@@ -49,6 +49,7 @@ class _DeviceRoute:
     workspace: object
     capacity: int
     fused_combine: bool
+    combine_ctas: int = 0
 
 
 class Workspace:
@@ -102,6 +103,11 @@ class NVLinkContext(Context):
         if not isinstance(config, Config) or not config.device_transport:
             raise TypeError("config must select a device transport")
         self.config = config
+        inert = config.inert_fields()
+        if inert:
+            import warnings
+            warnings.warn("these Config fields have no effect on the NVLink transport: " + ", ".join(inert),
+                          stacklevel=3)
         self._comm = nccl_comm
         self.rank, self.world_size = nccl_comm.rank, nccl_comm.world_size
         if not 1 <= self.world_size <= 63:
@@ -342,7 +348,10 @@ class NVLinkContext(Context):
                 raise RuntimeError("CUDA Graph capture requires a warmed, retained workspace")
             slot = self._core.create_slot(self._max_receive_capacity, self.config.max_tokens_per_rank,
                                           self._work_stream)
-            torch.cuda.current_stream(self.device).wait_stream(self._work_stream)
+            # The reset of the fresh slot runs on the context's stream: whichever stream executes
+            # the slot's first dispatch has to wait for it (see `_dispatch`).
+            slot.reset_done = torch.cuda.Event()
+            slot.reset_done.record(self._work_stream)
             self._pool.append(slot)
             return slot
         raise RuntimeError(f"all {self.config.slots} operation slots hold handles that were not combined yet; "
@@ -409,6 +418,10 @@ class NVLinkContext(Context):
                     execution.wait_stream(producer)
                 if workspace is not None:
                     workspace._acquire(execution, capturing=capturing)
+                reset_done = getattr(slot, "reset_done", None)
+                if reset_done is not None:
+                    execution.wait_event(reset_done)
+                    slot.reset_done = None
                 ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
                 weights = topk_weights if topk_weights.is_contiguous() else topk_weights.contiguous()
                 if ids.dtype not in (torch.int32, torch.int64):
@@ -417,16 +430,15 @@ class NVLinkContext(Context):
                     x = x.clone()
                 budget = max(1, self._core.max_ctas * channels // self.effective_channels)
                 ctas = self._core.pick_ctas(x.shape[0], budget)
+                combine_ctas = self._core.pick_combine_ctas(x.shape[0], capacity, budget)
                 profile = None if self._profile is None else self._profile.slice_for(
                     "dispatch", self._counter, tag, x.shape[0], capacity, ctas)
-                if profile is None and capturing:
-                    profile = self._decode_slice("dispatch", ctas)
                 with self._on(execution, stream, same_stream):
                     if not same_stream:
                         for tensor in (x, ids, weights):
                             tensor.record_stream(execution)
                     self._core.dispatch(slot, [x], [ids], [weights], [capacity], identity=identity, ctas=ctas,
-                                        stream=execution, profile=profile)
+                                        stream=execution, profile=profile, samples=self._sample_ring("dispatch"))
             except BaseException as error:
                 self._abort(error)
                 raise
@@ -437,13 +449,13 @@ class NVLinkContext(Context):
                 # A workspace has exactly this shape: its views were cut once, at creation
                 # (slicing six tensors costs more host time than the rest of the call).
                 route = _DeviceRoute(slot, workspace.inverse, views.count, channels, ctas, workspace.expected_ranks,
-                                     workspace.dest_rows, workspace, capacity, fused_combine)
+                                     workspace.dest_rows, workspace, capacity, fused_combine, combine_ctas)
                 handle = RouteHandle(self._id, self._counter, route, x.shape[0], capacity, tag)
                 batch = DispatchBatch(workspace.hidden, workspace.local_ids, workspace.weights, handle, views.count)
             else:
                 route = _DeviceRoute(slot, views.inverse[:capacity], views.count, channels, ctas,
                                      views.mask[:x.shape[0]], views.dest_rows[:x.shape[0]], workspace, capacity,
-                                     fused_combine)
+                                     fused_combine, combine_ctas)
                 handle = RouteHandle(self._id, self._counter, route, x.shape[0], capacity, tag)
                 batch = DispatchBatch(views.hidden[:capacity], views.local_ids[:capacity], views.weights[:capacity],
                                       handle, views.count)
@@ -509,9 +521,12 @@ class NVLinkContext(Context):
                 raise ValueError("combine accepts already-weighted rank partials only")
             if not isinstance(partial, torch.Tensor) or partial.requires_grad:
                 raise ValueError("partial must be an inference tensor")
-            rows_ok = partial.ndim == 2 and partial.shape[0] <= handle.received_count
+            # Every received row owes its token's owner a result row, so the partial tensor covers
+            # the dispatch's whole receive capacity (shape rule of ep_xpress/context.py:380).
+            rows_ok = partial.ndim == 2 and partial.shape[0] == handle.received_count
             if not rows_ok or partial.shape[1] != self.config.hidden_size or partial.dtype != torch.bfloat16:
-                raise ValueError("partial must be BF16 [rows <= capacity, hidden]")
+                raise ValueError(f"partial must be BF16 [{handle.received_count}, {self.config.hidden_size}]: one "
+                                 "row per row of the dispatch's receive capacity")
             if not same_stream and self._pending >= self.config.max_pending_operations:
                 raise RuntimeError("too many pending operations; wait on earlier tickets first")
             route = handle._plan
@@ -535,11 +550,14 @@ class NVLinkContext(Context):
                         output = workspace.output
                     profile = None if self._profile is None else self._profile.slice_for(
                         "combine", handle.operation, tag, handle.local_token_count, handle.received_count,
-                        route.ctas)
-                    if profile is None and capturing:
-                        profile = self._decode_slice("combine", route.ctas)
-                    self._core.combine(route.slot, [source], [output], identity=identity, ctas=route.ctas,
-                                       stream=execution, profile=profile)
+                        route.combine_ctas)
+                    # Receive-and-reduce in one pass (the mailbox protocol) is the default wherever it
+                    # applies; `fused_combine=True` at dispatch asks for it even when the context's
+                    # default is the sequential protocol (Config.combine_streaming="off").
+                    self._core.combine(route.slot, [source], [output], identity=identity, ctas=route.combine_ctas,
+                                       stream=execution, profile=profile,
+                                       mailbox=True if route.fused_combine else None,
+                                       samples=self._sample_ring("combine"))
             except BaseException as error:
                 self._abort(error)
                 raise
@@ -551,7 +569,7 @@ class NVLinkContext(Context):
                     workspace._combined(execution, capturing=capturing)
                 return output
             return self._finish(output, workspace, tensors=() if workspace is not None else (output,),
-                                metrics={"ctas": route.ctas, "active_channels": route.active_channels})
+                                metrics={"ctas": route.combine_ctas, "active_channels": route.active_channels})
 
     # ------------------------------------------------------------------ profiling
     def start_combine_profile(self, max_operations=1024):
@@ -590,56 +608,81 @@ class NVLinkContext(Context):
         return report
 
     # ---- decode profile: fixed storage that captured operations keep writing into -----------
-    def prepare_decode_profile(self, max_samples_per_channel=1, *, stage="combine"):
-        """Install fixed counters for CAPTURED operations of ``stage`` ("dispatch" or "combine").
+    def prepare_decode_profile(self, max_samples_per_channel=1024, *, stage="combine"):
+        """Install a bounded sample ring that every operation of ``stage`` records into.
 
-        Call before graph capture (same rule as the reference, ep_xpress/host_sm.py:515-545).
-        Operations captured afterwards stamp their per-CTA phase times into this storage at
-        every replay; it always holds the most recent replay (one sample per CTA, so
-        ``max_samples_per_channel`` above 1 is accepted but not needed).
+        ``stage`` is "dispatch", "combine" or "layer" (both). Call it before the graphs that
+        should be measured are captured (same rule as the reference,
+        ep_xpress/host_sm.py:515-545): a captured kernel carries the ring's address. Every
+        operation launched afterwards - eager or replayed - records one sample while the profile
+        is started: the earliest start and the latest end over its CTAs on the GPU's global
+        timer. The ring holds ``max_samples_per_channel`` operations per stage; later ones are
+        counted as ``dropped_samples``. Nothing is recorded, and the kernels do not touch the
+        ring's rows, between ``stop`` and the next ``start``.
         """
         with self._lock, torch.cuda.device(self.device):
             self._check_usable()
-            if stage not in ("dispatch", "combine"):
-                raise ValueError("stage must be dispatch or combine")
+            if stage not in ("dispatch", "combine", "layer"):
+                raise ValueError("stage must be dispatch, combine or layer")
+            if isinstance(max_samples_per_channel, bool) or not isinstance(max_samples_per_channel, int) \
+                    or not 1 <= max_samples_per_channel <= 1 << 20:
+                raise ValueError("max_samples_per_channel must be an integer in [1, 2^20]")
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("prepare_decode_profile must be called before graph capture")
-            stamps = self._core.native.PROFILE_STAMPS
-            self._decode_profile = {"stage": stage, "ctas": 0, "enabled": True,
-                                    "buffer": torch.zeros((self._core.max_ctas, stamps), dtype=torch.int64,
-                                                          device=self.device)}
+            words = self._core.native.SAMPLE_WORDS
+            stages = ("dispatch", "combine") if stage == "layer" else (stage,)
+            self._decode_profile = {
+                "stage": stage, "capacity": max_samples_per_channel, "running": False,
+                "rings": {name: torch.zeros((1, 1 + max_samples_per_channel, words), dtype=torch.int64,
+                                            device=self.device) for name in stages}}
 
-    def _decode_slice(self, stage, ctas):
+    def _sample_ring(self, stage):
         state = getattr(self, "_decode_profile", None)
-        if state is None or state["stage"] != stage:
-            return None
-        state["ctas"] = ctas
-        return state["buffer"]
+        return None if state is None else state["rings"].get(stage)
 
     def start_decode_profile(self):
-        if getattr(self, "_decode_profile", None) is None:
-            raise RuntimeError("prepare_decode_profile is required before the first capture")
-        with torch.cuda.device(self.device):
-            self._decode_profile["buffer"].zero_()
-
-    def stop_decode_profile(self):
-        """Phase stamps (ns, relative to the first CTA's start) of the most recent replay."""
-        from ..utils.profile import COMBINE_PHASES, DISPATCH_PHASES
+        """Begin recording at a quiescent boundary: synchronises the device, clears the rings and
+        maps the next operation of each stage to sample 0."""
         state = getattr(self, "_decode_profile", None)
         if state is None:
             raise RuntimeError("prepare_decode_profile is required before the first capture")
-        with torch.cuda.device(self.device):
+        with self._lock, torch.cuda.device(self.device):
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("start_decode_profile must be called outside capture")
             torch.cuda.synchronize(self.device)
-            stamps = state["buffer"][:max(state["ctas"], 1)].cpu()
-        names = DISPATCH_PHASES if state["stage"] == "dispatch" else COMBINE_PHASES
-        started = stamps[:, 0][stamps[:, 0] > 0]
-        begin = int(started.min()) if started.numel() else 0
-        phases = {}
-        for column, name in enumerate(names):
-            reached = stamps[:, column][stamps[:, column] > 0]
-            if reached.numel():
-                phases[name] = {"first_ns": int(reached.min()) - begin, "last_ns": int(reached.max()) - begin}
-        return {"schema": 1, "stage": state["stage"], "ctas": state["ctas"], "phases": phases}
+            _, _, dispatch_epoch, combine_epoch = self._core.status(0)
+            for name, ring in state["rings"].items():
+                ring.zero_()
+                ring[0, 1:, 0] = torch.iinfo(torch.int64).max          # earliest start: preset to "never"
+                ring[0, 0, 1] = (dispatch_epoch if name == "dispatch" else combine_epoch) + 1
+                ring[0, 0, 2] = 1
+            torch.cuda.synchronize(self.device)
+            state["running"] = True
+
+    def stop_decode_profile(self):
+        """Stop recording (synchronises the device) and return the samples of every stage:
+        ``{"stages": {name: {"samples": n, "dropped_samples": d, "begin_ns": [...], "elapsed_ns": [...]}}}``,
+        one entry per operation since ``start`` in submission order."""
+        state = getattr(self, "_decode_profile", None)
+        if state is None:
+            raise RuntimeError("prepare_decode_profile is required before the first capture")
+        if not state["running"]:
+            raise RuntimeError("start_decode_profile is required before stop_decode_profile")
+        with self._lock, torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            report = {"schema": 2, "stage": state["stage"], "max_samples_per_channel": state["capacity"],
+                      "stages": {}}
+            for name, ring in state["rings"].items():
+                ring[0, 0, 2] = 0
+                host = ring[0].cpu()
+                rows = host[1:]
+                used = int((rows[:, 2] > 0).sum())
+                begin, end = rows[:used, 0], rows[:used, 1]
+                report["stages"][name] = {"samples": used, "dropped_samples": int(host[0, 0]),
+                                          "begin_ns": begin.tolist(), "elapsed_ns": (end - begin).tolist(),
+                                          "ctas": rows[:used, 2].tolist()}
+            state["running"] = False
+        return report
 
     # ------------------------------------------------------------------ teardown
     def _release_resources(self, *, keep_own_heap=False):

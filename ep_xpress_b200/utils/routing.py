@@ -202,6 +202,45 @@ def combine_oracle(partials_by_rank, plan: RoutePlan, hidden_size: int, rounding
     return outputs
 
 
+def identity_layer_oracle(x, ids, weights, expert_to_rank, rank: int, world_size: int,
+                          rounding: str = "two_step"):
+    """Output of dispatch -> identity-times-routing-weight expert -> combine for ONE rank's tokens,
+    from that rank's own inputs alone (plain PyTorch FP32 on the tensors' device).
+
+    The rows a token sends out come back scaled by the weights of the experts that live on the
+    destination rank, so nothing of the other ranks' batches enters a rank's result: every
+    destination's partial row is ``bf16(x * scale_r)`` with ``scale_r`` accumulated over the slots
+    owned by rank ``r`` in slot order, and the combine adds them in rank order with the
+    library's rounding points (see :func:`combine_oracle`). Benchmarks use it to check every step's
+    output bit for bit without a group-wide route plan.
+    """
+    if rounding not in ("two_step", "single"):
+        raise ValueError("rounding must be two_step or single")
+    device = x.device
+    owner = torch.as_tensor(_as_owner_list(expert_to_rank, world_size), dtype=torch.int64, device=device)
+    ids = ids.to(torch.int64)
+    active = ids >= 0
+    dest = torch.where(active, owner[ids.clamp(min=0)], torch.full_like(ids, -1))
+    w = torch.where(active, weights.to(torch.float32), torch.zeros_like(weights, dtype=torch.float32))
+    xf = x.to(torch.float32)
+    remote = torch.zeros_like(xf)
+    local = torch.zeros_like(xf)
+    for r in range(world_size):
+        here = dest == r
+        scale = torch.zeros(x.shape[0], dtype=torch.float32, device=device)
+        for k in range(ids.shape[1]):
+            scale = torch.where(here[:, k], scale + w[:, k], scale)
+        partial = (xf * scale[:, None]).to(torch.bfloat16).to(torch.float32)
+        partial = torch.where(here.any(dim=1)[:, None], partial, torch.zeros_like(partial))
+        if r == rank and rounding == "two_step":
+            local = partial
+        else:
+            remote = remote + partial
+    if rounding == "two_step":
+        return (remote.to(torch.bfloat16).to(torch.float32) + local).to(torch.bfloat16)
+    return remote.to(torch.bfloat16)
+
+
 def direct_weighted_sum(x_by_rank, ids_by_rank, weights_by_rank, factors_by_expert=None):
     """What a dense MoE with identity-times-factor experts computes, in FP64."""
     outputs = []

@@ -113,65 +113,219 @@ def run_reverse_handles(ep, rank, world, args):
 
 
 def run_graph(ep, rank, world, args):
-    """Decode workspace captured once, replayed with changing routes, eager prefill interleaved."""
+    """Several decode buckets captured once each, replayed in turn with routes that change at every
+    replay; one bucket leaves a rank without tokens; eager operations run between replays; a
+    bounded sample ring records every operation (scenario of the reference's
+    tests/test_host_sm_graph_cuda.py:87-122,180-188)."""
     hidden, topk, tokens = args.hidden, 4, args.tokens
     emap = workloads.contiguous_expert_map(world * 4, world)
     factors = [torch.ones(4) for _ in range(world)]
     ep.enable_cuda_graph()
-    workspace = ep.create_workspace(world * tokens, tokens)
     stream = torch.cuda.Stream()
-    static = [torch.zeros((tokens, hidden), dtype=torch.bfloat16, device="cuda"),
-              torch.zeros((tokens, topk), dtype=torch.int64, device="cuda"),
-              torch.zeros((tokens, topk), dtype=torch.float32, device="cuda")]
+    # Bucket b gives rank r `sizes[b][r]` tokens; the last bucket empties the highest rank.
+    sizes = [[tokens] * world, [max(tokens // 2 - r, 1) for r in range(world)], [1] * world,
+             [tokens - 1 if r + 1 < world else 0 for r in range(world)]]
+    fused = bool(ep.config.decode_max_tokens)
 
-    def layer():
-        batch = ep.dispatch_on_stream(*static, stream=stream, workspace=workspace)
+    def inputs(bucket, iteration):
+        xs, ids, ws = [], [], []
+        case = "mixed" if iteration % 3 else "padding"
+        for r in range(world):
+            n = sizes[bucket][r]
+            i, w, _ = workloads.replay_case(case, rank=r, world_size=world, tokens=n, topk=topk, iteration=iteration)
+            xs.append(workloads.marker_payload(n, hidden, rank=r, iteration=iteration))
+            ids.append(i[:n])
+            ws.append(w[:n])
+        return xs, ids, ws
+
+    buckets = []
+    for b, per_rank in enumerate(sizes):
+        n = per_rank[rank]
+        workspace = ep.create_workspace(sum(per_rank), n, fused_combine=fused)
+        static = [torch.zeros((n, hidden), dtype=torch.bfloat16, device="cuda"),
+                  torch.zeros((n, topk), dtype=torch.int64, device="cuda"),
+                  torch.zeros((n, topk), dtype=torch.float32, device="cuda")]
+        buckets.append({"workspace": workspace, "static": static})
+
+    def layer(bucket):
+        batch = ep.dispatch_on_stream(*bucket["static"], stream=stream, workspace=bucket["workspace"],
+                                      fused_combine=fused)
         partial = scale_rows(ep, batch, stream=stream)
         return ep.combine_on_stream(partial, batch.handle, stream=stream), batch
 
-    def load(iteration):
-        xs, ids, ws = group_inputs("mixed" if iteration % 3 else "padding", world, tokens, hidden, topk, iteration)
-        for dst, src in zip(static, (xs[rank], ids[rank], ws[rank])):
+    def load(b, iteration):
+        xs, ids, ws = inputs(b, iteration)
+        for dst, src in zip(buckets[b]["static"], (xs[rank], ids[rank], ws[rank])):
             dst.copy_(src)
         return expected(xs, ids, ws, emap, world, topk, hidden, factors)
 
     with torch.cuda.stream(stream):
-        load(0)
-        layer()                                   # warm the workspace eagerly
+        for b in range(len(buckets)):
+            load(b, 0)
+            layer(buckets[b])                     # warm every workspace eagerly
     stream.synchronize()
     try:
         with torch.cuda.stream(stream):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                layer()
+                layer(buckets[0])
     except RuntimeError as error:
         assert "prepare_graph_capture" in str(error)
     else:
         raise AssertionError("capture without prepare_graph_capture must be rejected")
     torch.cuda.synchronize()
+    ep.prepare_decode_profile(max_samples_per_channel=64, stage="layer")
     ep.prepare_graph_capture()
-    ep.prepare_decode_profile(stage="combine")      # fixed counters the captured combine keeps writing
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=stream):
-        out, batch = layer()
+    for bucket in buckets:
+        bucket["graph"] = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(bucket["graph"], stream=stream):
+            bucket["out"], bucket["batch"] = layer(bucket)
+    ep.start_decode_profile()
+    operations = 0
     for iteration in range(1, args.replays + 1):
+        b = (iteration * 7 + iteration // 5) % len(buckets)          # bucket switches in an irregular order
+        bucket = buckets[b]
         with torch.cuda.stream(stream):
-            plan, rows, want = load(iteration)
+            plan, rows, want = load(b, iteration)
             ep.prepare_graph_replay(stream)
-            graph.replay()
-        stream.synchronize()
-        check_batch(batch, plan, rows, rank)
-        assert torch.equal(bits(out), bits(want[rank])), f"replay {iteration} differs"
-        if iteration % 4 == 0:                    # an eager operation between replays
+            bucket["graph"].replay()
+        operations += 1
+        if iteration % args.check_every == 0 or iteration == args.replays:
+            stream.synchronize()
+            check_batch(bucket["batch"], plan, rows, rank)
+            assert torch.equal(bits(bucket["out"]), bits(want[rank])), f"replay {iteration} (bucket {b}) differs"
+        if iteration % 16 == 0:                   # an eager operation between replays
             xs, ids, ws = group_inputs("uniform", world, tokens, hidden, topk, 100 + iteration)
             _, _, eager_want = expected(xs, ids, ws, emap, world, topk, hidden, factors)
             eager = ep.dispatch_async(xs[rank].cuda(), ids[rank].cuda(), ws[rank].cuda()).wait()
             result = ep.combine_async(scale_rows(ep, eager), eager.handle).wait()
             assert torch.equal(bits(result), bits(eager_want[rank]))
+            operations += 1
     decode = ep.stop_decode_profile()
-    assert decode["stage"] == "combine" and decode["phases"]["start"]["first_ns"] == 0
-    assert decode["phases"]["reduced"]["last_ns"] > 0
+    assert decode["stage"] == "layer" and set(decode["stages"]) == {"dispatch", "combine"}
+    for name, stage in decode["stages"].items():
+        # The ring is bounded: 64 samples are kept, every later operation is counted as dropped.
+        assert stage["samples"] == min(operations, 64), (name, stage["samples"], operations)
+        assert stage["dropped_samples"] == max(operations - 64, 0), (name, stage["dropped_samples"], operations)
+        assert all(0 < ns < 5_000_000_000 for ns in stage["elapsed_ns"])
+        assert stage["begin_ns"] == sorted(stage["begin_ns"])
     ep.check()
+
+
+def _layer_once(ep, x, ids, ws, *, stream=None, direct=True, factors=None, out=None):
+    if direct:
+        batch = ep.dispatch_on_stream(x, ids, ws, stream=stream)
+        partial = scale_rows(ep, batch, factors, stream=stream, out=out)
+        return ep.combine_on_stream(partial, batch.handle, stream=stream), batch
+    batch = ep.dispatch_async(x, ids, ws, stream=stream).wait(stream)
+    partial = scale_rows(ep, batch, factors, stream=stream, out=out)
+    return ep.combine_async(partial, batch.handle, stream=stream).wait(stream), batch
+
+
+def run_streams(ep, rank, world, args):
+    """Ticket API and direct-stream API interleaved on different streams, with consumers of the
+    results on yet another stream (scenario of the reference's tests/test_host_sm_stream_cuda.py:69-75)."""
+    hidden, topk, tokens = args.hidden, 4, args.tokens
+    emap = workloads.contiguous_expert_map(world * 4, world)
+    factors = [torch.ones(4) for _ in range(world)]
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    consumer = torch.cuda.Stream()
+    checks = []
+    for iteration in range(12):
+        xs, ids, ws = group_inputs("uniform", world, tokens, hidden, topk, iteration)
+        _, _, want = expected(xs, ids, ws, emap, world, topk, hidden, factors)
+        stream = streams[iteration % 3]
+        with torch.cuda.stream(stream):
+            x, i, w = xs[rank].cuda(non_blocking=True), ids[rank].cuda(non_blocking=True), ws[rank].cuda(non_blocking=True)
+            out, _ = _layer_once(ep, x, i, w, stream=stream, direct=iteration % 2 == 0)
+        consumer.wait_stream(stream)
+        with torch.cuda.stream(consumer):                 # a consumer on another stream reads the result
+            checks.append((out.clone(), want[rank]))
+            out.record_stream(consumer)
+    torch.cuda.synchronize()
+    for got, want in checks:
+        assert torch.equal(bits(got), bits(want))
+    ep.check()
+
+
+def run_stagger(ep, rank, world, args):
+    """Ranks that arrive late and readers that lag: before each of 32 back-to-back layers one
+    rank (a different one every time) stalls its stream, so its peers' rows wait in its planes and
+    its own rows arrive after everybody else's (scenario of the reference's
+    tests/test_host_sm_mailbox_reclaim_cuda.py:100-107 and test_host_sm_ready_prefetch_cuda.py:117-143)."""
+    hidden, topk, tokens = args.hidden, 4, args.tokens
+    emap = workloads.contiguous_expert_map(world * 4, world)
+    factors = [torch.ones(4) for _ in range(world)]
+    workspace = ep.create_workspace(world * tokens, tokens)
+    stream = torch.cuda.current_stream()
+    results = []
+    for iteration in range(32):
+        xs, ids, ws = group_inputs("uniform" if iteration % 2 else "mixed", world, tokens, hidden, topk, iteration)
+        _, _, want = expected(xs, ids, ws, emap, world, topk, hidden, factors)
+        x, i, w = xs[rank].cuda(), ids[rank].cuda(), ws[rank].cuda()
+        if iteration % world == rank:
+            torch.cuda._sleep(3_000_000)                  # about 1.5 ms of a 2 GHz clock
+        batch = ep.dispatch_on_stream(x, i, w, stream=stream, workspace=workspace)
+        partial = scale_rows(ep, batch, stream=stream)
+        if (iteration + 1) % world == rank:
+            torch.cuda._sleep(3_000_000)                  # this rank pushes late, its reducers wait
+        out = ep.combine_on_stream(partial, batch.handle, stream=stream)
+        results.append((out.clone(), want[rank]))
+    torch.cuda.synchronize()
+    for index, (got, want) in enumerate(results):
+        assert torch.equal(bits(got), bits(want)), f"layer {index} differs"
+    ep.check()
+
+
+def run_headline(ep, rank, world, args):
+    """The benchmarked shape (hidden 7168, 4096 tokens per rank, 256 experts, top-8), checked bit
+    for bit on this rank: received rows against the senders' inputs, output against the
+    rank-order FP32 formula."""
+    hidden, topk, tokens, experts = args.hidden, 8, args.tokens, 256
+    emap = workloads.contiguous_expert_map(experts, world)
+    owner = torch.tensor(emap)
+    for seed in range(2):
+        routes = [workloads.uniform_routing(tokens, experts, topk, seed=seed, rank=r, weights="sigmoid")
+                  for r in range(world)]
+        xs = [workloads.gaussian_payload(tokens, hidden, seed=seed, rank=r) for r in range(world)]
+        x, ids, w = xs[rank].cuda(), routes[rank][0].cuda(), routes[rank][1].cuda()
+        batch = ep.dispatch_on_stream(x, ids, w)
+        partial = scale_rows(ep, batch)
+        out = ep.combine_on_stream(partial, batch.handle)
+        torch.cuda.synchronize()
+        valid = int(batch.valid_count.item())
+        want_rows = sum(int((owner[i] == rank).any(dim=1).sum()) for i, _ in routes)
+        assert valid == want_rows, (valid, want_rows)
+        inverse = batch.handle.inverse_map[:valid].cpu()
+        everything = torch.stack(xs)                                   # [world, tokens, hidden]
+        assert torch.equal(bits(batch.hidden[:valid]), bits(everything[inverse[:, 0], inverse[:, 1]]))
+        assert (inverse[1:, 0] * tokens + inverse[1:, 1] > inverse[:-1, 0] * tokens + inverse[:-1, 1]).all()
+        want = routing.identity_layer_oracle(xs[rank], routes[rank][0], routes[rank][1], emap, rank, world)
+        assert torch.equal(bits(out), bits(want)), f"seed {seed}: combine output differs"
+    ep.check()
+
+
+def run_host_ce(comm, rank, world, args):
+    """The host-staged oracle transport on CUDA tensors over the borrowed NCCL communicator: its
+    combine runs on the native add_partial / finish_combine kernels."""
+    hidden, topk, tokens, experts = 128, 4, 29, world * 4
+    emap = workloads.round_robin_expert_map(experts, world)
+    for rounding in ("two_step", "single"):
+        cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=32, transport="host_ce",
+                     chunk_bytes=hidden * 2 * 8, timeout_seconds=30.0, combine_rounding=rounding)
+        with Context(nccl_comm=comm, expert_to_rank=emap, config=cfg) as ep:
+            xs, ids, ws = group_inputs("uniform", world, tokens, hidden, topk, 1)
+            ids = [workloads.uniform_routing(i.shape[0], experts, topk, seed=2, rank=r)[0] for r, i in enumerate(ids)]
+            plan = routing.plan_routes(ids, ws, emap, world, topk)
+            rows = routing.dispatch_oracle(xs, plan)
+            batch = ep.dispatch_async(xs[rank].cuda(), ids[rank].cuda(), ws[rank].cuda(), tag="oracle").wait()
+            assert batch.valid_count == plan.received[rank].rows and batch.hidden.is_cuda
+            assert torch.equal(bits(batch.hidden), bits(rows[rank]))
+            partials = [routing.scale_expert_oracle(rows[r], plan.received[r].local_ids, plan.received[r].weights)
+                        for r in range(world)]
+            out = ep.combine_async(partials[rank].cuda(), batch.handle, tag="oracle").wait()
+            want = routing.combine_oracle(partials, plan, hidden, rounding)
+            assert out.is_cuda and torch.equal(bits(out), bits(want[rank])), rounding
 
 
 def run_errors(ep, rank, world, args):
@@ -234,21 +388,41 @@ def run_profile(ep, rank, world, args):
     ep.check()
 
 
-CASES = {"profile": run_profile, "replay": run_replay, "reverse": run_reverse_handles, "graph": run_graph, "errors": run_errors}
+CASES = {"streams": run_streams, "stagger": run_stagger, "headline": run_headline, "profile": run_profile, "replay": run_replay, "reverse": run_reverse_handles, "graph": run_graph, "errors": run_errors}
 
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", choices=sorted(CASES), required=True)
+    parser.add_argument("--case", choices=sorted(CASES) + ["hostce"], required=True)
     parser.add_argument("--hidden", type=int, default=256)
     parser.add_argument("--tokens", type=int, default=24)
-    parser.add_argument("--replays", type=int, default=12)
+    parser.add_argument("--replays", type=int, default=1000)
+    parser.add_argument("--check-every", type=int, default=1)
+    parser.add_argument("--decode-max-tokens", type=int, default=0)
     args = parser.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     comm = get_nccl_comm_handle(dist.group.WORLD)
+    if args.case == "hostce":
+        run_host_ce(comm, rank, world, args)
+        dist.destroy_process_group()
+        print(f"rank {rank}: hostce ok", flush=True)
+        return
+    if args.case == "headline":
+        cfg = Config(hidden_size=args.hidden, topk=8, max_tokens_per_rank=args.tokens, timeout_seconds=20.0)
+        ep = Context(nccl_comm=comm, expert_to_rank=workloads.contiguous_expert_map(256, world), config=cfg)
+        try:
+            run_headline(ep, rank, world, args)
+        finally:
+            ep.close()
+        dist.destroy_process_group()
+        print(f"rank {rank}: headline ok", flush=True)
+        return
     cfg = Config(hidden_size=args.hidden, topk=4, max_tokens_per_rank=args.tokens,
+                 decode_max_tokens=args.decode_max_tokens, slots=2,
+                 workspace_pool_bytes=(8 << 20) + 6 * Config(hidden_size=args.hidden, topk=4,
+                                                             max_tokens_per_rank=args.tokens).nvlink_slot_bytes(world),
                  timeout_seconds=2.0 if args.case == "errors" else 10.0)
     emap = workloads.contiguous_expert_map(world * 4, world)
     ep = Context(nccl_comm=comm, expert_to_rank=emap, config=cfg)

@@ -102,3 +102,16 @@ def test_mapped_arena_is_empty_but_validated():
         cfg.mapped_arena_bytes(0, dispatch_banks=2)
     with pytest.raises(ValueError, match="queue_peers"):
         cfg.mapped_arena_bytes(2, queue_peers=2)
+
+
+def test_inert_fields_are_named_and_slot_breakdown_adds_up():
+    cfg = Config(hidden_size=512, topk=4, max_tokens_per_rank=64)
+    assert cfg.inert_fields() == ()
+    noisy = Config(hidden_size=512, topk=4, max_tokens_per_rank=64, chunk_bytes=1 << 20, decode_max_tokens=32,
+                   decode_single_frame=True, combine_warp_specialization=True, workload="decode")
+    assert set(noisy.inert_fields()) == {"chunk_bytes", "decode_single_frame", "combine_warp_specialization", "workload"}
+    assert Config(hidden_size=512, topk=4, max_tokens_per_rank=64, transport="host_ce", chunk_bytes=1 << 20).inert_fields() == ()
+    for world in (1, 3, 8):
+        parts = cfg.nvlink_slot_breakdown(world)
+        assert parts["total"] == cfg.nvlink_slot_bytes(world)
+        assert parts["staging"] >= 64 * min(4, world) * (512 * 2 + 128)

@@ -56,8 +56,31 @@ def test_build_identity_is_stable_and_lazy_import_does_not_touch_cuda():
 
 def test_launch_width_follows_items_per_cta():
     core = object.__new__(TransportCore)
-    core.hidden, core.max_ctas, core.items_per_cta = 7168, 148, 16
-    assert core.pick_ctas(128) == 56 and core.pick_ctas(4096) == 148 and core.pick_ctas(1) == 1
+    core.hidden, core.max_ctas, core.items_per_cta = 7168, 148, 4
+    # dispatch: one mover warp per row (four per CTA) until the budget is reached
+    assert core.pick_ctas(128) == 32 and core.pick_ctas(4096) == 148 and core.pick_ctas(1) == 1
     assert core.pick_ctas(128, budget=30) == 30 and core.pick_ctas(0) == 1
-    core.items_per_cta = 4
-    assert core.pick_ctas(8) == 14 and core.pick_ctas(128) == 148
+    core.items_per_cta = 1
+    assert core.pick_ctas(8) == 8 and core.pick_ctas(128) == 128
+    core.hidden = 16384                       # rows of 32 KiB move as three pieces
+    assert core.pick_ctas(8) == 24
+    # combine: six received rows per CTA and round trip, at least one CTA per token
+    assert core.pick_combine_ctas(128, 1024) == 148 and core.pick_combine_ctas(1, 8) == 2
+    assert core.pick_combine_ctas(16, 16) == 16 and core.pick_combine_ctas(4096, 32768, budget=100) == 100
+
+
+def test_load_refuses_a_binary_built_from_other_sources(monkeypatch):
+    """The stamp names the sources a library was built from: a mismatch is never imported."""
+    from ep_xpress_b200 import native
+    monkeypatch.setattr(native, "_module", None)
+    monkeypatch.setattr(native, "source_identity", lambda: "0123456789abcdef")
+    monkeypatch.setattr(native.shutil, "which", lambda name: None)
+    assert not native.is_built()
+    with pytest.raises(RuntimeError, match="built from other sources"):
+        native.load()
+    rebuilt = []
+    monkeypatch.setattr(native.shutil, "which", lambda name: "/usr/local/cuda/bin/nvcc")
+    monkeypatch.setattr(native, "build", lambda **kwargs: rebuilt.append(True) or (_ for _ in ()).throw(RuntimeError("stop")))
+    with pytest.raises(RuntimeError, match="stop"):
+        native.load()                                # with a compiler present it rebuilds instead
+    assert rebuilt == [True]

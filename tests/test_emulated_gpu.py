@@ -156,21 +156,23 @@ def test_invalid_routes_are_reported():
             assert statuses[1][0] in (0, 4)
 
 
-@pytest.mark.parametrize("world,hidden,topk,tokens,chunk_bytes,ctas", [
-    (2, 256, 2, 64, 0, None),            # one chunk: everything is published at the end
-    (4, 2048, 4, 700, 64 << 10, None),   # eight chunks, several row segments
-    (8, 1024, 8, 300, 32 << 10, 12),     # full fan-out, few CTAs per rank
-    (3, 64, 4, 600, 4 << 10, 5),         # tiny rows, more tokens than one route tile
-    (4, 264, 4, 33, 1 << 10, None),      # rows that are not 16-byte multiples: the register path runs instead
+@pytest.mark.parametrize("protocol", ["on", "off"])
+@pytest.mark.parametrize("world,hidden,topk,tokens,ctas", [
+    (2, 256, 2, 64, None),
+    (4, 2048, 4, 700, None),      # several row segments per reduce item
+    (8, 1024, 8, 300, 12),        # full fan-out, few CTAs per rank
+    (3, 64, 4, 600, 5),           # tiny rows, more tokens than one route tile
+    (4, 264, 4, 33, None),        # rows that are not 16-byte multiples: the register path runs instead
+    (2, 8192, 2, 40, 7),          # rows larger than one mover / pusher stage: two pieces per row
 ])
-def test_streamed_combine_matches_the_oracle(world, hidden, topk, tokens, chunk_bytes, ctas):
-    """Push and reduce side by side: progress words gate each token, results stay bit-exact."""
+def test_both_combine_protocols_match_the_oracle(world, hidden, topk, tokens, ctas, protocol):
+    """Mailbox (push and reduce side by side, one arrival word per row) and sequential (push,
+    signal, wait, reduce): both bit-exact, on uneven batches and skewed routes."""
     experts = world * 4
     cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=2.0,
-                 combine_streaming="on")
+                 combine_streaming=protocol)
     emap = workloads.round_robin_expert_map(experts, world)
     with EmulatedGroup(world, emap, cfg) as group:
-        group.core.engine.set_combine_streaming(1, chunk_bytes)
         slot = group.create_slot()
         for seed in range(4):
             xs, ids, ws = [], [], []
@@ -185,7 +187,30 @@ def test_streamed_combine_matches_the_oracle(world, hidden, topk, tokens, chunk_
                       rounding="two_step")
 
 
-def test_streamed_and_sequential_combine_agree_across_slots():
+def test_a_short_partial_is_an_error_not_stale_data():
+    """A rank whose partial tensor has fewer rows than it received cannot serve every owner: it
+    reports a capacity error and the owners that wait for the missing rows stop with a status,
+    instead of reducing whatever an earlier combine left in the staging rows."""
+    world, hidden, topk, tokens = 2, 256, 2, 32
+    cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=0.5)
+    emap = workloads.round_robin_expert_map(4, world)
+    with EmulatedGroup(world, emap, cfg) as group:
+        slot = group.create_slot()
+        dev = group.device
+        routes = [workloads.uniform_routing(tokens, 4, topk, seed=1, rank=r) for r in range(world)]
+        xs = [workloads.gaussian_payload(tokens, hidden, seed=1, rank=r).to(dev) for r in range(world)]
+        batches = group.dispatch(slot, xs, [i.to(dev) for i, _ in routes], [w.to(dev) for _, w in routes])
+        partials = [group.scale_rows(b) for b in batches]
+        received = int(batches[0].valid_count.item())
+        assert received > 8
+        partials[0] = partials[0][:received - 5].clone()
+        group.combine(slot, partials, [tokens] * world)
+        statuses = [status[0] for status in group.status()]
+        assert statuses[0] == 2 and statuses[1] in (3, 4)
+        assert torch.ones(2, device=dev).sum().item() == 2   # the GPU is still usable
+
+
+def test_mailbox_and_sequential_combine_agree_across_slots():
     """Two outstanding handles combined in reverse order, one mode per slot use."""
     world, hidden, topk, tokens = 4, 512, 4, 96
     experts = world * 2
@@ -196,7 +221,7 @@ def test_streamed_and_sequential_combine_agree_across_slots():
         slots = [group.create_slot(), group.create_slot()]
         outs = {}
         for mode in (1, 0):
-            group.core.engine.set_combine_streaming(mode, 16 << 10)
+            group.core.engine.set_combine_streaming(mode)
             batches = []
             for index, slot in enumerate(slots):
                 xs = [workloads.gaussian_payload(tokens, hidden, seed=index, rank=r).to(dev) for r in range(world)]

@@ -51,7 +51,37 @@ def test_reverse_order_handles():
 @pytest.mark.multigpu
 @pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
 def test_cuda_graph_replay_with_changing_routes():
-    launch("graph", min(gpu_count(), 4))
+    """1000 replays over four captured buckets (one leaves a rank empty), every replay checked."""
+    launch("graph", min(gpu_count(), 4), "--replays", "1000", timeout=900)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_cuda_graph_replay_at_decode_size_with_fused_combine():
+    launch("graph", min(gpu_count(), 4), "--hidden", "7168", "--tokens", "128", "--replays", "300",
+           "--check-every", "10", "--decode-max-tokens", "128", timeout=900)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_ticket_and_direct_calls_across_streams():
+    launch("streams", min(gpu_count(), 4))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_staggered_ranks_and_lagging_readers():
+    launch("stagger", min(gpu_count(), 4))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_benchmarked_shape_is_bit_exact():
+    launch("headline", min(gpu_count(), 8), "--hidden", "7168", "--tokens", "4096", timeout=900)
 
 
 @pytest.mark.gpu
@@ -66,3 +96,10 @@ def test_undersized_capacity_poisons_the_group_without_hanging():
 @pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
 def test_operation_profile():
     launch("profile", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_host_staged_transport_on_cuda_tensors():
+    launch("hostce", 2)
