@@ -197,7 +197,7 @@ def main():
     emap = workloads.contiguous_expert_map(shape["experts"], world)
     owner = torch.tensor(emap)
     cfg = Config(hidden_size=shape["hidden"], topk=shape["topk"], max_tokens_per_rank=max(args.tokens),
-                 timeout_seconds=30.0, gpu_pool_budget_bytes=64 << 30, slots=1,
+                 timeout_seconds=30.0, slots=1,
                  combine_streaming=args.combine_streaming,
                  workspace_pool_bytes=2 * Config(hidden_size=shape["hidden"], topk=shape["topk"],
                                                  max_tokens_per_rank=max(args.tokens)).nvlink_slot_bytes(world))

@@ -33,7 +33,7 @@ def main():
     parser.add_argument("--iterations", type=int, default=5)
     args = parser.parse_args()
     cfg = Config(hidden_size=args.hidden, topk=args.topk, max_tokens_per_rank=args.tokens, timeout_seconds=10.0,
-                 gpu_pool_budget_bytes=32 << 30, slots=1, workspace_pool_bytes=1 << 20)
+                 slots=1, workspace_pool_bytes=1 << 20)
     emap = workloads.contiguous_expert_map(args.experts, args.world)
     with EmulatedGroup(args.world, emap, cfg) as group:
         slot = group.create_slot()

@@ -94,7 +94,7 @@ def main():
     results = []
     for tokens in args.tokens:
         cfg = Config(hidden_size=args.hidden, topk=args.topk, max_tokens_per_rank=tokens, timeout_seconds=30.0,
-                     gpu_pool_budget_bytes=64 << 30, slots=1)
+                     slots=1)
         ep = Context(get_nccl_comm_handle(dist.group.WORLD), emap, cfg)
         pairs = int(tokens * args.topk * 1.5) + 1024
         layer = SwiGLUMoELayer(ep, w13, w2, max_local_pairs=pairs, pair_ctas=not args.single_cta)

@@ -8,8 +8,11 @@ position-marker payloads, checked bit for bit: received rows, local ids, weights
 map, padding, and the rank-order BF16 combine. ``--expect-error`` injects one fault on the
 host side of the API (invalid id, duplicate expert, NaN weight, capacity 0, consumed handle)
 and checks that it surfaces as the documented error without hanging any rank;
-``--delay-rank`` makes one rank enter every operation late. Behavioural re-creation of the
-reference's harness (benchmarks/replay.py:19-473).
+``--delay-rank`` makes one rank enter every operation late; ``--profile-combine`` runs every
+operation with the profiling kernels and checks the report's invariants (every CTA reaches the
+last phase, disjoint phases sum to the CTA's elapsed time, bytes = rows x row size, rows
+stored = rows the route plan sends; the checks of the reference's harness,
+benchmarks/replay.py:185-268). Behavioural re-creation of that harness (benchmarks/replay.py:19-473).
 """
 
 from __future__ import annotations
@@ -42,6 +45,7 @@ def main():
     parser.add_argument("--hidden", type=int, default=256)
     parser.add_argument("--expect-error", choices=ERRORS, default="none")
     parser.add_argument("--delay-rank", type=int, default=-1)
+    parser.add_argument("--profile-combine", action="store_true")
     args = parser.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -53,9 +57,13 @@ def main():
     ep = Context(get_nccl_comm_handle(dist.group.WORLD), emap, cfg)
     factors = [(r * per_rank + torch.arange(per_rank, dtype=torch.float32) + 1) / 8 for r in range(world)]
     mine = factors[rank].cuda()
+    profiled = []
     try:
         for case in workloads.REPLAY_CASES:
             for iteration in range(args.iterations):
+                if args.profile_combine:
+                    ep.start_combine_profile(max_operations=4)
+                    ep.set_combine_profile_label(f"{case}/{iteration}")
                 xs, ids, ws = [], [], []
                 for r in range(world):
                     i, w, _ = workloads.replay_case(case, rank=r, world_size=world, tokens=args.tokens, topk=topk,
@@ -82,6 +90,9 @@ def main():
                 assert (batch.local_ids[valid:] == -1).all() and (batch.hidden[valid:].view(torch.int16) == 0).all()
                 out = ep.combine_async(scale_rows(ep, batch, mine), batch.handle, tag=[case, iteration]).wait()
                 assert torch.equal(bits(out), bits(want[rank])), (case, iteration)
+                if args.profile_combine:
+                    report = ep.stop_combine_profile()
+                    profiled.append(check_profile(report, plan, rank, world, args.hidden, f"{case}/{iteration}"))
         ep.check()
         if args.expect_error != "none":
             inject(ep, args, rank, world, topk, per_rank)
@@ -90,9 +101,30 @@ def main():
     probe = torch.ones(1, device="cuda")
     dist.all_reduce(probe)
     dist.destroy_process_group()
+    if rank == 0 and profiled:
+        print(f"profile ok: {len(profiled)} dispatch/combine pairs, dispatch p50 "
+              f"{sorted(p[0] for p in profiled)[len(profiled) // 2]} ns, combine p50 "
+              f"{sorted(p[1] for p in profiled)[len(profiled) // 2]} ns on rank 0")
     if rank == 0:
         print(f"replay ok: {len(workloads.REPLAY_CASES)} cases x {args.iterations} iterations on {world} ranks"
               + (f", error '{args.expect_error}' surfaced as documented" if args.expect_error != "none" else ""))
+
+
+def check_profile(report, plan, rank, world, hidden, label):
+    """Invariants of one profiled dispatch/combine pair; returns their elapsed times (ns)."""
+    from ep_xpress_b200.utils.profile import check_invariants
+    assert report["dropped_operations"] == 0 and [op["kind"] for op in report["operations"]] == ["dispatch", "combine"]
+    dispatch, combine = report["operations"]
+    assert dispatch["label"] == combine["label"] == label
+    for entry in (dispatch, combine):
+        check_invariants(entry, row_bytes=hidden * 2)
+    sent = int((plan.dest_rows[rank] >= 0).sum())                       # rows this rank's tokens go to
+    owed = plan.received[rank].rows - int((plan.received[rank].source_rank == rank).sum())
+    assert dispatch["rows"] == sent, (dispatch["rows"], sent)
+    assert combine["rows"] == owed, (combine["rows"], owed)            # rows pushed back to other ranks
+    if world > 1 and sent:
+        assert dispatch["first_publish_ns"] is not None and dispatch["first_receive_ns"] is not None
+    return dispatch["elapsed_ns"], combine["elapsed_ns"]
 
 
 def inject(ep, args, rank, world, topk, per_rank):

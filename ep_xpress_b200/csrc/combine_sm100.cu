@@ -21,13 +21,14 @@
 // launches (host_sm.cu:559-590, :1212-1468, :592-607) and, like its mailbox kernel
 // (host_sm.cu:1952-2511), receives and reduces in the same kernel. Default protocol
 // ("mailbox", groups of two or more ranks, 16-byte rows, fan-out up to eight):
-//   push     two pusher warps per CTA claim received rows whose token lives on a peer.
-//            A row travels partial -> shared memory -> the owner's staging row as bulk
-//            asynchronous copies (TMA, no tensor map); when the copies of a batch have
-//            completed, the pusher stores the combine epoch into the arrival word that
-//            sits right behind the staging row (release, system scope). No CTA-wide
-//            fence, no counter, no "all rows are out" message.
-//   reduce   at the same time the other warps of every CTA walk the rank's own tokens:
+//   push     some CTAs of the launch only push: their pusher warp claims received rows whose
+//            token lives on a peer, fifteen per round. A row travels partial -> shared
+//            memory -> the owner's staging row as bulk asynchronous copies (TMA, no tensor
+//            map); when the copies of a round have completed, the pusher stores the
+//            combine epoch into the arrival word that sits right behind each staging row
+//            (one system-scope fence per round). No CTA-wide fence, no counter, no "all
+//            rows are out" message.
+//   reduce   at the same time the other CTAs walk the rank's own tokens:
 //            a producer warp polls the arrival words of exactly the rows a token is
 //            owed (local memory), copies them into a shared-memory stage, and four
 //            consumer warps add them in rank order and store the result.
@@ -211,19 +212,45 @@ constexpr int kMaxGroupStages = 3;
 constexpr int kChunksPerThread = 4;
 constexpr int kSegMaxBytes = 16384;               // largest row segment of one item
 
-// Mailbox protocol: 2 pipelines (10 warps) and 2 pusher warps per CTA.
-constexpr int kMailGroups = 2;
-constexpr int kPushers = 2;
-constexpr int kMailThreads = (kMailGroups * (kGroupWarps + 1) + kPushers) * 32;
-constexpr size_t kMailReduceSmem = 128 * 1024;    // stage rings of the two pipelines
-constexpr int kPushStages = 3;                    // bulk copies one pusher keeps in flight
+// Mailbox protocol: the CTAs of a launch split into PUSH CTAs and REDUCE CTAs. A push CTA runs
+// one pusher warp that owns the whole shared memory as fifteen row stages; a reduce CTA runs
+// four reduce pipelines. The roles live on different SMs because they disturb each other on one:
+// every bulk copy of an SM goes through that SM's one copy engine, where the reducers' loads
+// queue behind peer stores that the saturated link drains slowly (measured: 3.8 us per reduce
+// item next to a pusher, 1.1 us alone), and the system-scope fence in front of a round's
+// arrival words waits for every store the SM has in flight.
+//
+// That fence is the price of a release at system scope: it does not complete while its SM has
+// peer stores in flight and holds up the SM's next stores meanwhile. Measured at 2 GPUs, 4096
+// tokens (58 MB pushed per rank): pushers done after 113 us with the fence, 92 us when the words
+// are stored right after the copies completed without a fence (not kept: the copies are then
+// complete at their owner, but nothing in the PTX memory model makes a relaxed store a release);
+// moving the fence to a second warp of the push CTA, to a warp of a reduce CTA or to a CTA of
+// its own changed nothing or made it worse (the fence stalls whichever SM runs it, and a busy
+// SM's fence is as slow as the pusher's own).
+constexpr int kMailGroups = kMaxGroups;
+constexpr int kMailThreads = kBulkThreads;
+constexpr size_t kMailReduceSmem = kBulkSmemBytes;
+constexpr int kPushStages = 15;                   // bulk copies a pusher keeps in flight
 constexpr int kPushStageBytes = 14336;
-constexpr size_t kMailSmemBytes = kMailReduceSmem + static_cast<size_t>(kPushers) * kPushStages * kPushStageBytes;
+constexpr size_t kMailSmemBytes = static_cast<size_t>(kPushStages) * kPushStageBytes;   // >= kMailReduceSmem
+static_assert(kMailSmemBytes >= kMailReduceSmem, "a reduce CTA's rings must fit the launch's shared memory");
 
-// Segment size: as large as possible while every group still gets two stages of `fan`
-// contributor slots (one being filled while the other is reduced).
+// Push CTAs of a mailbox launch of `ctas` CTAs (at least two): enough SMs to keep the link
+// busy - a pusher moves fifteen rows per round trip - and the rest reduce, which is the heavier
+// job in bytes (every pushed row is read again, plus the local rows and the output).
+__host__ __device__ __forceinline__ int mailbox_push_ctas(int ctas) {
+  const int wanted = ctas * 7 / 16;
+  return wanted < 1 ? 1 : (wanted > 64 ? 64 : wanted);
+}
+
+// Segment size: as large as possible while every group still gets three stages of `fan`
+// contributor slots (an item's latency chain - arrival check, copy, reduce, hand-back - is
+// several times its reduce time, so two stages leave the consumers waiting); two stages when
+// three would push the segments below 2 KiB.
 __device__ __forceinline__ int ring_segment_bytes(int fan, size_t group_smem) {
-  const int fit = static_cast<int>(group_smem / (2 * static_cast<size_t>(fan))) / 512 * 512;
+  int fit = static_cast<int>(group_smem / (3 * static_cast<size_t>(fan))) / 512 * 512;
+  if (fit < 2048) fit = static_cast<int>(group_smem / (2 * static_cast<size_t>(fan))) / 512 * 512;
   return fit < kSegMaxBytes ? fit : kSegMaxBytes;
 }
 __device__ __forceinline__ int ring_stages(int fan, int segment_bytes, size_t group_smem) {
@@ -248,9 +275,6 @@ __device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
-}
-__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Shared -> global copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) by the
 // copy engine of this SM; the destination may be a peer's memory. Completion is tracked by the
@@ -278,6 +302,7 @@ struct BulkReduceArgs {
   bool single_round;
   unsigned long long timeout_ns;
   unsigned long long* profile;
+  int cta, ctas;          // this CTA's index among the CTAs that reduce, and their number
   // mailbox launches only
   const RankCtx* ctx;
   unsigned epoch;
@@ -289,9 +314,10 @@ struct BulkReduceArgs {
 // producer copies a token's rows, lane j waits (bounded) for the arrival word behind the staging
 // row of remote contributor j to carry this combine's epoch, and the CTAs take items round-robin
 // so that each of them owns tokens from every part of the batch.
-template <int kGroups, bool kMailbox, size_t kReduceSmem>
+template <int kGroups, bool kMailbox, size_t kReduceSmem, bool kProfile>
 __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem, unsigned long long* full_all,
-                                            unsigned long long* empty_all, StageItem* items_all) {
+                                            unsigned long long* empty_all, StageItem* items_all,
+                                            Profiler<kProfile>& prof) {
   constexpr int kConsumerWarps = kGroups * kGroupWarps;
   constexpr size_t kGroupSmemBytes = kReduceSmem / kGroups;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -308,13 +334,12 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   unsigned long long* const empty = empty_all + group * kMaxGroupStages;
   StageItem* const slots = items_all + group * kMaxGroupStages;
   // Items of this CTA are a contiguous range (local memory only: a static split is balanced),
-  // or every gridDim.x-th item in mailbox launches; the groups take them round-robin.
-  const int lo = kMailbox ? static_cast<int>(blockIdx.x)
-                          : static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
-  const int hi = static_cast<int>(static_cast<long long>(items) * (blockIdx.x + 1) / gridDim.x);
-  const int stride = kMailbox ? static_cast<int>(gridDim.x) : 1;
+  // or every ctas-th item in mailbox launches; the groups take them round-robin.
+  const int lo = kMailbox ? a.cta : static_cast<int>(static_cast<long long>(items) * a.cta / a.ctas);
+  const int hi = static_cast<int>(static_cast<long long>(items) * (a.cta + 1) / a.ctas);
+  const int stride = kMailbox ? a.ctas : 1;
   const int cta_items = kMailbox ? (items > lo ? (items - lo + stride - 1) / stride : 0)
-                                 : hi - static_cast<int>(static_cast<long long>(items) * blockIdx.x / gridDim.x);
+                                 : hi - static_cast<int>(static_cast<long long>(items) * a.cta / a.ctas);
   const int mine = cta_items > group ? (cta_items - group + kGroups - 1) / kGroups : 0;
   long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
   bool ok = true;
@@ -338,11 +363,25 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       if (base + 32 < mine) load_batch(base + 32, mask_next, rows_next);
 #pragma unroll
       for (int r = 0; r < 8; ++r) {
+        // Mailbox: one look at the arrival words of the next four items (lane 8q + j: contributor
+        // j of item 4r + q), so that the words' latency is paid once per four items. A word that
+        // already carries the epoch is final; the others are polled again when their item is up.
+        unsigned early = a.epoch;
+        if (kMailbox) {
+          const unsigned long long mk = __shfl_sync(0xffffffffu, mask_now, 4 * r + (lane >> 3));
+          const int k = base + 4 * r + (lane >> 3), j = lane & 7;
+          if (k < mine && j < __popcll(mk) && rows_now[r] >= 0 && nth_set_bit(mk, j) != a.self) {
+            const long long tk = item_of(k) / rsegs;
+            early = ld_acquire_sys_u32(reinterpret_cast<const unsigned*>(a.staging + (tk * a.fan + j) * a.stride + a.row_bytes));
+          }
+          __syncwarp();        // the lane that copies a row is not the lane that looked at its word
+        }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int i = 4 * r + q;
           const unsigned long long m = __shfl_sync(0xffffffffu, mask_now, i);
           const int row = __shfl_sync(0xffffffffu, rows_now[r], q * 8 + (lane & 7));
+          const unsigned seen = __shfl_sync(0xffffffffu, early, q * 8 + (lane & 7));
           if (base + i >= mine || !ok) continue;                 // warp-uniform
           const int stage = use % stages;
           const unsigned parity = ((use / stages) & 1u) ^ 1u;
@@ -371,15 +410,19 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             // Contributor `lane` is a peer: its row is in once the word behind it carries this epoch.
             const bool remote = src != nullptr && !is_self;
             bool fine = true;
-            if (remote) {
+            const unsigned long long wait_begin = prof.on() && group == 0 && lane == 0 ? global_timer_ns() : 0ull;
+            if (remote && seen != a.epoch) {
               const unsigned* word = reinterpret_cast<const unsigned*>(src + a.row_bytes);
               if (ld_acquire_sys_u32(word) != a.epoch)
-                fine = bounded_wait(*a.ctx, kPhaseCombine, 5, [&] { return ld_acquire_sys_u32(word) == a.epoch; });
+                fine = bounded_wait(*a.ctx, kPhaseCombine, 5, [&] { return ld_acquire_sys_u32(word) == a.epoch; },
+                                    prof.poll_counter());
             }
+            if (remote && fine) prof.first(kProfFirstReceive);
             if (!__all_sync(0xffffffffu, fine)) {
               ok = false;
               continue;
             }
+            if (wait_begin != 0ull) prof.count(kProfArrivalWait, global_timer_ns() - wait_begin);
             fence_proxy_async();      // the rows were written by a peer; the copies below read them through the async proxy
           }
           const unsigned valid = __ballot_sync(0xffffffffu, src != nullptr);
@@ -392,6 +435,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             slot.self_index = self_vote ? __ffs(self_vote) - 1 : -1;
             slot.valid = valid;
             slot.end = 0;
+            prof.count(kProfItems, 1);
             mbarrier_arrive_expect_tx(full + stage, static_cast<unsigned>(__popc(valid)) * static_cast<unsigned>(bytes));
           }
           __syncwarp();
@@ -467,7 +511,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       worked += clock64() - t1;
     }
   }
-  if (a.profile != nullptr && lane == 0 && (warp == 0 || warp == kConsumerWarps)) {   // group 0
+  if (kProfile && a.profile != nullptr && lane == 0 && (warp == 0 || warp == kConsumerWarps)) {   // group 0
     unsigned long long* slot = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps + (warp == 0 ? 4 : 6);
     slot[0] = static_cast<unsigned long long>(waited);
     slot[1] = static_cast<unsigned long long>(worked);
@@ -512,8 +556,8 @@ __device__ __forceinline__ bool push_target(const PushArgs& p, long long q, long
   return *row < p.valid;
 }
 
-template <int kWords, int kUnroll>
-__device__ __forceinline__ void push_item(const PushArgs& p, long long item, int lane) {
+template <int kWords, int kUnroll, bool kProfile>
+__device__ __forceinline__ void push_item(const PushArgs& p, long long item, int lane, Profiler<kProfile>& prof) {
   constexpr int kChunk = kWords * 4;
   const int seg = static_cast<int>(item % p.segs);
   long long row;
@@ -524,6 +568,7 @@ __device__ __forceinline__ void push_item(const PushArgs& p, long long item, int
   char* dst = p.stage[source] + back * p.stride;
   const long long b0 = seg * p.seg_bytes;
   const long long b1 = min(p.row_bytes, b0 + p.seg_bytes);
+  if (lane == 0 && b1 > b0) prof.moved(seg == 0 ? 1 : 0, static_cast<unsigned long long>(b1 - b0));
   for (long long base = b0 + static_cast<long long>(lane) * kChunk; base < b1; base += 32ll * kChunk * kUnroll) {
     Chunk<kWords> v[kUnroll];
 #pragma unroll
@@ -540,70 +585,88 @@ __device__ __forceinline__ void push_item(const PushArgs& p, long long item, int
 }
 
 // ---- mailbox push ---------------------------------------------------------------------------
-// Run by ONE thread of each pusher warp. Rows are claimed from the rank's counter and moved in
-// batches of kPushStages pieces (a row of up to kPushStageBytes is one piece): all loads of a
-// batch are issued, each store follows its load, and once every copy of the batch has
-// completed the arrival words of the rows that ended in it are released. The copies run in the
-// SM's copy engine; the thread only issues and waits, so two pushers per CTA keep far more
-// bytes in flight than the link needs.
+// Run by the pusher warp of a push CTA; lane i < kPushStages owns stage i. Per round the
+// warp claims one piece per lane with a single atomic (a row of up to kPushStageBytes is one
+// piece; towards the end of the batch the rounds shrink to an even share of what is left),
+// every lane resolves its piece, loads it into its stage, stores it to the owner's
+// staging row and waits for its own copies to complete; then ONE system-scope fence orders the
+// round's completed rows before the arrival words, which the lanes that moved a row's last
+// piece store relaxed (a release per word would serialise a round trip to the peer per word).
+// The copies run in the SM's copy engine; the lanes only issue and wait, in lockstep, so a
+// round costs one chain of latencies (claim, look-up, load, store + acknowledgement, fence)
+// whatever the number of rows in it.
+template <bool kProfile>
 __device__ __forceinline__ bool mailbox_push(const PushArgs& p, const RankCtx& c, CtrlHeader* hdr, char* stages,
-                                             unsigned long long* full, unsigned epoch) {
+                                             unsigned long long* full, unsigned epoch, int lane, int push_ctas,
+                                             Profiler<kProfile>& prof) {
   const int peers = p.world - 1;
   const long long blocks = (p.most + kPushBlock - 1) / kPushBlock;
-  const long long items = blocks * peers * kPushBlock;
   const int pieces = static_cast<int>((p.row_bytes + kPushStageBytes - 1) / kPushStageBytes);
   const int piece_bytes = static_cast<int>(align_up((p.row_bytes + pieces - 1) / pieces, 16));
-  unsigned parity = 0;
-  const char* src_row = nullptr;     // row being moved: source, destination, next piece
-  char* dst_row = nullptr;
-  int piece = pieces;                // == pieces: no row in hand
-  bool more = true;
-  while (more) {
-    unsigned* words[kPushStages];
-    char* dst[kPushStages];
-    int bytes[kPushStages];
-    int count = 0;
-    while (count < kPushStages) {
-      if (piece == pieces) {
-        const long long item = atomicAdd(&hdr->cwork_push, 1u);
-        if (item >= items) { more = false; break; }
-        long long row;
-        int source;
-        if (!push_target(p, item, &row, &source)) continue;
-        src_row = p.partial + row * p.row_bytes;
-        dst_row = p.stage[source] + static_cast<long long>(p.ret[row]) * p.stride;
-        piece = 0;
-      }
-      const long long b0 = static_cast<long long>(piece) * piece_bytes;
-      bytes[count] = static_cast<int>(min(p.row_bytes, b0 + piece_bytes) - b0);
-      dst[count] = dst_row + b0;
-      ++piece;
-      words[count] = piece == pieces ? reinterpret_cast<unsigned*>(dst_row + p.row_bytes) : nullptr;
-      char* stage = stages + static_cast<size_t>(count) * kPushStageBytes;
-      mbarrier_arrive_expect_tx(full + count, static_cast<unsigned>(bytes[count]));
-      bulk_load_to_smem(stage, src_row + b0, static_cast<unsigned>(bytes[count]), full + count);
-      ++count;
+  const long long items = blocks * peers * kPushBlock * pieces;
+  // All pieces of a row travel in the same round, so that the row's arrival word can follow it.
+  const unsigned per_round = static_cast<unsigned>(kPushStages / pieces * pieces);
+  char* const stage = stages + static_cast<size_t>(lane < kPushStages ? lane : 0) * kPushStageBytes;
+  unsigned long long* const bar = full + (lane < kPushStages ? lane : 0);
+  unsigned parity = 0;                                  // of this lane's barrier
+  bool ok = true;
+  while (true) {
+    unsigned base = 0, take = per_round;
+    if (lane == 0) {
+      const long long left = items - static_cast<long long>(ld_volatile_u32(&hdr->cwork_push));
+      const long long share = ((left > 0 ? left : 0) / pieces + push_ctas - 1) / push_ctas * pieces;
+      if (share < static_cast<long long>(take)) take = static_cast<unsigned>(share < pieces ? pieces : share);
+      base = atomicAdd(&hdr->cwork_push, take);
     }
-    if (count == 0) break;
-    for (int i = 0; i < count; ++i) {
-      if (!mbarrier_wait_bounded(full + i, parity, c.timeout_ns)) return false;
-      bulk_store_from_smem(dst[i], stages + static_cast<size_t>(i) * kPushStageBytes, static_cast<unsigned>(bytes[i]));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    take = __shfl_sync(0xffffffffu, take, 0);
+    if (static_cast<long long>(base) >= items) break;
+    const long long item = static_cast<long long>(base) + lane;
+    char* dst = nullptr;
+    unsigned* word = nullptr;
+    int bytes = 0;
+    if (lane < static_cast<int>(take) && item < items) {
+      const int piece = static_cast<int>(item % pieces);
+      long long row;
+      int source;
+      if (push_target(p, item / pieces, &row, &source)) {
+        const long long b0 = static_cast<long long>(piece) * piece_bytes;
+        bytes = static_cast<int>(min(p.row_bytes, b0 + piece_bytes) - b0);
+        char* dst_row = p.stage[source] + static_cast<long long>(p.ret[row]) * p.stride;
+        dst = dst_row + b0;
+        if (piece == pieces - 1) word = reinterpret_cast<unsigned*>(dst_row + p.row_bytes);
+        mbarrier_arrive_expect_tx(bar, static_cast<unsigned>(bytes));
+        bulk_load_to_smem(stage, p.partial + row * p.row_bytes + b0, static_cast<unsigned>(bytes), bar);
+      }
+    }
+    const unsigned long long wait_begin = prof.on() && lane == 0 ? global_timer_ns() : 0ull;
+    if (dst != nullptr) {
+      if (mbarrier_wait_bounded(bar, parity, c.timeout_ns)) {
+        parity ^= 1u;
+        fence_proxy_async();
+        bulk_store_from_smem(dst, stage, static_cast<unsigned>(bytes));
+        prof.moved(word != nullptr ? 1 : 0, static_cast<unsigned long long>(bytes));
+      } else {
+        ok = false;
+      }
     }
     bulk_commit_group();
     bulk_wait_all_complete();
+    if (wait_begin != 0ull) prof.count(kProfPushWait, global_timer_ns() - wait_begin);
     fence_proxy_async();               // the copies wrote through the async proxy; the words below are ordinary stores
-    for (int i = 0; i < count; ++i)
-      if (words[i] != nullptr) st_release_sys_u32(words[i], epoch);
-    // A stage whose barrier was not used in this batch keeps its phase: only full batches flip
-    // every barrier, and a short batch is always the last one.
-    parity ^= 1u;
+    if (!__all_sync(0xffffffffu, ok)) break;
+    __threadfence_system();
+    if (word != nullptr) {
+      st_relaxed_sys_u32(word, epoch);
+      prof.first(kProfFirstPublish);
+    }
   }
-  return true;
+  return __all_sync(0xffffffffu, ok);
 }
 
 enum CombineMode : int { kModeRegister = 0, kModeBulk = 1, kModeMailbox = 2 };
 
-template <bool kVec16, int kMode>
+template <bool kVec16, int kMode, bool kProfile>
 __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_smem) {
   static_assert(kVec16 || kMode == kModeRegister, "the bulk-copy paths need 16-byte rows");
   constexpr bool kBulk = kMode != kModeRegister;
@@ -636,10 +699,12 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   __shared__ int s_most;
   __shared__ int s_last;
   __shared__ unsigned long long s_full[kMaxGroups * kMaxGroupStages], s_empty[kMaxGroups * kMaxGroupStages];
-  __shared__ unsigned long long s_push_full[kPushers * kPushStages];
+  __shared__ unsigned long long s_push_full[kPushStages + 1];
   __shared__ StageItem s_items[kMaxGroups * kMaxGroupStages];
 
-  profile_stamp(op.profile, 0);
+  Profiler<kProfile> prof(op.profile);
+  prof.stamp(0);
+  if (prof.on() && threadIdx.x == 0) prof.record[kProfMode] = 1 + kMode;
   const unsigned e = ld_volatile_u32(&hdr->comb_epoch) + 1;
   if (e > kLastEpoch) {       // epochs never wrap; uniform over the rank's CTAs
     if (threadIdx.x == 0 && blockIdx.x == 0) report_error(c, kEpochsExhausted, kPhaseCombine, 0xE0, e);
@@ -672,7 +737,8 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       mbarrier_init(s_full + tid, 1);
       mbarrier_init(s_empty + tid, kGroupWarps);
     }
-    if (tid >= 96 && tid < 96 + kPushers * kPushStages) mbarrier_init(s_push_full + (tid - 96), 1);
+    if (tid >= 96 && tid < 96 + kPushStages) mbarrier_init(s_push_full + (tid - 96), 1);
+
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
@@ -697,22 +763,22 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   reduce.ctx = &c;
   reduce.epoch = e;
 
+  reduce.cta = static_cast<int>(blockIdx.x);
+  reduce.ctas = static_cast<int>(gridDim.x);
   if (kMode == kModeMailbox) {
-    // ---- push and reduce side by side ----------------------------------------------------
-    constexpr int kReduceWarps = kMailGroups * (kGroupWarps + 1);
-    const int warp = tid >> 5;
+    // ---- push CTAs and reduce CTAs side by side (a mailbox launch has >= 2 CTAs) ----
+    const int push_ctas = mailbox_push_ctas(static_cast<int>(gridDim.x));
     debug_delay(c, 4);
-    if (warp >= kReduceWarps) {
-      if (lane == 0) {
-        const int pusher = warp - kReduceWarps;
-        char* stages = dynamic_smem + kMailReduceSmem + static_cast<size_t>(pusher) * kPushStages * kPushStageBytes;
-        if (!mailbox_push(push, c, hdr, stages, s_push_full + pusher * kPushStages, e))
+    if (static_cast<int>(blockIdx.x) < push_ctas) {
+      if (tid < 32) {
+        if (!mailbox_push<kProfile>(push, c, hdr, dynamic_smem, s_push_full, e, lane, push_ctas, prof) && lane == 0)
           report_error(c, kTimeout, kPhaseCombine, 6, 0);
-        if (op.profile != nullptr && pusher == 0)
-          op.profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + 1] = global_timer_ns();
+        if (kProfile && prof.on() && lane == 0) prof.record[1] = global_timer_ns();
       }
     } else {
-      if (!bulk_reduce<kMailGroups, true, kMailReduceSmem>(reduce, dynamic_smem, s_full, s_empty, s_items))
+      reduce.cta = static_cast<int>(blockIdx.x) - push_ctas;
+      reduce.ctas = static_cast<int>(gridDim.x) - push_ctas;
+      if (!bulk_reduce<kMailGroups, true, kMailReduceSmem, kProfile>(reduce, dynamic_smem, s_full, s_empty, s_items, prof))
         report_error(c, kTimeout, kPhaseCombine, 4, 0);
     }
   } else {
@@ -727,11 +793,11 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       const long long item = __shfl_sync(0xffffffffu, next_claim, 0);
       if (item >= items) break;
       if (lane == 0) next_claim = atomicAdd(&hdr->cwork_push, 1u);   // in flight while this item is copied
-      push_item<kWords, kUnroll>(push, item, lane);
+      push_item<kWords, kUnroll, kProfile>(push, item, lane, prof);
     }
   }
   __syncthreads();
-  profile_stamp(op.profile, 1);
+  prof.stamp(1);
   debug_delay(c, 5);
 
   // A group of one rank has nobody to signal or to wait for.
@@ -747,23 +813,25 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
     if (s_last && tid < W && tid != self) {
       unsigned long long* word = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.ready) + self;
       red_max_release_sys(word, all_pushed);
+      prof.first(kProfFirstPublish);
     }
 
     // ---- C. wait for the peers that push to me ----------------------------------------------
     bool ok = true;
     if (tid < W && s_need[tid]) {
       const unsigned long long* word = reinterpret_cast<const unsigned long long*>(my_heap + cl.ready) + tid;
-      ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(word) >= all_pushed; });
+      ok = bounded_wait(c, kPhaseCombine, 2, [&] { return ld_acquire_sys(word) >= all_pushed; }, prof.poll_counter());
+      if (ok) prof.first(kProfFirstReceive);
     }
     if (!__syncthreads_and(ok)) return;
   }
-  profile_stamp(op.profile, 2);
+  prof.stamp(2);
   debug_delay(c, 6);
 
   // ---- D. rank-order reduce from local memory -----------------------------------------------
   if (kBulk) {
     fence_proxy_async();      // the rows were written by generic stores; the reduce reads them through the async proxy
-    if (!bulk_reduce<kMaxGroups, false, kBulkSmemBytes>(reduce, dynamic_smem, s_full, s_empty, s_items))
+    if (!bulk_reduce<kMaxGroups, false, kBulkSmemBytes, kProfile>(reduce, dynamic_smem, s_full, s_empty, s_items, prof))
       report_error(c, kTimeout, kPhaseCombine, 4, 0);
   } else {
     const long long items = static_cast<long long>(T) * segs;
@@ -772,6 +840,7 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       if (lane == 0) claimed = atomicAdd(&hdr->cwork_reduce, 1u);
       const long long item = __shfl_sync(0xffffffffu, claimed, 0);
       if (item >= items) break;
+      if (lane == 0) prof.count(kProfItems, 1);
       const int t = static_cast<int>(item / segs), seg = static_cast<int>(item % segs);
       const unsigned long long m = mask_arr[t];
       const int n = __popcll(m);
@@ -834,8 +903,9 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
 
   // ---- E. retire the epoch ---------------------------------------------------------------
   __syncthreads();
-  if (kMode == kModeMailbox) profile_stamp(op.profile, 2);
-  profile_stamp(op.profile, 3);
+  if (kMode == kModeMailbox) prof.stamp(2);
+  prof.stamp(3);
+  prof.flush(&hdr->status);
   sample_end(op.samples, sample);
   if (tid == 0) {
     const unsigned prev = atomicAdd(&hdr->cfin_count, 1u);
@@ -850,11 +920,11 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   }
 }
 
-template <bool kVec16, int kMode>
+template <bool kVec16, int kMode, bool kProfile>
 __global__ void __launch_bounds__(kMode == kModeMailbox ? kMailThreads : (kMode == kModeBulk ? kBulkThreads : kThreads), 1)
 combine_kernel(const __grid_constant__ CombineArgs args) {
   extern __shared__ __align__(128) char combine_smem[];
-  combine_body<kVec16, kMode>(args.op[blockIdx.y], combine_smem);
+  combine_body<kVec16, kMode, kProfile>(args.op[blockIdx.y], combine_smem);
 }
 
 struct CombineVariant {
@@ -864,21 +934,26 @@ struct CombineVariant {
 };
 
 // The bulk-copy reduce needs 16-byte rows and at most kPeerBatch contributors per token; the
-// mailbox protocol exists for the bulk-copy reduce and for groups of two or more ranks.
-cudaError_t pick_combine(bool vec16, int fanout, bool mailbox, CombineVariant* out) {
+// mailbox protocol exists for the bulk-copy reduce and for groups of two or more ranks. The
+// profiling specialisations are separate kernels: an ordinary launch carries no timers.
+template <bool kProfile>
+cudaError_t pick_combine_of(bool vec16, int fanout, bool mailbox, CombineVariant* out) {
   if (vec16 && fanout <= kPeerBatch) {
     if (mailbox) {
-      *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeMailbox>), kMailThreads, kMailSmemBytes};
-      return cudaFuncSetAttribute(combine_kernel<true, kModeMailbox>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(kMailSmemBytes));
+      *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeMailbox, kProfile>), kMailThreads, kMailSmemBytes};
+      return cudaFuncSetAttribute(combine_kernel<true, kModeMailbox, kProfile>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMailSmemBytes));
     }
-    *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeBulk>), kBulkThreads, kBulkSmemBytes};
-    return cudaFuncSetAttribute(combine_kernel<true, kModeBulk>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeBulk, kProfile>), kBulkThreads, kBulkSmemBytes};
+    return cudaFuncSetAttribute(combine_kernel<true, kModeBulk, kProfile>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(kBulkSmemBytes));
   }
-  if (vec16) *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeRegister>), kThreads, 0};
-  else *out = {reinterpret_cast<const void*>(combine_kernel<false, kModeRegister>), kThreads, 0};
+  if (vec16) *out = {reinterpret_cast<const void*>(combine_kernel<true, kModeRegister, kProfile>), kThreads, 0};
+  else *out = {reinterpret_cast<const void*>(combine_kernel<false, kModeRegister, kProfile>), kThreads, 0};
   return cudaSuccess;
+}
+cudaError_t pick_combine(bool vec16, int fanout, bool mailbox, CombineVariant* out, bool profile = false) {
+  return profile ? pick_combine_of<true>(vec16, fanout, mailbox, out) : pick_combine_of<false>(vec16, fanout, mailbox, out);
 }
 
 }  // namespace
@@ -902,14 +977,21 @@ cudaError_t combine_max_ctas(bool vec16, int fanout, int* ctas) {
   return cudaSuccess;
 }
 
-bool combine_can_mailbox(bool vec16, int fanout, int world) { return vec16 && fanout <= kPeerBatch && world > 1; }
+bool combine_can_mailbox(bool vec16, int fanout, int world, long long row_bytes) {
+  // (A row travels as at most kPushStages pieces inside one round of a pusher.)
+  return vec16 && fanout <= kPeerBatch && world > 1 && row_bytes <= static_cast<long long>(kPushStages) * kPushStageBytes;
+}
 
 cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout, int world,
-                           bool mailbox, bool cooperative, cudaStream_t stream) {
+                           int hidden, bool mailbox, bool cooperative, cudaStream_t stream) {
   void* params[] = {const_cast<CombineArgs*>(&args)};
   CombineVariant variant;
-  cudaError_t err = pick_combine(vec16, fanout, mailbox && combine_can_mailbox(vec16, fanout, world), &variant);
+  const long long row_bytes = static_cast<long long>(hidden) * 2;
+  cudaError_t err = pick_combine(vec16, fanout, mailbox && combine_can_mailbox(vec16, fanout, world, row_bytes), &variant,
+                                 args.op[0].profile != nullptr);
   if (err != cudaSuccess) return err;
+  if (variant.threads == kMailThreads && variant.dynamic_smem == kMailSmemBytes && ctas_per_rank < 2)
+    ctas_per_rank = 2;                      // one CTA pushes, one reduces
   const dim3 grid(ctas_per_rank, ranks, 1), block(variant.threads, 1, 1);
   if (!cooperative) return cudaLaunchKernel(variant.kernel, grid, block, params, variant.dynamic_smem, stream);
   return cudaLaunchCooperativeKernel(variant.kernel, grid, block, params, variant.dynamic_smem, stream);

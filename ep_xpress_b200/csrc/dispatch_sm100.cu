@@ -70,7 +70,7 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
   return __ffsll(static_cast<long long>(mask)) - 1;
 }
 
-template <typename IdT, bool kVec16>
+template <typename IdT, bool kVec16, bool kProfile>
 __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_base) {
   const RankCtx& c = *op.ctx;
   const int W = c.world, self = c.rank, H = c.hidden, K = c.topk, E = c.num_experts;
@@ -96,7 +96,9 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   __shared__ int s_last;
   __shared__ unsigned long long s_mfull[kMovers * kMoveStages];
 
-  profile_stamp(op.profile, 0);
+  Profiler<kProfile> prof(op.profile);
+  prof.stamp(0);
+  if (prof.on() && threadIdx.x == 0) prof.record[kProfMode] = kVec16 ? 2 : 1;
   const unsigned g = ld_volatile_u32(&hdr->disp_epoch) + 1;
   // Generations never wrap (the reference stops at 2^31 too, ep_xpress/csrc/host_sm.cu:563-567):
   // every CTA reads the same header word, so all of them leave here together.
@@ -128,6 +130,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     st_relaxed_sys(a + 1, tagged(g, static_cast<unsigned>(op.slot_capacity)));
     st_relaxed_sys(a + 2, tagged(g, static_cast<unsigned>(op.capacity)));
     st_relaxed_sys(a + 3, tagged(g, static_cast<unsigned>(op.identity)));
+    if (tid == 0) prof.first(kProfFirstPublish);
   }
 
   // ---- 1. route ------------------------------------------------------------
@@ -223,9 +226,9 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     __syncthreads();
   }
 
-  profile_stamp(op.profile, 1);
+  prof.stamp(1);
   if (!solo && !rank_barrier(c, &hdr->bar_count, gridDim.x, kPhaseDispatch)) return;
-  profile_stamp(op.profile, 2);
+  prof.stamp(2);
   debug_delay(c, 1);
 
   // ---- 2. publish my count row ----------------------------------------------
@@ -268,15 +271,22 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   unsigned long long b_mask[kMoveStages];
   unsigned mparity = 0;        // bit i: phase parity of stage i's barrier
   bool more = mover;
+  // Towards the end of the batch a mover takes one piece at a time: a full claim is tens of
+  // microseconds of link time, which the last claimers would spend alone.
+  const long long tail_items = static_cast<long long>(gridDim.x) * kMovers * kMoveStages;
   auto claim_and_load = [&]() {
-    unsigned base = 0;
-    if (lane == 0) base = atomicAdd(&hdr->work_next, claim);
+    unsigned base = 0, taken = claim;
+    if (lane == 0) {
+      if (claim > 1 && move_items - static_cast<long long>(ld_volatile_u32(&hdr->work_next)) < tail_items) taken = 1;
+      base = atomicAdd(&hdr->work_next, taken);
+    }
     base = __shfl_sync(0xffffffffu, base, 0);
+    taken = __shfl_sync(0xffffffffu, taken, 0);
 #pragma unroll
     for (int i = 0; i < kMoveStages; ++i) {
       const long long item = static_cast<long long>(base) + i;
       b_mask[i] = 0ull;
-      if (i < static_cast<int>(claim) && item < move_items) {
+      if (i < static_cast<int>(taken) && item < move_items) {
         const int t = static_cast<int>(item / pieces);
         const long long b0 = (item - static_cast<long long>(t) * pieces) * piece_bytes;
         b_tok[i] = t;
@@ -291,7 +301,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
         }
       }
     }
-    more = static_cast<long long>(base) + claim < move_items;
+    more = static_cast<long long>(base) + taken < move_items;
   };
   if (mover) claim_and_load();
 
@@ -305,14 +315,15 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       const unsigned tag = tag_of(ld_acquire_sys(my_cnt + i));
       ahead = static_cast<int>(tag - g) > 0;
       return tag == g || ahead;
-    });
+    }, prof.poll_counter());
     if (ok && ahead) {
       report_error(c, kIdentityMismatch, kPhaseDispatch, 7, static_cast<unsigned>(i / W));
       ok = false;
     }
   }
   for (int i = tid; i < W * 4 && ok; i += kThreads)
-    ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(my_addr + i)) == g; });
+    ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(my_addr + i)) == g; },
+                      prof.poll_counter());
   if (!__syncthreads_and(ok)) {
     // Giving up: the loads already issued still target this CTA's shared memory, so they are
     // waited for (bounded) before the CTA may exit.
@@ -323,7 +334,8 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     }
     return;
   }
-  profile_stamp(op.profile, 3);
+  prof.stamp(3);
+  if (tid == 0 && W > 1) prof.first(kProfFirstReceive);
   debug_delay(c, 2);
 
   if (tid < W) {
@@ -388,6 +400,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
                                   dest_rows[static_cast<long long>(t) * fan + j];
             bulk_store_from_smem(s_planes[d].hidden + row * row_bytes + b_b0[i],
                                  ring + static_cast<size_t>(i) * kMoveStageBytes, static_cast<unsigned>(b_bytes[i]));
+            prof.moved(b_b0[i] == 0 ? 1 : 0, static_cast<unsigned long long>(b_bytes[i]));
           }
         }
         bulk_commit_group();
@@ -492,6 +505,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
           const int d2 = __shfl_sync(0xffffffffu, d, jj);
           const long long r2 = __shfl_sync(0xffffffffu, row, jj);
           if (r2 < 0) continue;
+          if (lane == 0 && batch == b0) prof.moved(seg == 0 ? 1 : 0, static_cast<unsigned long long>(b1 - b0));
           char* dst = s_planes[d2].hidden + r2 * row_bytes;
 #pragma unroll
           for (int u = 0; u < kUnroll; ++u) {
@@ -539,7 +553,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   const int valid = s_ok[self] ? s_total[self] : 0;
   debug_delay(c, 3);
   __syncthreads();
-  profile_stamp(op.profile, 4);
+  prof.stamp(4);
   if (tid == 0) {
     // This CTA's peer stores are performed system-wide before it arrives (a group of one rank
     // has no peers: device scope is enough there).
@@ -554,6 +568,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       unsigned long long* flag = reinterpret_cast<unsigned long long*>(s_heap[tid] + cl.done) +
                                  static_cast<size_t>(par) * W + self;
       st_release_sys(flag, tagged(g, 1u));
+      if (tid == 0) prof.first(kProfFirstPublish);
     }
     if (tid == 0) {
       misc[kValidCount] = valid;
@@ -566,7 +581,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     }
   }
 
-  profile_stamp(op.profile, 5);
+  prof.stamp(5);
   // ---- 6. receive side -------------------------------------------------------------
   // Rows in [valid, previous valid) held data of the slot's previous operation.
   if (dirty_prev > valid) {
@@ -593,27 +608,34 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       }
     }
   }
-  profile_stamp(op.profile, 6);
+  prof.stamp(6);
   ok = true;
   // (Not for this rank's own rows: the launch itself completes only when they are written.)
   if (tid < W && tid != self && s_ok[self] && value_of(ld_relaxed_sys(my_cnt + tid * W + self)) > 0)
-    ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return tag_of(ld_acquire_sys(my_done + tid)) == g; });
+    ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return tag_of(ld_acquire_sys(my_done + tid)) == g; },
+                      prof.poll_counter());
   __syncthreads_and(ok);
-  profile_stamp(op.profile, 7);
+  prof.stamp(7);
+  prof.flush(&hdr->status);
   sample_end(op.samples, sample);
 }
 
-template <typename IdT, bool kVec16>
+template <typename IdT, bool kVec16, bool kProfile>
 __global__ void __launch_bounds__(kThreads, 1) dispatch_kernel(const __grid_constant__ DispatchArgs args) {
   extern __shared__ __align__(128) int tile_base[];
-  dispatch_body<IdT, kVec16>(args.op[blockIdx.y], tile_base);
+  dispatch_body<IdT, kVec16, kProfile>(args.op[blockIdx.y], tile_base);
 }
 
 using DispatchKernel = void (*)(const DispatchArgs);
 
-DispatchKernel pick_kernel(bool ids64, bool vec16) {
-  if (ids64) return vec16 ? dispatch_kernel<long long, true> : dispatch_kernel<long long, false>;
-  return vec16 ? dispatch_kernel<int, true> : dispatch_kernel<int, false>;
+// The profiling specialisations are separate kernels: an ordinary launch carries no timers.
+template <bool kProfile>
+DispatchKernel pick_kernel_of(bool ids64, bool vec16) {
+  if (ids64) return vec16 ? dispatch_kernel<long long, true, kProfile> : dispatch_kernel<long long, false, kProfile>;
+  return vec16 ? dispatch_kernel<int, true, kProfile> : dispatch_kernel<int, false, kProfile>;
+}
+DispatchKernel pick_kernel(bool ids64, bool vec16, bool profile = false) {
+  return profile ? pick_kernel_of<true>(ids64, vec16) : pick_kernel_of<false>(ids64, vec16);
 }
 
 }  // namespace
@@ -645,7 +667,7 @@ cudaError_t dispatch_max_ctas(bool ids64, bool vec16, size_t dynamic_smem, int* 
 
 cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_rank, bool ids64, bool vec16,
                             size_t dynamic_smem, bool cooperative, cudaStream_t stream) {
-  DispatchKernel kernel = pick_kernel(ids64, vec16);
+  DispatchKernel kernel = pick_kernel(ids64, vec16, args.op[0].profile != nullptr);
   if (dynamic_smem > 48 * 1024) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            static_cast<int>(dynamic_smem));

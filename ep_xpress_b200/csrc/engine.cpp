@@ -115,7 +115,7 @@ class Engine {
   void set_combine_streaming(int mode) { streaming_ = mode; }
   // Whether the mailbox combine protocol applies to this group's shape (16-byte rows, fan-out
   // up to eight, two or more ranks); tensors that are not 16-byte aligned still fall back.
-  bool can_mailbox() const { return combine_can_mailbox(hidden_ % 8 == 0, route_fanout(topk_, world_), world_); }
+  bool can_mailbox() const { return combine_can_mailbox(hidden_ % 8 == 0, route_fanout(topk_, world_), world_, static_cast<long long>(hidden_) * 2); }
   int sm_count() const { return sms_; }
   std::vector<int> experts_per_rank() const { return experts_per_rank_; }
   size_t ctrl_bytes() const { return ctrl_layout(world_).bytes; }
@@ -295,7 +295,7 @@ class Engine {
       args.op[i].samples = ring; args.op[i].sample_capacity = capacity;
     });
     const int fanout = route_fanout(topk_, world_);
-    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, fanout, world_, mailbox < 0 ? streaming_ != 0 : mailbox != 0, cooperative_,
+    cuda_check(launch_combine(args, static_cast<int>(n), ctas, vec16, fanout, world_, hidden_, mailbox < 0 ? streaming_ != 0 : mailbox != 0, cooperative_,
                               stream_of(stream)), "combine launch");
   }
 

@@ -109,7 +109,8 @@ static __device__ __noinline__ void report_error(const RankCtx& c, int code, uns
 // raised or a peer published an error. Returns true only when `ready()` held.
 // Never traps, never spins forever: on failure the caller unwinds and returns.
 template <typename Ready>
-__device__ __forceinline__ bool bounded_wait(const RankCtx& c, unsigned phase, unsigned where, Ready ready) {
+__device__ __forceinline__ bool bounded_wait(const RankCtx& c, unsigned phase, unsigned where, Ready ready,
+                                             unsigned long long* polls = nullptr) {
   if (ready()) return true;
   CtrlHeader* h = header_of(c.heap[c.rank]);
   const CtrlLayout l = ctrl_layout(c.world);
@@ -117,7 +118,10 @@ __device__ __forceinline__ bool bounded_wait(const RankCtx& c, unsigned phase, u
   const unsigned long long start = global_timer_ns();
   unsigned spins = 0;
   while (true) {
-    if (ready()) return true;
+    if (ready()) {
+      if (polls != nullptr) *polls += spins;
+      return true;
+    }
     if ((++spins & 63u) == 0) {
       if (ld_volatile_i32(&h->abort_flag) != 0) return false;
       for (int p = 0; p < c.world; ++p) {
@@ -210,11 +214,50 @@ __device__ __forceinline__ void debug_delay(const RankCtx& c, unsigned site) {
   __syncthreads();
 }
 
-// Opt-in phase timestamp of one CTA (thread 0 only); a null buffer costs one predicate.
-__device__ __forceinline__ void profile_stamp(unsigned long long* profile, int index) {
-  if (profile != nullptr && threadIdx.x == 0)
-    profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + index] = global_timer_ns();
-}
+// Profile record of this CTA (kProfileStamps words) in a profiling launch. The transport
+// kernels are templates on `kProfile`: their ordinary specialisation contains none of this.
+template <bool kProfile>
+struct Profiler {
+  unsigned long long* record;
+  unsigned long long polls;     // per thread, flushed at the end
+  unsigned long long rows, bytes;
+  __device__ __forceinline__ explicit Profiler(unsigned long long* base)
+      : record(kProfile && base != nullptr ? base + static_cast<size_t>(blockIdx.x) * kProfileStamps : nullptr),
+        polls(0), rows(0), bytes(0) {}
+  __device__ __forceinline__ bool on() const { return kProfile && record != nullptr; }
+  // Phase stamp by thread 0 of the CTA.
+  __device__ __forceinline__ void stamp(int index) const {
+    if (!kProfile) return;
+    if (record != nullptr && threadIdx.x == 0) {
+      record[index] = global_timer_ns();
+      record[kProfCompletion] = static_cast<unsigned long long>(index);
+    }
+  }
+  __device__ __forceinline__ unsigned long long* poll_counter() { return on() ? &polls : nullptr; }
+  __device__ __forceinline__ void moved(unsigned long long n_rows, unsigned long long n_bytes) {
+    if (!kProfile) return;
+    rows += n_rows;
+    bytes += n_bytes;
+  }
+  // First time anything happened (any thread): keeps the earliest non-zero value.
+  __device__ __forceinline__ void first(int word) const {
+    if (!kProfile) return;
+    if (record != nullptr) atomicCAS(record + word, 0ull, global_timer_ns());
+  }
+  __device__ __forceinline__ void count(int word, unsigned long long n) const {
+    if (!kProfile) return;
+    if (record != nullptr && n != 0) atomicAdd(record + word, n);
+  }
+  // Called by every thread on its way out.
+  __device__ __forceinline__ void flush(const int* status) const {
+    if (!kProfile) return;
+    if (record == nullptr) return;
+    if (rows) atomicAdd(record + kProfRows, rows);
+    if (bytes) atomicAdd(record + kProfBytes, bytes);
+    if (polls) atomicAdd(record + kProfPolls, polls);
+    if (threadIdx.x == 0) record[kProfStatus] = static_cast<unsigned long long>(ld_volatile_i32(status));
+  }
+};
 
 // Sample ring of graph-replayed operations (layout: kSampleWords in epx_layout.h). Returns the
 // sample index of the operation with `generation`, or ~0u when nothing is to be recorded;

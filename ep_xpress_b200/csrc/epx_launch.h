@@ -27,11 +27,11 @@ cudaError_t launch_dispatch(const DispatchArgs& args, int ranks, int ctas_per_ra
 // `mailbox`: push and reduce run side by side in every CTA (pusher warps move rows with bulk
 // copies and release one arrival word per row; the other warps reduce a token as soon as the
 // rows it is owed are in) instead of one after the other. It applies to 16-byte rows, fan-outs
-// up to eight and groups of two or more ranks (`combine_can_mailbox`); elsewhere, and when not
+// up to eight, rows of up to 112 KiB and groups of two or more ranks (`combine_can_mailbox`); elsewhere, and when not
 // asked for, the sequential protocol runs. All ranks of a group must choose the same protocol.
-bool combine_can_mailbox(bool vec16, int fanout, int world);
+bool combine_can_mailbox(bool vec16, int fanout, int world, long long row_bytes);
 cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank, bool vec16, int fanout, int world,
-                           bool mailbox, bool cooperative, cudaStream_t stream);
+                           int hidden, bool mailbox, bool cooperative, cudaStream_t stream);
 
 // Synthetic expert used by the validation harness and the communication
 // benchmark: partial[row] = bf16(hidden[row] * sum_k weights[row,k] * factor[local_ids[row,k]])

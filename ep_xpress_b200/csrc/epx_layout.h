@@ -29,7 +29,7 @@ constexpr int kThreads = 512;        // threads per CTA of the transport kernels
 constexpr int kRouteTile = kThreads; // tokens routed per CTA iteration
 constexpr int kSlotAlign = 256;      // every sub-buffer starts on a 256-byte boundary
 constexpr int kMaxRouteTiles = 8192; // bound of the per-CTA prefix table
-constexpr int kProfileStamps = 8;    // phase timestamps one CTA records when profiling
+constexpr int kProfileStamps = 24;   // words of one CTA's profile record: 8 phase stamps, then ProfileWord
 constexpr int kFlagLine = 128;       // arrival words that follow every staging row (one u32 per row segment)
 constexpr int kMaxRowSegments = kFlagLine / 4;
 
@@ -120,6 +120,22 @@ struct SlotLayout {
   size_t misc;       // i32   [64]  valid_count, dirty_rows, ...
   size_t output;     // bf16  [tokens, hidden]     combine result (workspaces)
   size_t bytes;
+};
+
+// Words 8.. of a CTA's profile record (profiling launches only). Words 0..7 are phase stamps
+// on the GPU's global timer (combine: 4..7 hold pipeline cycle counts instead).
+enum ProfileWord : int {
+  kProfRows = 8,          // rows this CTA stored to destination planes (dispatch) or pushed (combine)
+  kProfBytes = 9,         // payload bytes of those rows
+  kProfItems = 10,        // combine: (token, row segment) items this CTA's producers issued
+  kProfPolls = 11,        // iterations of bounded waits on words that peers write
+  kProfFirstPublish = 12, // time of this CTA's first publication to a peer (0: none)
+  kProfFirstReceive = 13, // time this CTA first saw data or a word from a peer (0: none)
+  kProfStatus = 14,       // the rank's status word when the CTA left
+  kProfCompletion = 15,   // index of the last phase stamp the CTA wrote
+  kProfMode = 16,         // combine: 1 + protocol (0 register, 1 bulk, 2 mailbox); dispatch: 1 register path, 2 bulk-copy movers
+  kProfPushWait = 17,     // combine, mailbox: ns the CTA's pushers spent waiting for their copies (loads landed, stores completed)
+  kProfArrivalWait = 18,  // combine, mailbox: ns producer 0 spent waiting for arrival words of peers' rows
 };
 
 enum MiscWord : int { kValidCount = 0, kDirtyRows = 1, kSendTotal = 2 };

@@ -5,6 +5,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <optional>
+
 #include "moe_gemm.h"
 
 namespace py = pybind11;
@@ -25,8 +27,12 @@ void expect(const at::Tensor& t, at::ScalarType type, const char* name) {
 void moe_forward(const at::Tensor& hidden, const at::Tensor& local_ids, const at::Tensor& weights,
                  const at::Tensor& valid_count, const at::Tensor& w13, const at::Tensor& w2, at::Tensor& partial,
                  at::Tensor& sorted_row, at::Tensor& sorted_scale, at::Tensor& entry_pos, at::Tensor& tile_expert,
-                 at::Tensor& counters, at::Tensor& error_flag, at::Tensor& sorted_x, at::Tensor& act, at::Tensor& y,
-                 int64_t stream_handle, bool pair) {
+                 at::Tensor& counters, at::Tensor& error_flag, const std::optional<at::Tensor>& sorted_x_opt,
+                 at::Tensor& act, at::Tensor& y, int64_t stream_handle, bool pair) {
+  // Without a `sorted_x` workspace the first GEMM gathers its activation rows itself (TMA gather
+  // copies driven by `sorted_row`); with one, a gather kernel permutes them first.
+  const bool gathered = !sorted_x_opt.has_value();
+  at::Tensor sorted_x = gathered ? hidden : *sorted_x_opt;
   expect(hidden, at::kBFloat16, "hidden");
   expect(local_ids, at::kLong, "local_ids");
   expect(weights, at::kFloat, "weights");
@@ -40,7 +46,7 @@ void moe_forward(const at::Tensor& hidden, const at::Tensor& local_ids, const at
   expect(tile_expert, at::kInt, "tile_expert");
   expect(counters, at::kInt, "counters");
   expect(error_flag, at::kInt, "error_flag");
-  expect(sorted_x, at::kBFloat16, "sorted_x");
+  if (sorted_x_opt.has_value()) expect(*sorted_x_opt, at::kBFloat16, "sorted_x");
   expect(act, at::kBFloat16, "act");
   expect(y, at::kBFloat16, "y");
   TORCH_CHECK(hidden.dim() == 2 && local_ids.dim() == 2 && w13.dim() == 3 && w2.dim() == 3, "bad ranks");
@@ -56,8 +62,10 @@ void moe_forward(const at::Tensor& hidden, const at::Tensor& local_ids, const at
   TORCH_CHECK(sorted_rows % tile == 0 && sorted_scale.numel() == sorted_rows, "sorted buffers mismatch");
   TORCH_CHECK(entry_pos.numel() >= rows * topk && counters.numel() >= 2 && error_flag.numel() >= 1, "small buffers");
   TORCH_CHECK(tile_expert.numel() >= sorted_rows / tile, "tile_expert is too small");
-  TORCH_CHECK(sorted_x.numel() >= sorted_rows * hidden_size && y.numel() >= sorted_rows * hidden_size &&
+  TORCH_CHECK((gathered || sorted_x.numel() >= sorted_rows * hidden_size) && y.numel() >= sorted_rows * hidden_size &&
               act.numel() >= sorted_rows * inter, "workspace tensors are too small");
+  TORCH_CHECK(!gathered || (reinterpret_cast<uintptr_t>(hidden.data_ptr()) % 16 == 0 && rows > 0),
+              "gathered loads need a 16-byte aligned, non-empty activation matrix");
   c10::cuda::CUDAGuard guard(hidden.device());
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_handle);
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
@@ -67,12 +75,14 @@ void moe_forward(const at::Tensor& hidden, const at::Tensor& local_ids, const at
                          static_cast<int>(experts), sorted_rows, max_tiles, sorted_row.data_ptr<int>(),
                          sorted_scale.data_ptr<float>(), entry_pos.data_ptr<int>(), tile_expert.data_ptr<int>(),
                          counters.data_ptr<int>(), error_flag.data_ptr<int>(), tile, stream), "align");
-  check(launch_moe_gather(hidden.data_ptr(), sorted_row.data_ptr<int>(), counters.data_ptr<int>(), sorted_x.data_ptr(),
-                          sorted_rows, static_cast<int>(hidden_size), stream), "gather");
+  if (!gathered)
+    check(launch_moe_gather(hidden.data_ptr(), sorted_row.data_ptr<int>(), counters.data_ptr<int>(), sorted_x.data_ptr(),
+                            sorted_rows, static_cast<int>(hidden_size), stream), "gather");
   check(launch_moe_gemm_gate_up(sorted_x.data_ptr(), w13.data_ptr(), act.data_ptr(), counters.data_ptr<int>(),
                                 tile_expert.data_ptr<int>(), error_flag.data_ptr<int>(), sorted_rows,
                                 static_cast<int>(experts), static_cast<int>(hidden_size), static_cast<int>(inter), sms,
-                                pair, stream), "gate/up GEMM");
+                                pair, stream, gathered ? sorted_row.data_ptr<int>() : nullptr, gathered ? rows : 0),
+        "gate/up GEMM");
   check(launch_moe_gemm_down(act.data_ptr(), w2.data_ptr(), y.data_ptr(), sorted_scale.data_ptr<float>(),
                              counters.data_ptr<int>(), tile_expert.data_ptr<int>(), error_flag.data_ptr<int>(),
                              sorted_rows, static_cast<int>(experts), static_cast<int>(hidden_size),

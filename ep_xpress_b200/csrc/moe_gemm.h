@@ -46,10 +46,14 @@ cudaError_t launch_moe_gather(const void* hidden, const int* sorted_row, const i
 // first, then up rows), K-major. GEMM 2: y[pos, :] = (act W2_e) * sorted_scale[pos], w2 is
 // [experts, hidden, inter]. Shapes: hidden % 256 == 0, inter % 128 == 0. `pair` runs the GEMM on
 // clusters of two CTAs (tcgen05 cta_group::2, 256-row tiles: align with tile_rows = 256).
+// With `gather_rows` (= the align step's sorted_row, 16-byte aligned), `sorted_x` is the UNSORTED
+// activation matrix [gather_height, hidden]: the kernel's TMA producer gathers the rows of every
+// tile itself (four rows per copy) and no gather launch or sorted copy of the activations is needed.
 cudaError_t launch_moe_gemm_gate_up(const void* sorted_x, const void* w13, void* act, const int* counters,
                                     const int* tile_expert, int* error_flag, long long max_sorted_rows,
                                     int experts, int hidden_size, int inter_size, int sms, bool pair,
-                                    cudaStream_t stream);
+                                    cudaStream_t stream, const int* gather_rows = nullptr,
+                                    long long gather_height = 0);
 cudaError_t launch_moe_gemm_down(const void* act, const void* w2, void* y, const float* sorted_scale,
                                  const int* counters, const int* tile_expert, int* error_flag,
                                  long long max_sorted_rows, int experts, int hidden_size, int inter_size, int sms,

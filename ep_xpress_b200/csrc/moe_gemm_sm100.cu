@@ -62,6 +62,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_address(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_address(bar)) : "memory");
 }
+// Four rows of a row-major matrix (any four row indices) x one 64-column box, written to `dst`
+// as four consecutive 128-byte rows; the tensor map has a box of {64, 1}. A row index at or
+// beyond the matrix height reads zeros. No fan-out: the copy lands in this CTA only.
+__device__ __forceinline__ void tma_gather4(void* dst, const CUtensorMap* map, int x, int r0, int r1, int r2, int r3,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(smem_address(dst)), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_address(bar))
+      : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(unsigned* smem_result, unsigned columns) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                ::"r"(smem_address(smem_result)), "r"(columns) : "memory");
@@ -123,7 +134,20 @@ struct GemmParams {
   int out_columns;               // row pitch of `out` in elements
   int b_rows_per_expert;         // rows of the weight matrix that belong to one expert
   int up_row_offset;             // kMode 0: row distance between gate and up projections
+  const int* gather_rows;        // null, or [padded rows]: source row of every sorted position (-1: padding);
+                                 // the A operand is then gathered from the unsorted matrix behind map_a
+  int gather_height;             // rows of that matrix; an index at or above it reads zeros
 };
+
+// Row indices of lane `lane`'s four rows of the 128-row block that starts at `first`.
+__device__ __forceinline__ int4 gather_indices(const GemmParams& p, long long first, int lane) {
+  int4 rows = *reinterpret_cast<const int4*>(p.gather_rows + first + 4 * lane);
+  if (rows.x < 0) rows.x = p.gather_height;
+  if (rows.y < 0) rows.y = p.gather_height;
+  if (rows.z < 0) rows.z = p.gather_height;
+  if (rows.w < 0) rows.w = p.gather_height;
+  return rows;
+}
 
 // kMode 0: B tile = [128 gate rows; 128 up rows], epilogue silu(gate) * up -> 128 columns.
 // kMode 1: B tile = 256 rows, epilogue acc * row_scale -> 256 columns.
@@ -165,7 +189,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (elect_one()) {
+    if (p.gather_rows != nullptr) {
+      // Gathered A operand: the whole warp takes part, lane l fetches rows 4l..4l+3 of the tile
+      // with ONE gather copy per k-step straight from the unsorted activation matrix.
+      unsigned use = 0;
+      bool go = true;
+      for (long long tile = blockIdx.x; tile < total_tiles && go; tile += gridDim.x) {
+        const int m_tile = static_cast<int>(tile / p.n_tiles), n_tile = static_cast<int>(tile % p.n_tiles);
+        const int expert = p.tile_expert[m_tile];
+        const int b_row = expert * p.b_rows_per_expert + n_tile * kOutTile;
+        const int4 rows = gather_indices(p, static_cast<long long>(m_tile) * kTileM, lane);
+        for (int k = 0; k < p.k_steps && go; ++k, ++use) {
+          const int s = use % kGemmStages;
+          unsigned char* a_dst = smem + static_cast<size_t>(s) * kStageBytesGemm;
+          unsigned char* b_dst = a_dst + kABytes;
+          int ok = 1;
+          if (lane == 0) {
+            ok = !failed && mbar_wait(empty_bar + s, ((use / kGemmStages) & 1u) ^ 1u) ? 1 : 0;
+            if (ok) mbarrier_arrive_expect_tx(full_bar + s, kStageBytesGemm);
+            else failed = 1;
+          }
+          go = __shfl_sync(0xffffffffu, ok, 0) != 0;
+          if (!go) break;
+          tma_gather4(a_dst + lane * 512, &map_a, k * kTileK, rows.x, rows.y, rows.z, rows.w, full_bar + s);
+          if (lane == 0) {
+            if (kMode == 0) {
+              tma_load_2d(b_dst, &map_b, k * kTileK, b_row, full_bar + s);
+              tma_load_2d(b_dst + kBBytes / 2, &map_b, k * kTileK, b_row + p.up_row_offset, full_bar + s);
+            } else {
+              tma_load_2d(b_dst, &map_b, k * kTileK, b_row, full_bar + s);
+            }
+          }
+        }
+      }
+    } else if (elect_one()) {
       unsigned use = 0;
       for (long long tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
         const int m_tile = static_cast<int>(tile / p.n_tiles), n_tile = static_cast<int>(tile % p.n_tiles);
@@ -307,6 +364,13 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_address(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster) : "memory");
 }
+__device__ __forceinline__ void tma_gather4_pair(void* dst, const CUtensorMap* map, int x, int r0, int r1, int r2, int r3,
+                                                 unsigned bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2 "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(smem_address(dst)), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar_cluster) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc_pair(unsigned* smem_result, unsigned columns) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
                ::"r"(smem_address(smem_result)), "r"(columns) : "memory");
@@ -369,7 +433,33 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
-    if (elect_one()) {
+    if (p.gather_rows != nullptr) {
+      // Gathered A operand (see the single-CTA kernel): each CTA gathers its own 128 rows.
+      unsigned use = 0;
+      bool go = true;
+      for (long long tile = cluster_id; tile < total_tiles && go; tile += clusters) {
+        const int m_tile = static_cast<int>(tile / p.n_tiles), n_tile = static_cast<int>(tile % p.n_tiles);
+        const int expert = p.tile_expert[m_tile];
+        const int b_row = expert * p.b_rows_per_expert + n_tile * kOutTile +
+                          (kMode == 0 ? static_cast<int>(rank) * p.up_row_offset : static_cast<int>(rank) * (kTileN / 2));
+        const int4 rows = gather_indices(p, static_cast<long long>(m_tile) * kPairM + static_cast<long long>(rank) * kTileM, lane);
+        for (int k = 0; k < p.k_steps && go; ++k, ++use) {
+          const int s = use % kPairStages;
+          unsigned char* a_dst = smem + static_cast<size_t>(s) * kPairStageBytes;
+          const unsigned leader_full = peer_smem_address(full_bar + s, 0);
+          int ok = 1;
+          if (lane == 0) {
+            ok = !failed && mbar_wait(empty_bar + s, ((use / kPairStages) & 1u) ^ 1u) ? 1 : 0;
+            if (!ok) failed = 1;
+            else if (rank == 0) mbarrier_arrive_expect_tx(full_bar + s, 2 * kPairStageBytes);
+          }
+          go = __shfl_sync(0xffffffffu, ok, 0) != 0;
+          if (!go) break;
+          tma_gather4_pair(a_dst + lane * 512, &map_a, k * kTileK, rows.x, rows.y, rows.z, rows.w, leader_full);
+          if (lane == 0) tma_load_2d_pair(a_dst + kABytes, &map_b, k * kTileK, b_row, leader_full);
+        }
+      }
+    } else if (elect_one()) {
       unsigned use = 0;
       for (long long tile = cluster_id; tile < total_tiles && !failed; tile += clusters) {
         const int m_tile = static_cast<int>(tile / p.n_tiles), n_tile = static_cast<int>(tile % p.n_tiles);
@@ -638,6 +728,11 @@ cudaError_t make_map(CUtensorMap* map, const void* base, long long rows, long lo
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// Same matrix addressed one row at a time (box 1 x 64 columns): the form gather copies need.
+cudaError_t make_gather_map(CUtensorMap* map, const void* base, long long rows, long long columns) {
+  return make_map(map, base, rows, columns, 1);
+}
+
 constexpr size_t kGemmSmemBytes = static_cast<size_t>(kGemmStages) * kStageBytesGemm + 1024;
 
 template <int kMode>
@@ -706,10 +801,15 @@ cudaError_t launch_moe_gather(const void* hidden, const int* sorted_row, const i
 cudaError_t launch_moe_gemm_gate_up(const void* sorted_x, const void* w13, void* act, const int* counters,
                                     const int* tile_expert, int* error_flag, long long max_sorted_rows,
                                     int experts, int hidden_size, int inter_size, int sms, bool pair,
-                                    cudaStream_t stream) {
+                                    cudaStream_t stream, const int* gather_rows, long long gather_height) {
   if (hidden_size % kTileK || inter_size % kMoeGateUpTile) return cudaErrorInvalidValue;
+  if (gather_rows != nullptr && (gather_height <= 0 || gather_height >= (1ll << 31) ||
+                                 reinterpret_cast<uintptr_t>(gather_rows) % 16 != 0))
+    return cudaErrorInvalidValue;
   CUtensorMap map_a, map_b;
-  cudaError_t err = make_map(&map_a, sorted_x, max_sorted_rows, hidden_size, kTileM);
+  // With `gather_rows`, `sorted_x` is the UNSORTED activation matrix [gather_height, hidden].
+  cudaError_t err = gather_rows != nullptr ? make_gather_map(&map_a, sorted_x, gather_height, hidden_size)
+                                           : make_map(&map_a, sorted_x, max_sorted_rows, hidden_size, kTileM);
   if (err != cudaSuccess) return err;
   err = make_map(&map_b, w13, static_cast<long long>(experts) * 2 * inter_size, hidden_size, kTileN / 2);
   if (err != cudaSuccess) return err;
@@ -723,6 +823,8 @@ cudaError_t launch_moe_gemm_gate_up(const void* sorted_x, const void* w13, void*
   params.out_columns = inter_size;
   params.b_rows_per_expert = 2 * inter_size;
   params.up_row_offset = inter_size;
+  params.gather_rows = gather_rows;
+  params.gather_height = static_cast<int>(gather_height);
   return pair ? launch_gemm_pair<0>(map_a, map_b, params, sms, stream)
               : launch_gemm<0>(map_a, map_b, params, sms, stream);
 }

@@ -22,8 +22,14 @@ from .. import native as _native_loader
 
 
 class GroupedSwiGLU:
-    def __init__(self, w13, w2, *, max_rows, topk, max_local_pairs=None, pair_ctas=False):
+    def __init__(self, w13, w2, *, max_rows, topk, max_local_pairs=None, pair_ctas=False, gather_loads=True):
         """``max_local_pairs`` bounds the (row, slot) pairs whose expert lives on this rank.
+
+        ``gather_loads`` (default): the first GEMM's TMA producer gathers the activation rows of
+        every expert tile straight from the dispatch batch (four rows per gather copy), so no
+        expert-sorted copy of the activations exists; ``False`` keeps the separate gather kernel
+        and its ``[sorted rows, hidden]`` workspace.
+
 
         The default is the worst case (every slot of every row is local). A tighter,
         CPU-known bound saves workspace; exceeding it is reported by :meth:`check`,
@@ -55,10 +61,12 @@ class GroupedSwiGLU:
         self.tile_expert = torch.zeros(sorted_rows // tile, dtype=torch.int32, device=device)
         self.counters = torch.zeros(2, dtype=torch.int32, device=device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=device)
-        self.sorted_x = torch.empty((sorted_rows, hidden), dtype=torch.bfloat16, device=device)
+        self.gather_loads = bool(gather_loads)
+        self.sorted_x = None if self.gather_loads else torch.empty((sorted_rows, hidden), dtype=torch.bfloat16,
+                                                                   device=device)
         self.act = torch.empty((sorted_rows, inter), dtype=torch.bfloat16, device=device)
         self.y = torch.empty((sorted_rows, hidden), dtype=torch.bfloat16, device=device)
-        self.kernel_launches_per_forward = 6
+        self.kernel_launches_per_forward = 5 if self.gather_loads else 6
 
     def forward(self, hidden, local_ids, weights, valid_count, out=None, stream=None):
         rows = hidden.shape[0]
@@ -67,6 +75,8 @@ class GroupedSwiGLU:
         if out is None:
             out = torch.empty((rows, self.hidden), dtype=torch.bfloat16, device=hidden.device)
         stream = stream or torch.cuda.current_stream(hidden.device)
+        if self.gather_loads and (rows == 0 or hidden.data_ptr() % 16):
+            raise ValueError("gathered loads need a non-empty, 16-byte aligned activation matrix")
         self.native.moe_forward(hidden, local_ids, weights, valid_count, self.w13, self.w2, out, self.sorted_row,
                                 self.sorted_scale, self.entry_pos, self.tile_expert, self.counters, self.error_flag,
                                 self.sorted_x, self.act, self.y, stream.cuda_stream, self.pair_ctas)

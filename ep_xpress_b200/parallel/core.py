@@ -191,10 +191,12 @@ class TransportCore:
         return max(1, min(budget, wanted))
 
     def pick_combine_ctas(self, tokens: int, capacity: int, budget: Optional[int] = None) -> int:
-        """CTAs per rank of a combine: a CTA pushes about six received rows per round trip and
-        reduces four (token, row segment) items at a time."""
+        """CTAs per rank of a combine. Under the mailbox protocol 7/16 of them (at most 64) only
+        push - fifteen received rows per round trip each - and the others reduce four (token, row
+        segment) items at a time; small batches get enough CTAs for one round trip to move
+        everything, and never fewer than two (one pushes, one reduces)."""
         budget = self.max_ctas if budget is None else max(1, min(budget, self.max_ctas))
-        wanted = max(-(-max(capacity, 1) // 6), max(tokens, 1))
+        wanted = max(2, -(-max(capacity, 1) // 6), max(tokens, 1))
         return max(1, min(budget, wanted))
 
     def dispatch(self, slot: Slot, xs, ids, weights, capacities, *, identity=0, ctas=None, stream=None,

@@ -190,7 +190,7 @@ def run_graph(ep, rank, world, args):
             ep.prepare_graph_replay(stream)
             bucket["graph"].replay()
         operations += 1
-        if iteration % args.check_every == 0 or iteration == args.replays:
+        if iteration % args.check_every == 0 or iteration <= 40 or iteration == args.replays:
             stream.synchronize()
             check_batch(bucket["batch"], plan, rows, rank)
             assert torch.equal(bits(bucket["out"]), bits(want[rank])), f"replay {iteration} (bucket {b}) differs"
@@ -260,7 +260,12 @@ def run_stagger(ep, rank, world, args):
     stream = torch.cuda.current_stream()
     results = []
     for iteration in range(32):
-        xs, ids, ws = group_inputs("uniform" if iteration % 2 else "mixed", world, tokens, hidden, topk, iteration)
+        if iteration % 2:
+            routes = [workloads.uniform_routing(tokens, world * 4, topk, seed=iteration, rank=r) for r in range(world)]
+            ids, ws = [i for i, _ in routes], [w for _, w in routes]
+            xs = [workloads.marker_payload(tokens, hidden, rank=r, iteration=iteration) for r in range(world)]
+        else:
+            xs, ids, ws = group_inputs("mixed", world, tokens, hidden, topk, iteration)
         _, _, want = expected(xs, ids, ws, emap, world, topk, hidden, factors)
         x, i, w = xs[rank].cuda(), ids[rank].cuda(), ws[rank].cuda()
         if iteration % world == rank:
@@ -351,7 +356,8 @@ def run_errors(ep, rank, world, args):
 
 
 def run_profile(ep, rank, world, args):
-    """Bounded operation profile: per-CTA phase stamps, dropped operations, single readback."""
+    """Bounded operation profile: per-CTA phase stamps and counters, dropped operations, single readback."""
+    from ep_xpress_b200.utils.profile import check_invariants
     hidden, topk, tokens = args.hidden, 4, args.tokens
     stream = torch.cuda.current_stream()
     try:
@@ -379,6 +385,11 @@ def run_profile(ep, rank, world, args):
         assert names[0] == "start" and op["phases"]["start"]["first_ns"] == 0
         lasts = [op["phases"][n]["last_ns"] for n in names]
         assert lasts == sorted(lasts), (op["kind"], lasts)      # phases are reached in order
+        check_invariants(op, row_bytes=hidden * 2)               # disjoint phases sum to elapsed, bytes = rows x row
+        assert op["protocol"] in ("bulk", "mailbox") and op["polls"] >= 0
+        assert op["rows"] > 0 or (op["kind"] == "combine" and world == 1)     # a lone rank pushes nothing
+        if world > 1:
+            assert op["first_publish_ns"] is not None and op["first_receive_ns"] is not None
     stats = ep.stats()
     assert stats["status"] == 0 and stats["dispatch_epoch"] == 3 and stats["combine_epoch"] == 3
     try:

@@ -64,9 +64,10 @@ def test_launch_width_follows_items_per_cta():
     assert core.pick_ctas(8) == 8 and core.pick_ctas(128) == 128
     core.hidden = 16384                       # rows of 32 KiB move as three pieces
     assert core.pick_ctas(8) == 24
-    # combine: six received rows per CTA and round trip, at least one CTA per token
+    # combine: six received rows per CTA, at least one CTA per token and two CTAs in all
     assert core.pick_combine_ctas(128, 1024) == 148 and core.pick_combine_ctas(1, 8) == 2
     assert core.pick_combine_ctas(16, 16) == 16 and core.pick_combine_ctas(4096, 32768, budget=100) == 100
+    assert core.pick_combine_ctas(1, 1) == 2 and core.pick_combine_ctas(8, 64) == 11
 
 
 def test_load_refuses_a_binary_built_from_other_sources(monkeypatch):

@@ -51,8 +51,9 @@ def test_reverse_order_handles():
 @pytest.mark.multigpu
 @pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
 def test_cuda_graph_replay_with_changing_routes():
-    """1000 replays over four captured buckets (one leaves a rank empty), every replay checked."""
-    launch("graph", min(gpu_count(), 4), "--replays", "1000", timeout=900)
+    """1000 replays over four captured buckets (one leaves a rank empty); the first 40 replays and
+    every fourth one after them are checked against the oracle."""
+    launch("graph", min(gpu_count(), 4), "--replays", "1000", "--check-every", "4", timeout=900)
 
 
 @pytest.mark.gpu

@@ -97,6 +97,39 @@ def test_operation_profile_decodes_stamps_and_counts_drops(profiled_context):
     assert combine["cycles"]["consumer_wait_cycles"] == 11 and combine["cycles"]["producer_other_cycles"] == 44
 
 
+def test_wide_profile_records_give_disjoint_phases_that_sum_to_elapsed():
+    """24-word records: per-CTA phases between consecutive stamps, counters, milestones, invariants."""
+    record = {"kind": "dispatch", "operation": 3, "tag": None, "label": None, "tokens": 8, "capacity": 16, "ctas": 2}
+    stamps = torch.zeros((2, 24), dtype=torch.int64)
+    stamps[0, :8] = torch.tensor([1000, 1100, 1200, 1300, 1900, 1950, 1960, 2000])
+    stamps[1, :8] = torch.tensor([1010, 1020, 1210, 1310, 1800, 1900, 1900, 2040])
+    stamps[:, profile.WORDS["rows"]] = torch.tensor([5, 7])
+    stamps[:, profile.WORDS["bytes"]] = torch.tensor([5 * 512, 7 * 512])
+    stamps[:, profile.WORDS["polls"]] = torch.tensor([40, 2])
+    stamps[0, profile.WORDS["first_publish"]] = 1005
+    stamps[:, profile.WORDS["first_receive"]] = torch.tensor([1290, 1305])
+    stamps[:, profile.WORDS["completion"]] = 7
+    stamps[:, profile.WORDS["mode"]] = 2
+    entry = profile.summarize(record, stamps)
+    assert entry["protocol"] == "bulk" and entry["rows"] == 12 and entry["bytes"] == 12 * 512 and entry["polls"] == 42
+    assert entry["first_publish_ns"] == 5 and entry["first_receive_ns"] == 290
+    assert entry["cta_phase_ns"]["payload"] == [600, 490] and entry["cta_elapsed_ns"] == [1000, 1030]
+    assert list(entry["cta_phase_ns"]) == list(profile.DISPATCH_INTERVALS)
+    profile.check_invariants(entry, row_bytes=512)
+    stamps[1, profile.WORDS["completion"]] = 4                       # a CTA that never finished
+    with pytest.raises(AssertionError):
+        profile.check_invariants(profile.summarize(record, stamps))
+    mailbox = {"kind": "combine", "operation": 3, "tag": None, "label": None, "tokens": 8, "capacity": 16, "ctas": 1}
+    stamps = torch.zeros((1, 24), dtype=torch.int64)
+    stamps[0, :4] = torch.tensor([500, 0, 900, 950])                 # this CTA's pusher found no row
+    stamps[0, profile.WORDS["completion"]] = 3
+    stamps[0, profile.WORDS["mode"]] = 3
+    entry = profile.summarize(mailbox, stamps)
+    assert entry["protocol"] == "mailbox" and entry["cta_phase_ns"]["retire"] == [50]
+    assert sum(v[0] for v in entry["cta_phase_ns"].values()) == entry["cta_elapsed_ns"][0] == 450
+    profile.check_invariants(entry)
+
+
 def test_operation_profile_budget_and_arguments(profiled_context):
     with pytest.raises(ValueError, match="64 MiB budget"):
         profile.OperationProfile(profiled_context, max_operations=(64 << 20) // (4 * 8 * 8) + 1)
