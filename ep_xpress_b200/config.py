@@ -207,7 +207,8 @@ class Config:
         _check_world(world_size)
         w = world_size
         words = 2 * w * w + 2 * w * 4 + 2 * w + w + 2 * w
-        return _round_up(_CTRL_HEADER_BYTES + words * 8 + w * 4, 4096)
+        hand = _round_up(_CTRL_HEADER_BYTES + words * 8 + w * 4, 256)       # hand-over slots of the push CTAs
+        return _round_up(hand + 64 * (64 + 8 * 4 * 16), 4096)
 
     def nvlink_slot_bytes(self, world_size, capacity=None, tokens=None) -> int:
         """Bytes of one operation slot: receive planes, partial plane and route state."""

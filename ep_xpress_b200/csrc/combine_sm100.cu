@@ -221,13 +221,14 @@ constexpr int kSegMaxBytes = 16384;               // largest row segment of one 
 // arrival words waits for every store the SM has in flight.
 //
 // That fence is the price of a release at system scope: it does not complete while its SM has
-// peer stores in flight and holds up the SM's next stores meanwhile. Measured at 2 GPUs, 4096
-// tokens (58 MB pushed per rank): pushers done after 113 us with the fence, 92 us when the words
-// are stored right after the copies completed without a fence (not kept: the copies are then
-// complete at their owner, but nothing in the PTX memory model makes a relaxed store a release);
-// moving the fence to a second warp of the push CTA, to a warp of a reduce CTA or to a CTA of
-// its own changed nothing or made it worse (the fence stalls whichever SM runs it, and a busy
-// SM's fence is as slow as the pusher's own).
+// peer stores in flight and holds up the SM's next stores meanwhile (measured at 2 GPUs, 4096
+// tokens: pushers done after 113 us with a fence per round, 92 us without). Large batches
+// therefore hand every completed round to a HERALD warp on an SM that stores nothing else - a
+// few CTAs of the launch hold one herald warp per pusher - which runs the fence and stores the
+// arrival words while the pusher already moves its next round. (A herald warp inside the push
+// CTA or inside a reduce CTA does not help: the fence stalls whichever SM runs it, and a busy
+// SM's fence is as slow as the pusher's own.) Small batches, one round per pusher, keep the
+// fence in the pusher: the hand-over would only add latency.
 constexpr int kMailGroups = kMaxGroups;
 constexpr int kMailThreads = kBulkThreads;
 constexpr size_t kMailReduceSmem = kBulkSmemBytes;
@@ -238,11 +239,18 @@ static_assert(kMailSmemBytes >= kMailReduceSmem, "a reduce CTA's rings must fit 
 
 // Push CTAs of a mailbox launch of `ctas` CTAs (at least two): enough SMs to keep the link
 // busy - a pusher moves fifteen rows per round trip - and the rest reduce, which is the heavier
-// job in bytes (every pushed row is read again, plus the local rows and the output).
+// job in bytes (every pushed row is read again, plus the local rows and the output). With
+// heralds, one CTA per sixteen pushers is taken from the reducers.
 __host__ __device__ __forceinline__ int mailbox_push_ctas(int ctas) {
   const int wanted = ctas * 7 / 16;
-  return wanted < 1 ? 1 : (wanted > 64 ? 64 : wanted);
+  return wanted < 1 ? 1 : (wanted > kMaxPushCtas ? kMaxPushCtas : wanted);
 }
+constexpr int kHeraldWarpsPerCta = 16;
+__host__ __device__ __forceinline__ int mailbox_herald_ctas(int push_ctas) {
+  return (push_ctas + kHeraldWarpsPerCta - 1) / kHeraldWarpsPerCta;
+}
+// Smallest launch that has a push CTA, its herald CTA and a reduce CTA.
+constexpr int kMinHeraldLaunch = 3;
 
 // Segment size: as large as possible while every group still gets three stages of `fan`
 // contributor slots (an item's latency chain - arrival check, copy, reduce, hand-back - is
@@ -595,10 +603,16 @@ __device__ __forceinline__ void push_item(const PushArgs& p, long long item, int
 // The copies run in the SM's copy engine; the lanes only issue and wait, in lockstep, so a
 // round costs one chain of latencies (claim, look-up, load, store + acknowledgement, fence)
 // whatever the number of rows in it.
+__device__ __forceinline__ void st_release_gpu_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// `hand`: null = this warp fences and publishes its own arrival words; otherwise completed rounds
+// are posted there for the pusher's herald warp.
 template <bool kProfile>
 __device__ __forceinline__ bool mailbox_push(const PushArgs& p, const RankCtx& c, CtrlHeader* hdr, char* stages,
-                                             unsigned long long* full, unsigned epoch, int lane, int push_ctas,
-                                             Profiler<kProfile>& prof) {
+                                             unsigned long long* full, unsigned epoch, PushSlot* hand, int lane,
+                                             int push_ctas, Profiler<kProfile>& prof) {
   const int peers = p.world - 1;
   const long long blocks = (p.most + kPushBlock - 1) / kPushBlock;
   const int pieces = static_cast<int>((p.row_bytes + kPushStageBytes - 1) / kPushStageBytes);
@@ -609,6 +623,7 @@ __device__ __forceinline__ bool mailbox_push(const PushArgs& p, const RankCtx& c
   char* const stage = stages + static_cast<size_t>(lane < kPushStages ? lane : 0) * kPushStageBytes;
   unsigned long long* const bar = full + (lane < kPushStages ? lane : 0);
   unsigned parity = 0;                                  // of this lane's barrier
+  unsigned round = 0;
   bool ok = true;
   while (true) {
     unsigned base = 0, take = per_round;
@@ -655,13 +670,70 @@ __device__ __forceinline__ bool mailbox_push(const PushArgs& p, const RankCtx& c
     if (wait_begin != 0ull) prof.count(kProfPushWait, global_timer_ns() - wait_begin);
     fence_proxy_async();               // the copies wrote through the async proxy; the words below are ordinary stores
     if (!__all_sync(0xffffffffu, ok)) break;
-    __threadfence_system();
-    if (word != nullptr) {
-      st_relaxed_sys_u32(word, epoch);
-      prof.first(kProfFirstPublish);
+    if (hand == nullptr) {
+      __threadfence_system();
+      if (word != nullptr) {
+        st_relaxed_sys_u32(word, epoch);
+        prof.first(kProfFirstPublish);
+      }
+      continue;
     }
+    // The round's rows are complete at their owners: its arrival words go to the herald warp,
+    // which publishes them behind a system-scope fence while this warp already moves the next
+    // round. The pusher runs at most kPushSlotRounds rounds ahead of its herald.
+    if (lane == 0 && round >= kPushSlotRounds)
+      ok = bounded_wait(c, kPhaseCombine, 9, [&] {
+        return ld_acquire_gpu_u32(&hand->heralded) + kPushSlotRounds > round; }, prof.poll_counter());
+    if (!__all_sync(0xffffffffu, ok)) break;
+    if (lane < kPushRoundWords)
+      hand->words[round % kPushSlotRounds][lane] = reinterpret_cast<unsigned long long>(word);
+    __syncwarp();
+    if (lane == 0) st_release_gpu_u32(&hand->posted, round + 1);
+    ++round;
   }
-  return __all_sync(0xffffffffu, ok);
+  const bool fine = __all_sync(0xffffffffu, ok);
+  if (hand != nullptr && lane == 0) st_release_gpu_u32(&hand->final_rounds, round + 1);
+  return fine;
+}
+
+// The herald warp of ONE pusher, on an SM whose only stores are arrival words. Whenever the
+// pusher has posted rounds: ONE system-scope fence - cumulative over the pusher's completed
+// copies, which reached this warp through the release/acquire on `posted` - then the rounds'
+// arrival words as relaxed stores (lane l: the word of stage l). A release per word would
+// serialise a round trip to the peer per word.
+template <bool kProfile>
+__device__ __forceinline__ bool mailbox_herald(const RankCtx& c, PushSlot* slot, unsigned epoch, int lane,
+                                               Profiler<kProfile>& prof) {
+  unsigned done = 0;                                      // rounds whose words are out
+  const unsigned long long start = global_timer_ns();
+  unsigned spins = 0;
+  while (true) {
+    unsigned long long both = 0;
+    // (posted, final_rounds) in one load; a pusher that is done posts nothing more.
+    if (lane == 0) both = ld_acquire_gpu_u64(reinterpret_cast<const unsigned long long*>(&slot->posted));
+    both = __shfl_sync(0xffffffffu, both, 0);
+    const unsigned posted = static_cast<unsigned>(both), final_rounds = static_cast<unsigned>(both >> 32);
+    if (posted == done) {
+      if (final_rounds != 0 && done + 1 == final_rounds) return true;
+      if ((++spins & 63u) == 0) {
+        if (ld_volatile_i32(&header_of(c.heap[c.rank])->abort_flag) != 0) return false;
+        if (global_timer_ns() - start > c.timeout_ns) return false;
+      }
+      continue;
+    }
+    __threadfence_system();
+    for (unsigned round = done; round != posted; ++round) {
+      unsigned long long word = 0;
+      if (lane < kPushRoundWords) word = ld_relaxed_sys(&slot->words[round % kPushSlotRounds][lane]);
+      if (word != 0ull) {
+        st_relaxed_sys_u32(reinterpret_cast<unsigned*>(word), epoch);
+        prof.first(kProfFirstPublish);
+      }
+    }
+    __syncwarp();
+    done = posted;
+    if (lane == 0) st_release_gpu_u32(&slot->heralded, done);
+  }
 }
 
 enum CombineMode : int { kModeRegister = 0, kModeBulk = 1, kModeMailbox = 2 };
@@ -766,18 +838,29 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
   reduce.cta = static_cast<int>(blockIdx.x);
   reduce.ctas = static_cast<int>(gridDim.x);
   if (kMode == kModeMailbox) {
-    // ---- push CTAs and reduce CTAs side by side (a mailbox launch has >= 2 CTAs) ----
+    // ---- push CTAs, herald CTAs and reduce CTAs side by side ----
+    // (A mailbox launch has at least two CTAs; heralds are used from kMinHeraldLaunch CTAs on.)
     const int push_ctas = mailbox_push_ctas(static_cast<int>(gridDim.x));
+    const bool heralds = op.herald != 0 && static_cast<int>(gridDim.x) >= kMinHeraldLaunch + 1;
+    const int herald_ctas = heralds ? mailbox_herald_ctas(push_ctas) : 0;
+    PushSlot* const hand = reinterpret_cast<PushSlot*>(my_heap + cl.hand);
+    const int cta = static_cast<int>(blockIdx.x);
     debug_delay(c, 4);
-    if (static_cast<int>(blockIdx.x) < push_ctas) {
+    if (cta < push_ctas) {
       if (tid < 32) {
-        if (!mailbox_push<kProfile>(push, c, hdr, dynamic_smem, s_push_full, e, lane, push_ctas, prof) && lane == 0)
+        if (!mailbox_push<kProfile>(push, c, hdr, dynamic_smem, s_push_full, e, heralds ? hand + cta : nullptr, lane,
+                                    push_ctas, prof) && lane == 0)
           report_error(c, kTimeout, kPhaseCombine, 6, 0);
         if (kProfile && prof.on() && lane == 0) prof.record[1] = global_timer_ns();
       }
+    } else if (cta < push_ctas + herald_ctas) {
+      const int pusher = (cta - push_ctas) * kHeraldWarpsPerCta + (tid >> 5);
+      if ((tid >> 5) < kHeraldWarpsPerCta && pusher < push_ctas &&
+          !mailbox_herald<kProfile>(c, hand + pusher, e, lane, prof) && lane == 0)
+        report_error(c, kTimeout, kPhaseCombine, 8, 0);
     } else {
-      reduce.cta = static_cast<int>(blockIdx.x) - push_ctas;
-      reduce.ctas = static_cast<int>(gridDim.x) - push_ctas;
+      reduce.cta = cta - push_ctas - herald_ctas;
+      reduce.ctas = static_cast<int>(gridDim.x) - push_ctas - herald_ctas;
       if (!bulk_reduce<kMailGroups, true, kMailReduceSmem, kProfile>(reduce, dynamic_smem, s_full, s_empty, s_items, prof))
         report_error(c, kTimeout, kPhaseCombine, 4, 0);
     }
@@ -914,6 +997,10 @@ __device__ __forceinline__ void combine_body(const CombineOp& op, char* dynamic_
       hdr->cfin_count = 0;
       hdr->cwork_push = 0;
       hdr->cwork_reduce = 0;
+      if (kMode == kModeMailbox && op.herald != 0) {
+        PushSlot* hand = reinterpret_cast<PushSlot*>(my_heap + cl.hand);
+        for (int i = 0; i < kMaxPushCtas; ++i) { hand[i].posted = 0; hand[i].final_rounds = 0; hand[i].heralded = 0; }
+      }
       hdr->comb_epoch = e;
       __threadfence();
     }

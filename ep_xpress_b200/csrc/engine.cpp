@@ -289,6 +289,9 @@ class Engine {
     for (size_t i = 0; i < n; ++i) {
       args.op[i].segments = segments;
       args.op[i].vec16 = vec16 ? 1 : 0;
+      // Heralds pay off once the pushers run several rounds: more received rows than the push
+      // CTAs move in two rounds of fifteen. (Every rank derives the same answer from the slot.)
+      args.op[i].herald = slot_capacity[i] > 2 * 15 * 64 ? 1 : 0;
     }
     attach_profile(profile, ctas, n, [&](size_t i, unsigned long long* p) { args.op[i].profile = p; });
     attach_samples(samples, n, [&](size_t i, unsigned long long* ring, int capacity) {

@@ -77,8 +77,22 @@ struct CtrlLayout {
   size_t ready;  // u64 [W]        combine: (epoch << 32 | rows of yours I have pushed), monotone, max-updated
   size_t ident;  // u64 [2][W]     diagnostics: operation identity of every peer
   size_t perr;   // u32 [W]        error code published by a failing peer
+  size_t hand;   // PushSlot [kMaxPushCtas]  rank-local: rounds that push CTAs hand to herald warps (mailbox combine)
   size_t bytes;  // size of the whole control region
 };
+
+// One pusher's hand-over to its herald warp (rank-local: both run in the same launch).
+constexpr int kMaxPushCtas = 64;
+constexpr int kPushSlotRounds = 4;      // rounds a pusher may run ahead of its herald
+constexpr int kPushRoundWords = 16;     // arrival words of one round (one per stage lane; 0 = none)
+struct PushSlot {
+  unsigned posted;       // rounds whose rows are complete at their owners (release, gpu scope)
+  unsigned final_rounds; // 0 while the pusher runs; 1 + its number of rounds once it is done
+  unsigned heralded;     // rounds whose arrival words are out
+  unsigned reserved[13];
+  unsigned long long words[kPushSlotRounds][kPushRoundWords];   // addresses of round r's arrival words at r % kPushSlotRounds
+};
+static_assert(sizeof(PushSlot) == 64 + 8 * kPushSlotRounds * kPushRoundWords, "hand-over slot layout");
 
 EPX_HD CtrlLayout ctrl_layout(int world) {
   CtrlLayout l;
@@ -89,7 +103,8 @@ EPX_HD CtrlLayout ctrl_layout(int world) {
   l.ready = l.done + 2 * w * 8;
   l.ident = l.ready + w * 8;
   l.perr = l.ident + 2 * w * 8;
-  l.bytes = align_up(l.perr + w * 4, 4096);
+  l.hand = align_up(l.perr + w * 4, 256);
+  l.bytes = align_up(l.hand + sizeof(PushSlot) * kMaxPushCtas, 4096);
   return l;
 }
 
@@ -226,6 +241,7 @@ struct CombineOp {
   int segments;
   int vec16;
   int partial_rows;       // rows of `partial`; fewer than the received rows is an error
+  int herald;             // mailbox protocol: non-zero = arrival words are published by herald CTAs (large batches)
 };
 
 // Bounded timing record of operations that run from CUDA graphs (every replay is a new
