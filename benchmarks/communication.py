@@ -4,11 +4,15 @@
         --master-port 29500 -m benchmarks.communication --tokens 1 8 64 512 4096 --shape qwen3 --routing zipf
 
 Method (the reference's, benchmarks/communication.py:137-276, applied to the NVLink
-transport): every phase is captured ONCE as a CUDA graph on a retained workspace and
-replayed; ``--warmup`` untimed then ``--samples`` timed replays, each bracketed by CUDA
-events; route patterns rotate between samples (random, hotspot with full dedup, a third of
-the tokens dropped, or uniform / Zipf-skewed); per sample the MAXIMUM over ranks is taken,
-and the report gives median / p95 / min / max over samples. Payload volume is counted
+transport): the layer (dispatch, synthetic expert, combine) is captured ONCE as a CUDA graph
+on a retained workspace and replayed; ``--warmup`` untimed then ``--samples`` timed replays;
+route patterns rotate between samples (random, hotspot with full dedup, a third of the
+tokens dropped, or uniform / Zipf-skewed); per sample the MAXIMUM over ranks is taken, and
+the report gives median / p95 / min / max over samples. Phase times are DEVICE times from the
+library's sample ring (earliest CTA start to latest CTA end of the replayed kernel; the layer
+is first dispatch CTA to last combine CTA): timing a phase's own graph from the host with
+events measures launch latency and the skew of the ranks' hosts - tens of microseconds -
+instead of the kernel (``layer_host_us`` keeps that figure for comparison). Payload volume is counted
 logically: a (token, remote rank) pair moves ``2 * hidden`` bytes per phase. The roofline
 fraction compares the p50 with the time those bytes need over one direction of the rank's
 NVLink at the measured peer-copy bandwidth (770 GB/s, 900 nominal).
@@ -119,18 +123,20 @@ def run_tokens(ep, args, shape, tokens, rank, world, owner):
     def do_combine():
         state["out"] = ep.combine_on_stream(state["partial"], state["batch"].handle, stream=stream)
 
+    def layer():
+        do_dispatch(); do_expert(); do_combine()
+
     with torch.cuda.stream(stream):                      # eager warm-up of the workspace
         load(0)
-        do_dispatch(); do_expert(); do_combine()
+        layer()
     stream.synchronize()
+    ep.prepare_decode_profile(max_samples_per_channel=args.warmup + args.samples, stage="layer")
     ep.prepare_graph_capture()
-    graphs = []
-    for phase in (do_dispatch, do_expert, do_combine):   # one graph per phase, captured in order
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            phase()
-        graphs.append(graph)
-    samples = {"dispatch": [], "combine": [], "layer": []}
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        layer()
+    ep.start_decode_profile()
+    host_layer = []
     for step in range(args.warmup + args.samples):
         with torch.cuda.stream(stream):
             load(step)
@@ -138,21 +144,25 @@ def run_tokens(ep, args, shape, tokens, rank, world, owner):
             stream.synchronize()
             if world > 1:
                 dist.barrier()
-            marks = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
             marks[0].record(stream)
-            graphs[0].replay()
+            graph.replay()
             marks[1].record(stream)
-            graphs[1].replay()
-            marks[2].record(stream)
-            graphs[2].replay()
-            marks[3].record(stream)
         stream.synchronize()
         if step >= args.warmup:
-            samples["dispatch"].append(marks[0].elapsed_time(marks[1]) * 1e3)
-            samples["combine"].append(marks[2].elapsed_time(marks[3]) * 1e3)
-            samples["layer"].append(marks[0].elapsed_time(marks[3]) * 1e3)
+            host_layer.append(marks[0].elapsed_time(marks[1]) * 1e3)
+    ring = ep.stop_decode_profile()["stages"]
+    first = args.warmup
+    dispatch, combine = ring["dispatch"], ring["combine"]
+    assert dispatch["samples"] == combine["samples"] == args.warmup + args.samples and not dispatch["dropped_samples"]
+    samples = {"dispatch": [ns / 1e3 for ns in dispatch["elapsed_ns"][first:]],
+               "combine": [ns / 1e3 for ns in combine["elapsed_ns"][first:]],
+               "layer": [(cb + ce - db) / 1e3 for db, cb, ce in zip(dispatch["begin_ns"][first:], combine["begin_ns"][first:],
+                                                                   combine["elapsed_ns"][first:])],
+               "layer_host": host_layer}
     ep.check()
-    result = {"tokens_per_rank": tokens, "capacity": capacity, "ctas": state["batch"].handle._plan.ctas}
+    result = {"tokens_per_rank": tokens, "capacity": capacity, "ctas": state["batch"].handle._plan.ctas,
+              "combine_ctas": state["batch"].handle._plan.combine_ctas}
     for name, values in samples.items():
         result[name + "_us"] = summarize(max_over_ranks(values, world))
     mean_bytes = sum(volumes) / len(volumes)
@@ -205,8 +215,8 @@ def main():
     ep.enable_cuda_graph()
     if args.items_per_cta is not None or args.max_ctas is not None:
         ep.set_tuning(items_per_cta=args.items_per_cta, max_ctas=args.max_ctas)
-    report = {"schema": 1, "world_size": world, "shape": args.shape, **shape, "routing": args.routing,
-              "combine_streaming": args.combine_streaming, "warmup": args.warmup, "samples": args.samples, "timing": "CUDA events, max over ranks per sample",
+    report = {"schema": 2, "world_size": world, "shape": args.shape, **shape, "routing": args.routing,
+              "combine_streaming": args.combine_streaming, "warmup": args.warmup, "samples": args.samples, "timing": "device sample ring per phase (layer_host_us: CUDA events around the replay), max over ranks per sample",
               "link_gbs_measured": LINK_GBS_MEASURED, "results": []}
     for tokens in args.tokens:
         report["results"].append(run_tokens(ep, args, shape, tokens, rank, world, owner))

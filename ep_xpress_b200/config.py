@@ -206,7 +206,7 @@ class Config:
     def ctrl_bytes(self, world_size) -> int:
         _check_world(world_size)
         w = world_size
-        words = 2 * w * w + 2 * w * 4 + 2 * w + w + 2 * w
+        words = 2 * w * w + 2 * w * 8 + 2 * w + w + 2 * w
         hand = _round_up(_CTRL_HEADER_BYTES + words * 8 + w * 4, 256)       # hand-over slots of the push CTAs
         return _round_up(hand + 64 * (64 + 8 * 4 * 16), 4096)
 

@@ -24,7 +24,8 @@
 //                counts are awaited. The other warps write the translated local
 //                expert ids, the weights and the (source, token) inverse entry.
 //                Rows that are not 16-byte aligned take a register path;
-//   5. signal    the last CTA publishes "done" to every peer after a system fence;
+//   5. signal    every CTA, after a system fence, counts itself in at the destinations
+//                that got rows from this rank;
 //   6. receive   padding rows are reset, valid_count is written, and the launch
 //                ends once every sender with rows for this rank has signalled.
 // Every wait is bounded by RankCtx::timeout_ns and ends in a status code.
@@ -90,7 +91,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   const int ntiles = route_tiles(T);
 
   __shared__ int s_warp_cnt[kWarps][64];
-  __shared__ int s_send[64], s_off[64], s_total[64], s_ok[64];
+  __shared__ int s_send[64], s_off[64], s_total[64], s_ok[64], s_ctas[64];
   __shared__ char* s_heap[64];
   __shared__ PeerPlanes s_planes[64];
   __shared__ int s_last;
@@ -112,7 +113,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   unsigned long long* const my_cnt = reinterpret_cast<unsigned long long*>(my_heap + cl.cnt) +
                                      static_cast<size_t>(par) * W * W;
   unsigned long long* const my_addr = reinterpret_cast<unsigned long long*>(my_heap + cl.addr) +
-                                      static_cast<size_t>(par) * W * 4;
+                                      static_cast<size_t>(par) * W * kAddrWords;
   unsigned long long* const my_done = reinterpret_cast<unsigned long long*>(my_heap + cl.done) +
                                       static_cast<size_t>(par) * W;
   if (tid < W) s_heap[tid] = c.heap[tid];
@@ -125,11 +126,12 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   // Credit + address: does not depend on routing, so it leaves first.
   if (blockIdx.x == 0 && tid < W) {
     unsigned long long* a = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.addr) +
-                            (static_cast<size_t>(par) * W + self) * 4;
+                            (static_cast<size_t>(par) * W + self) * kAddrWords;
     st_relaxed_sys(a + 0, tagged(g, static_cast<unsigned>(op.slot_off >> 8)));
     st_relaxed_sys(a + 1, tagged(g, static_cast<unsigned>(op.slot_capacity)));
     st_relaxed_sys(a + 2, tagged(g, static_cast<unsigned>(op.capacity)));
     st_relaxed_sys(a + 3, tagged(g, static_cast<unsigned>(op.identity)));
+    st_relaxed_sys(a + 4, tagged(g, gridDim.x));
     if (tid == 0) prof.first(kProfFirstPublish);
   }
 
@@ -321,9 +323,10 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       ok = false;
     }
   }
-  for (int i = tid; i < W * 4 && ok; i += kThreads)
-    ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(my_addr + i)) == g; },
-                      prof.poll_counter());
+  for (int i = tid; i < W * 5 && ok; i += kThreads) {
+    const unsigned long long* word = my_addr + (i / 5) * kAddrWords + i % 5;
+    ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(word)) == g; }, prof.poll_counter());
+  }
   if (!__syncthreads_and(ok)) {
     // Giving up: the loads already issued still target this CTA's shared memory, so they are
     // waited for (bounded) before the CTA may exit.
@@ -346,10 +349,11 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       if (s < self) off += v;
       total += v;
     }
-    const unsigned long long base = static_cast<unsigned long long>(value_of(ld_relaxed_sys(my_addr + d * 4 + 0))) << 8;
-    const int layout_cap = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * 4 + 1)));
-    const int bound = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * 4 + 2)));
-    const unsigned ident = value_of(ld_relaxed_sys(my_addr + d * 4 + 3));
+    const unsigned long long base = static_cast<unsigned long long>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 0))) << 8;
+    const int layout_cap = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 1)));
+    const int bound = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 2)));
+    const unsigned ident = value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 3));
+    s_ctas[d] = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 4)));
     const SlotLayout pl = slot_layout(layout_cap, 0, H, K, W);
     char* peer_slot = s_heap[d] + base;
     s_planes[d].hidden = peer_slot + pl.hidden;
@@ -554,31 +558,35 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   debug_delay(c, 3);
   __syncthreads();
   prof.stamp(4);
-  if (tid == 0) {
-    // This CTA's peer stores are performed system-wide before it arrives (a group of one rank
-    // has no peers: device scope is enough there).
+  if (tid < 32) {
+    // This CTA's peer stores are performed system-wide before it tells anybody: one fence by the
+    // whole first warp (cumulative over the CTA's stores through the barrier above), then lane d
+    // counts this CTA in at destination d - every rank that gets rows from this one waits for
+    // as many arrivals as this launch has CTAs. (A group of one rank has no peers: device scope
+    // is enough there.) No election of a last CTA and no second fence sit on the peers' path.
     if (W > 1) __threadfence_system(); else __threadfence();
-    const unsigned prev = atomicAdd(&hdr->done_count, 1u);
-    s_last = (prev == gridDim.x - 1) ? 1 : 0;
-    if (s_last) __threadfence();   // acquire side of the arrival counter; the flag store below releases at sys scope
-  }
-  __syncthreads();
-  if (s_last) {
-    if (tid < W) {
-      unsigned long long* flag = reinterpret_cast<unsigned long long*>(s_heap[tid] + cl.done) +
-                                 static_cast<size_t>(par) * W + self;
-      st_release_sys(flag, tagged(g, 1u));
-      if (tid == 0) prof.first(kProfFirstPublish);
+    for (int d = tid; d < W; d += 32) {
+      if (d == self || !s_ok[d] || s_send[d] <= 0) continue;
+      unsigned long long* arrivals = reinterpret_cast<unsigned long long*>(s_heap[d] + cl.done) +
+                                     static_cast<size_t>(par) * W + self;
+      red_add_relaxed_sys(arrivals, 1ull);
+      prof.first(kProfFirstPublish);
     }
     if (tid == 0) {
-      misc[kValidCount] = valid;
-      misc[kDirtyRows] = valid;
-      hdr->bar_count = 0;
-      hdr->done_count = 0;
-      hdr->work_next = 0;
-      hdr->disp_epoch = g;
-      __threadfence();
+      const unsigned prev = atomicAdd(&hdr->done_count, 1u);
+      s_last = (prev == gridDim.x - 1) ? 1 : 0;
+      if (s_last) __threadfence();   // acquire side of the arrival counter
     }
+  }
+  __syncthreads();
+  if (s_last && tid == 0) {          // rank-local bookkeeping of the launch
+    misc[kValidCount] = valid;
+    misc[kDirtyRows] = valid;
+    hdr->bar_count = 0;
+    hdr->done_count = 0;
+    hdr->work_next = 0;
+    hdr->disp_epoch = g;
+    __threadfence();
   }
 
   prof.stamp(5);
@@ -611,10 +619,27 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   prof.stamp(6);
   ok = true;
   // (Not for this rank's own rows: the launch itself completes only when they are written.)
-  if (tid < W && tid != self && s_ok[self] && value_of(ld_relaxed_sys(my_cnt + tid * W + self)) > 0)
-    ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return tag_of(ld_acquire_sys(my_done + tid)) == g; },
+  // Every CTA of a source counts itself in once its rows for this rank are stored. The counter
+  // belongs to this generation's parity and goes back to zero below, for the generation after
+  // next (no source can be there before this rank has entered the next generation, i.e.
+  // finished this one).
+  if (tid < W && tid != self && s_ok[self] && value_of(ld_relaxed_sys(my_cnt + tid * W + self)) > 0) {
+    const unsigned long long expected = static_cast<unsigned long long>(s_ctas[tid]);
+    ok = bounded_wait(c, kPhaseDispatch, 6, [&] { return ld_acquire_sys(my_done + tid) >= expected; },
                       prof.poll_counter());
-  __syncthreads_and(ok);
+  }
+  if (__syncthreads_and(ok) && W > 1) {
+    // The CTA that is through last puts the counters back (the others no longer read them).
+    if (tid == 0) {
+      __threadfence();
+      s_last = atomicAdd(&hdr->fin_count, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      if (tid < W) st_relaxed_sys(my_done + tid, 0ull);
+      if (tid == 0) hdr->fin_count = 0;
+    }
+  }
   prof.stamp(7);
   prof.flush(&hdr->status);
   sample_end(op.samples, sample);

@@ -65,15 +65,17 @@ struct CtrlHeader {
   unsigned work_next;       // dispatch: next unclaimed (token, segment) work item
   unsigned cwork_push;      // combine: next unclaimed (row, segment) item of the push phase
   unsigned cwork_reduce;    // combine: next unclaimed (token, segment) item of the reduce phase
-  unsigned reserved0;
+  unsigned fin_count;       // dispatch CTAs that are through with the launch's last wait
   unsigned long long reserved[25];
 };
 static_assert(sizeof(CtrlHeader) == 256, "control header is one 256-byte block");
 
+constexpr int kAddrWords = 8;         // address words one rank publishes per dispatch
+
 struct CtrlLayout {
   size_t cnt;    // u64 [2][W][W]  counts row of every source, by generation parity
-  size_t addr;   // u64 [2][W][4]  (slot offset >> 8, slot capacity, row bound, -) of every peer
-  size_t done;   // u64 [2][W]     "all my rows for you are stored"
+  size_t addr;   // u64 [2][W][8]  (slot offset >> 8, slot capacity, row bound, identity, CTAs of the launch, -, -, -) of every peer
+  size_t done;   // u64 [2][W]     CTAs of source s whose rows for this rank are stored (counted up by s, reset by the reader)
   size_t ready;  // u64 [W]        combine: (epoch << 32 | rows of yours I have pushed), monotone, max-updated
   size_t ident;  // u64 [2][W]     diagnostics: operation identity of every peer
   size_t perr;   // u32 [W]        error code published by a failing peer
@@ -99,7 +101,7 @@ EPX_HD CtrlLayout ctrl_layout(int world) {
   const size_t w = static_cast<size_t>(world);
   l.cnt = sizeof(CtrlHeader);
   l.addr = l.cnt + 2 * w * w * 8;
-  l.done = l.addr + 2 * w * 4 * 8;
+  l.done = l.addr + 2 * w * kAddrWords * 8;
   l.ready = l.done + 2 * w * 8;
   l.ident = l.ready + w * 8;
   l.perr = l.ident + 2 * w * 8;

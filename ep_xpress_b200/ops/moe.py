@@ -22,13 +22,16 @@ from .. import native as _native_loader
 
 
 class GroupedSwiGLU:
-    def __init__(self, w13, w2, *, max_rows, topk, max_local_pairs=None, pair_ctas=False, gather_loads=True):
+    def __init__(self, w13, w2, *, max_rows, topk, max_local_pairs=None, pair_ctas=False, gather_loads=False):
         """``max_local_pairs`` bounds the (row, slot) pairs whose expert lives on this rank.
 
-        ``gather_loads`` (default): the first GEMM's TMA producer gathers the activation rows of
-        every expert tile straight from the dispatch batch (four rows per gather copy), so no
-        expert-sorted copy of the activations exists; ``False`` keeps the separate gather kernel
-        and its ``[sorted rows, hidden]`` workspace.
+        ``gather_loads=True``: the first GEMM's TMA producer gathers the activation rows of every
+        expert tile straight from the dispatch batch (``tile::gather4``, four rows per copy), so
+        no gather launch and no expert-sorted copy of the activations exist. Bit-identical, but
+        opt-in: a 128-row operand tile then takes 32 copies of 512 bytes per k-step instead of
+        one 16 KB box, and the copy engine's issue rate, not the tensor pipe, bounds the GEMM
+        (measured at hidden 7168 / inter 2048, 2 GPUs, 4096 tokens per rank: 7.4 ms against
+        3.7 ms with the gather kernel, whose cost is 0.15 ms).
 
 
         The default is the worst case (every slot of every row is local). A tighter,

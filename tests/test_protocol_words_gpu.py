@@ -42,8 +42,8 @@ class LoneRank:
         for dest, count in ((0, count_for_me), (1, 0)):
             poke(0, self.offsets["cnt"] + 8 * ((parity * WORLD + 1) * WORLD + dest), tag | count)
         peer_slot = self.slot.offsets[0]            # rank 1 "uses" the same layout in its own heap
-        for k, value in enumerate((peer_slot >> 8, WORLD * TOKENS, WORLD * TOKENS, identity)):
-            poke(0, self.offsets["addr"] + 8 * ((parity * WORLD + 1) * 4 + k), tag | value)
+        for k, value in enumerate((peer_slot >> 8, WORLD * TOKENS, WORLD * TOKENS, identity, 4)):   # 4 = its CTAs
+            poke(0, self.offsets["addr"] + 8 * ((parity * WORLD + 1) * 8 + k), tag | value)
 
     def dispatch(self, ids, identity=0):
         x = torch.ones((TOKENS, HIDDEN), dtype=torch.bfloat16, device="cuda")
@@ -138,9 +138,9 @@ def test_identity_mismatch_is_detected_with_diagnostics():
     rank.close()
 
 
-def test_announced_rows_that_never_arrive_time_out_on_the_done_flag():
+def test_announced_rows_that_never_arrive_time_out_on_the_arrival_count():
     rank = LoneRank(timeout=0.05)
-    rank.forge_peer_dispatch_words(1, count_for_me=3)  # the peer promises three rows and never signals done
+    rank.forge_peer_dispatch_words(1, count_for_me=3)  # the peer promises three rows; none of its CTAs ever counts in
     status, detail, _, _ = rank.dispatch(LOCAL)
     assert status == 3 and (detail >> 32) & 0xff == 6 and usable()
     rank.close()
@@ -154,4 +154,17 @@ def test_generations_never_wrap():
     status, detail, dispatch_epoch, combine_epoch = rank.dispatch(LOCAL)
     assert status == 6 and detail & 0xFFFFFFFF == last + 1
     assert (dispatch_epoch, combine_epoch) == (last, last) and usable()
+    rank.close()
+
+
+def test_cpu_played_peer_counts_its_ctas_in_and_the_counter_is_reset():
+    """The peer announces rows and four CTAs; the wait ends when the arrival count reaches four
+    (forged from the host before the launch), and the rank puts the counter back to zero."""
+    rank = LoneRank(timeout=1.0)
+    rank.forge_peer_dispatch_words(1, count_for_me=3)
+    counter = rank.offsets["done"] + 8 * ((1 * WORLD) + 1)          # parity 1, source rank 1
+    rank.core.engine.poke_u64(0, counter, 4)
+    status, _, dispatch_epoch, _ = rank.dispatch(LOCAL)
+    assert (status, dispatch_epoch) == (0, 1)
+    assert rank.core.engine.peek_u64(0, counter) == 0 and usable()
     rank.close()
