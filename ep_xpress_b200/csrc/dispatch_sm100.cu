@@ -123,8 +123,10 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     fence_proxy_async();
   }
 
+  // A group of one rank exchanges nothing: its counts and its slot are known here.
+  const bool lone = W == 1;
   // Credit + address: does not depend on routing, so it leaves first.
-  if (blockIdx.x == 0 && tid < W) {
+  if (blockIdx.x == 0 && tid < W && !lone) {
     unsigned long long* a = reinterpret_cast<unsigned long long*>(c.heap[tid] + cl.addr) +
                             (static_cast<size_t>(par) * W + self) * kAddrWords;
     st_relaxed_sys(a + 0, tagged(g, static_cast<unsigned>(op.slot_off >> 8)));
@@ -244,7 +246,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
     s_send[tid] = run;
   }
   __syncthreads();
-  if (blockIdx.x == 0) {
+  if (blockIdx.x == 0 && !lone) {
     for (int i = tid; i < W * W; i += kThreads) {
       const int p = i / W, d = i % W;
       unsigned long long* dst = reinterpret_cast<unsigned long long*>(s_heap[p] + cl.cnt) +
@@ -311,7 +313,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   // A word of a LATER generation in this parity's place means the group is out of step (a rank
   // ran more dispatches than this one): that is reported at once instead of timing out.
   bool ok = true;
-  for (int i = tid; i < W * W && ok; i += kThreads) {
+  for (int i = tid; i < W * W && ok && !lone; i += kThreads) {
     bool ahead = false;
     ok = bounded_wait(c, kPhaseDispatch, 3, [&] {
       const unsigned tag = tag_of(ld_acquire_sys(my_cnt + i));
@@ -323,7 +325,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       ok = false;
     }
   }
-  for (int i = tid; i < W * 5 && ok; i += kThreads) {
+  for (int i = tid; i < W * 5 && ok && !lone; i += kThreads) {
     const unsigned long long* word = my_addr + (i / 5) * kAddrWords + i % 5;
     ok = bounded_wait(c, kPhaseDispatch, 4, [&] { return tag_of(ld_acquire_sys(word)) == g; }, prof.poll_counter());
   }
@@ -344,16 +346,18 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   if (tid < W) {
     const int d = tid;
     int off = 0, total = 0;
-    for (int s = 0; s < W; ++s) {
+    for (int s = 0; s < W && !lone; ++s) {
       const int v = static_cast<int>(value_of(ld_relaxed_sys(my_cnt + s * W + d)));
       if (s < self) off += v;
       total += v;
     }
-    const unsigned long long base = static_cast<unsigned long long>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 0))) << 8;
-    const int layout_cap = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 1)));
-    const int bound = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 2)));
-    const unsigned ident = value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 3));
-    s_ctas[d] = static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 4)));
+    if (lone) total = s_send[0];
+    const unsigned long long base = lone ? op.slot_off
+        : static_cast<unsigned long long>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 0))) << 8;
+    const int layout_cap = lone ? op.slot_capacity : static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 1)));
+    const int bound = lone ? op.capacity : static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 2)));
+    const unsigned ident = lone ? static_cast<unsigned>(op.identity) : value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 3));
+    s_ctas[d] = lone ? static_cast<int>(gridDim.x) : static_cast<int>(value_of(ld_relaxed_sys(my_addr + d * kAddrWords + 4)));
     const SlotLayout pl = slot_layout(layout_cap, 0, H, K, W);
     char* peer_slot = s_heap[d] + base;
     s_planes[d].hidden = peer_slot + pl.hidden;
@@ -368,7 +372,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
       reinterpret_cast<unsigned long long*>(slot + sl.peer_off)[d] = base;
       reinterpret_cast<int*>(slot + sl.peer_cap)[d] = layout_cap;
       reinterpret_cast<int*>(slot + sl.send_cnt)[d] = s_ok[d] ? s_send[d] : 0;
-      reinterpret_cast<int*>(slot + sl.recv_cnt)[d] = static_cast<int>(value_of(ld_relaxed_sys(my_cnt + d * W + self)));
+      reinterpret_cast<int*>(slot + sl.recv_cnt)[d] = lone ? s_send[0] : static_cast<int>(value_of(ld_relaxed_sys(my_cnt + d * W + self)));
       if (!s_ok[d] && (d == self || s_send[d] > 0))
         report_error(c, kCapacityExceeded, kPhaseDispatch, static_cast<unsigned>(d), static_cast<unsigned>(total));
       if (ident != static_cast<unsigned>(op.identity))

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) scale_rows_kernel(const unsigned short* _
     const unsigned short* src = hidden + row * hidden_size;
     unsigned short* dst = partial + row * hidden_size;
     if (vec) {
-      constexpr int kUnroll = 4;   // 64 bytes per lane in flight: the kernel is a pure HBM stream
+      constexpr int kUnroll = 8;   // 128 bytes per lane in flight: the kernel is a pure HBM stream, bound by latency
       for (int base = lane * 8; base < hidden_size; base += 32 * 8 * kUnroll) {
         uint4 v[kUnroll];
 #pragma unroll
