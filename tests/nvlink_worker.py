@@ -333,6 +333,76 @@ def run_host_ce(comm, rank, world, args):
             assert out.is_cuda and torch.equal(bits(out), bits(want[rank])), rounding
 
 
+def run_topk(comm, rank, world, args):
+    """top-k 3 and 33 with a placement that is neither contiguous nor balanced (one rank owns no
+    expert when there are at least three) - scenario of the reference's
+    tests/test_dispatch_route_tiles_cuda.py:105-114."""
+    hidden, tokens, experts = 192, 37, 40
+    owners = [(e * 7 + 3) % world for e in range(experts)]
+    if world >= 3:
+        owners = [o if o != 1 else 0 for o in owners]                  # rank 1 owns nothing
+    for topk in (3, 33):
+        cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=10.0)
+        with Context(nccl_comm=comm, expert_to_rank=owners, config=cfg) as ep:
+            for iteration in range(3):
+                routes = [workloads.uniform_routing(tokens - r, experts, topk, seed=iteration, rank=r) for r in range(world)]
+                ids, ws = [i for i, _ in routes], [w for _, w in routes]
+                if iteration == 1:
+                    ids = [i.to(torch.int32) for i in ids]
+                xs = [workloads.marker_payload(tokens - r, hidden, rank=r, iteration=iteration) for r in range(world)]
+                per_rank = [owners.count(r) for r in range(world)]
+                factors = [torch.arange(1, max(n, 1) + 1, dtype=torch.float32) / 4 for n in per_rank]
+                plan, rows, want = expected(xs, [i.to(torch.int64) for i in ids], ws, owners, world, topk, hidden, factors)
+                batch = ep.dispatch_async(xs[rank].cuda(), ids[rank].cuda(), ws[rank].cuda(), tag=iteration).wait()
+                check_batch(batch, plan, rows, rank)
+                out = ep.combine_async(scale_rows(ep, batch, factors[rank].cuda()), batch.handle, tag=iteration).wait()
+                assert torch.equal(bits(out), bits(want[rank])), f"topk {topk} iteration {iteration}: combine differs"
+            ep.check()
+
+
+def run_subgroup(rank, world, args):
+    """An EP group over a NON-contiguous subgroup ([0, 2] of four ranks); on one member the handle
+    object is dropped and garbage-collected and then looked up again - that must not communicate
+    (the other member does not call anything) - and the subgroup's communicator still works
+    after the context is closed (scenario of the reference's tests/test_nccl_comm_cuda.py:46-87)."""
+    import gc
+    members = [0, 2]
+    group = dist.new_group(members)                     # collective over ALL ranks
+    if rank in members:
+        comm = get_nccl_comm_handle(group)              # collective over the subgroup (warms it up)
+        assert (comm.rank, comm.world_size) == (members.index(rank), 2)
+        pointer = comm.get()
+        if rank == 0:
+            del comm
+            gc.collect()
+        torch.cuda.synchronize()
+        comm = get_nccl_comm_handle(group)              # rank 0: a fresh handle object, no collective
+        assert comm.get() == pointer
+        hidden, topk, tokens = 128, 2, 16
+        emap = workloads.round_robin_expert_map(4, 2)
+        cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=10.0)
+        me = members.index(rank)
+        with Context(nccl_comm=comm, expert_to_rank=emap, config=cfg) as ep:
+            routes = [workloads.uniform_routing(tokens, 4, topk, seed=9, rank=r) for r in range(2)]
+            xs = [workloads.marker_payload(tokens, hidden, rank=r, iteration=0) for r in range(2)]
+            ids, ws = [i for i, _ in routes], [w for _, w in routes]
+            plan, rows, want = expected(xs, ids, ws, emap, 2, topk, hidden, [torch.ones(2)] * 2)
+            batch = ep.dispatch_async(xs[me].cuda(), ids[me].cuda(), ws[me].cuda()).wait()
+            check_batch(batch, plan, rows, me)
+            out = ep.combine_async(scale_rows(ep, batch), batch.handle).wait()
+            assert torch.equal(bits(out), bits(want[me]))
+            try:
+                Context(nccl_comm=comm, expert_to_rank=emap, config=cfg, device=torch.device("cuda", (rank + 1) % world))
+            except ValueError as error:
+                assert "same CUDA device" in str(error)
+            else:
+                raise AssertionError("a context on another device than its communicator must be rejected")
+        probe = torch.ones(1, device="cuda")
+        dist.all_reduce(probe, group=group)             # the borrowed communicator survives close()
+        assert probe.item() == 2
+    dist.barrier()
+
+
 def run_errors(ep, rank, world, args):
     """A capacity that is too small poisons the group within the timeout; the GPU stays usable."""
     hidden, topk, tokens = args.hidden, 4, args.tokens
@@ -404,7 +474,7 @@ CASES = {"streams": run_streams, "stagger": run_stagger, "headline": run_headlin
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", choices=sorted(CASES) + ["hostce"], required=True)
+    parser.add_argument("--case", choices=sorted(CASES) + ["hostce", "topk", "subgroup"], required=True)
     parser.add_argument("--hidden", type=int, default=256)
     parser.add_argument("--tokens", type=int, default=24)
     parser.add_argument("--replays", type=int, default=1000)
@@ -415,6 +485,14 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     comm = get_nccl_comm_handle(dist.group.WORLD)
+    if args.case in ("topk", "subgroup"):
+        if args.case == "topk":
+            run_topk(comm, rank, world, args)
+        else:
+            run_subgroup(rank, world, args)
+        dist.destroy_process_group()
+        print(f"rank {rank}: {args.case} ok", flush=True)
+        return
     if args.case == "hostce":
         run_host_ce(comm, rank, world, args)
         dist.destroy_process_group()

@@ -96,6 +96,24 @@ def test_single_round_mode_and_noncontiguous_placement():
         run_round(group, slot, xs, ids, ws, emap, rounding="single")
 
 
+@pytest.mark.parametrize("world,topk", [(4, 3), (4, 33), (8, 33), (2, 33)])
+def test_wide_topk_with_a_scattered_expert_map(world, topk):
+    """top-k 3 and 33 (above the routed-from-registers width), a placement that is neither
+    contiguous nor balanced, one rank without experts."""
+    hidden, tokens, experts = 192, 37, 40
+    owners = [(e * 7 + 3) % world for e in range(experts)]
+    if world >= 3:
+        owners = [o if o != 1 else 0 for o in owners]
+    cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=2.0)
+    with EmulatedGroup(world, owners, cfg) as group:
+        slot = group.create_slot()
+        for seed in range(3):
+            routes = [workloads.uniform_routing(tokens - r, experts, topk, seed=seed, rank=r) for r in range(world)]
+            xs = [workloads.marker_payload(tokens - r, hidden, rank=r, iteration=seed) for r in range(world)]
+            ids = [i if seed != 1 else i.to(torch.int32) for i, _ in routes]
+            run_round(group, slot, xs, ids, [w for _, w in routes], owners)
+
+
 def test_intermediate_rounding_is_observable():
     """remote-sum -> bf16 -> + local -> bf16 differs from a single rounding on chosen values."""
     world, hidden = 3, 64

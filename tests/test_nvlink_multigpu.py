@@ -104,3 +104,17 @@ def test_operation_profile():
 @pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
 def test_host_staged_transport_on_cuda_tensors():
     launch("hostce", 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_topk_3_and_33_with_a_scattered_expert_map():
+    launch("topk", min(gpu_count(), 4))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 3, reason="needs at least three CUDA devices")
+def test_noncontiguous_subgroup_and_handle_reacquisition():
+    launch("subgroup", min(gpu_count(), 4))

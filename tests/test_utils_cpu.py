@@ -9,7 +9,7 @@ from unittest import mock
 import pytest
 import torch
 
-from ep_xpress_b200.utils import clocks, profile, workloads
+from ep_xpress_b200.utils import clocks, profile, routing, workloads
 
 
 def fake_nvml(clock_values, reason_bits):
@@ -184,3 +184,25 @@ def test_communication_patterns_rotate():
     assert (dropped[::3] == -1).all() and (dropped[1::3] >= 0).all()
     empty, _ = workloads.communication_pattern(0, rank=0, world_size=4, tokens=0, num_experts=16, topk=4)
     assert empty.shape == (0, 4)
+
+
+@pytest.mark.parametrize("rounding", ["two_step", "single"])
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_identity_layer_oracle_matches_the_group_wide_oracles(world, rounding):
+    """The per-rank shortcut the benchmarks verify against equals dispatch -> weighted identity
+    expert -> combine computed over the whole group's route plan, bit for bit."""
+    torch.manual_seed(3)
+    experts, topk, hidden, tokens = 12, 4, 64, 23
+    owners = workloads.round_robin_expert_map(experts, world)
+    routes = [workloads.uniform_routing(tokens - r, experts, topk, seed=5, rank=r, weights="sigmoid") for r in range(world)]
+    ids, ws = [i.clone() for i, _ in routes], [w for _, w in routes]
+    ids[0][3, 1] = -1                                   # an inactive slot
+    xs = [workloads.gaussian_payload(tokens - r, hidden, seed=7, rank=r) for r in range(world)]
+    plan = routing.plan_routes(ids, ws, owners, world, topk)
+    rows = routing.dispatch_oracle(xs, plan)
+    partials = [routing.scale_expert_oracle(rows[r], plan.received[r].local_ids, plan.received[r].weights)
+                for r in range(world)]
+    want = routing.combine_oracle(partials, plan, hidden, rounding)
+    for rank in range(world):
+        got = routing.identity_layer_oracle(xs[rank], ids[rank], ws[rank], owners, rank, world, rounding)
+        assert torch.equal(got.view(torch.int16), want[rank].view(torch.int16))
