@@ -349,7 +349,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   const int cta_items = kMailbox ? (items > lo ? (items - lo + stride - 1) / stride : 0)
                                  : hi - static_cast<int>(static_cast<long long>(items) * a.cta / a.ctas);
   const int mine = cta_items > group ? (cta_items - group + kGroups - 1) / kGroups : 0;
-  long long waited = 0, worked = 0;          // profiling only: cycles spent waiting / working
+  long long waited = 0, worked = 0, stored = 0;   // profiling only: cycles spent waiting / working / in the store loop
   bool ok = true;
   if (producer) {
     auto item_of = [&](int k) { return lo + (group + k * kGroups) * stride; };
@@ -399,7 +399,11 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             ok = false;
             continue;
           }
-          waited += clock64() - t0;
+          if (kProfile) {
+            const long long t1 = clock64();
+            waited += t1 - t0;
+            worked -= t1 - t0;         // `worked` below adds the whole item: leave the wait out of it
+          }
           const int item = item_of(base + i);
           const int t = item / rsegs, seg = item - t * rsegs;
           const int n = __popcll(m);
@@ -450,6 +454,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           if (src != nullptr)
             bulk_load_to_smem(ring + static_cast<size_t>(stage) * stage_bytes + lane * seg_max, src + b0,
                               static_cast<unsigned>(bytes), full + stage);
+          if (kProfile) worked += clock64() - t0;
         }
       }
       mask_now = mask_next;
@@ -507,12 +512,14 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
             }
           }
         }
+        const long long t2 = kProfile ? clock64() : 0;
 #pragma unroll
         for (int u = 0; u < kChunksPerThread; ++u) {
           const int chunk = first + u * kGroupThreads;
           if (chunk < chunks)
             store_chunk<4>(a.out + item.out_offset + chunk * 16, finish<4>(acc[u], local[u], has_local, a.single_round));
         }
+        if (kProfile) stored += clock64() - t2;
       }
       __syncwarp();
       if (lane == 0) mbarrier_arrive(empty + stage);
@@ -523,6 +530,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
     unsigned long long* slot = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps + (warp == 0 ? 4 : 6);
     slot[0] = static_cast<unsigned long long>(waited);
     slot[1] = static_cast<unsigned long long>(worked);
+    if (warp == 0) a.profile[static_cast<size_t>(blockIdx.x) * kProfileStamps + kProfStoreCycles] = static_cast<unsigned long long>(stored);
   }
   return ok;
 }
@@ -1014,6 +1022,94 @@ combine_kernel(const __grid_constant__ CombineArgs args) {
   combine_body<kVec16, kMode, kProfile>(args.op[blockIdx.y], combine_smem);
 }
 
+// ---- a group of ONE rank ----------------------------------------------------------------------
+// Nothing is pushed, signalled or awaited: every token's only contributor is this rank's own
+// partial row, so combine is one pass over local memory, `out[t] = finish(partial[row(t)])` with
+// the same rounding helpers as the general reduce (0 + x in FP32, so -0 becomes +0 there too).
+// A pass like that is bound by memory latency, not by arithmetic: it wants many resident warps
+// with several 16-byte loads in flight each, not one 640-thread CTA per SM with its stage rings.
+// So it is a plain launch of small CTAs, one warp per token at a time. Epoch, sample ring and
+// error reporting are those of the general kernel; profiled operations use the general kernel.
+constexpr int kLoneThreads = 256;
+constexpr int kLoneUnroll = 8;
+constexpr int kLoneMaxCtas = 148 * 8;
+
+__global__ void __launch_bounds__(kLoneThreads) combine_lone_kernel(const __grid_constant__ CombineArgs args) {
+  const CombineOp& op = args.op[blockIdx.y];
+  const RankCtx& c = *op.ctx;
+  const int H = c.hidden, K = c.topk;
+  const bool single_round = c.single_round != 0;
+  const int tid = threadIdx.x, lane = tid & 31;
+  char* const my_heap = c.heap[c.rank];
+  CtrlHeader* const hdr = header_of(my_heap);
+  const SlotLayout sl = slot_layout(op.slot_capacity, op.slot_tokens, H, K, 1);
+  char* const slot = my_heap + op.slot_off;
+  const unsigned long long* const mask_arr = reinterpret_cast<const unsigned long long*>(slot + sl.mask);
+  const int* const send_rows = reinterpret_cast<const int*>(slot + sl.send_rows);
+  const int* const misc = reinterpret_cast<const int*>(slot + sl.misc);
+  const char* const partial = reinterpret_cast<const char*>(op.partial);
+  char* const out = reinterpret_cast<char*>(op.out);
+  const int fan = route_fanout(K, 1);
+  const long long row_bytes = static_cast<long long>(H) * 2;
+
+  const unsigned e = ld_volatile_u32(&hdr->comb_epoch) + 1;
+  if (e > kLastEpoch) {
+    if (tid == 0 && blockIdx.x == 0) report_error(c, kEpochsExhausted, kPhaseCombine, 0xE0, e);
+    return;
+  }
+  const unsigned sample = sample_begin(op.samples, e, op.sample_capacity);
+  if (misc[kValidCount] > op.partial_rows && tid == 0 && blockIdx.x == 0)
+    report_error(c, kCapacityExceeded, kPhaseCombine, 7, static_cast<unsigned>(op.partial_rows));
+
+  const int warps = kLoneThreads / 32;
+  for (long long t = static_cast<long long>(blockIdx.x) * warps + (tid >> 5); t < op.tokens;
+       t += static_cast<long long>(gridDim.x) * warps) {
+    const int row = (mask_arr[t] & 1ull) ? send_rows[t * fan] : -1;
+    const bool usable = row >= 0 && row < op.partial_rows;       // warp-uniform
+    const char* src = partial + static_cast<long long>(usable ? row : 0) * row_bytes;
+    char* dst = out + t * row_bytes;
+    for (long long base = static_cast<long long>(lane) * 16; base < row_bytes; base += 32ll * 16 * kLoneUnroll) {
+      Chunk<4> v[kLoneUnroll] = {};
+#pragma unroll
+      for (int u = 0; u < kLoneUnroll; ++u) {
+        const long long off = base + static_cast<long long>(u) * 512;
+        if (usable && off < row_bytes) v[u] = load_local_chunk<4>(src + off);
+      }
+#pragma unroll
+      for (int u = 0; u < kLoneUnroll; ++u) {
+        const long long off = base + static_cast<long long>(u) * 512;
+        if (off >= row_bytes) continue;
+        unsigned long long acc[4] = {0ull, 0ull, 0ull, 0ull};
+        Chunk<4> result;
+        if (!usable) {
+          result = finish<4>(acc, v[u], false, single_round);          // no contributor: zeros
+        } else if (single_round) {
+          accumulate<4>(acc, v[u]);
+          result = finish<4>(acc, v[u], false, true);
+        } else {
+          result = finish<4>(acc, v[u], true, false);
+        }
+        store_chunk<4>(dst + off, result);
+      }
+    }
+  }
+
+  __syncthreads();
+  sample_end(op.samples, sample);
+  if (tid == 0) {
+    __threadfence();
+    const unsigned prev = atomicAdd(&hdr->cfin_count, 1u);
+    if (prev == gridDim.x - 1) {
+      hdr->cdone_count = 0;
+      hdr->cfin_count = 0;
+      hdr->cwork_push = 0;
+      hdr->cwork_reduce = 0;
+      hdr->comb_epoch = e;
+      __threadfence();
+    }
+  }
+}
+
 struct CombineVariant {
   const void* kernel;
   int threads;
@@ -1074,6 +1170,15 @@ cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank
   void* params[] = {const_cast<CombineArgs*>(&args)};
   CombineVariant variant;
   const long long row_bytes = static_cast<long long>(hidden) * 2;
+  if (world == 1 && ranks == 1 && vec16 && args.op[0].profile == nullptr) {
+    // One rank: a streaming pass over local memory, eight tokens per CTA and pass.
+    const int warps = kLoneThreads / 32, tokens = args.op[0].tokens;
+    int ctas = (tokens + warps - 1) / warps;
+    if (ctas < 1) ctas = 1;
+    if (ctas > kLoneMaxCtas) ctas = kLoneMaxCtas;
+    return cudaLaunchKernel(reinterpret_cast<const void*>(combine_lone_kernel), dim3(ctas, 1, 1),
+                            dim3(kLoneThreads, 1, 1), params, 0, stream);
+  }
   cudaError_t err = pick_combine(vec16, fanout, mailbox && combine_can_mailbox(vec16, fanout, world, row_bytes), &variant,
                                  args.op[0].profile != nullptr);
   if (err != cudaSuccess) return err;

@@ -153,6 +153,7 @@ enum ProfileWord : int {
   kProfMode = 16,         // combine: 1 + protocol (0 register, 1 bulk, 2 mailbox); dispatch: 1 register path, 2 bulk-copy movers
   kProfPushWait = 17,     // combine, mailbox: ns the CTA's pushers spent waiting for their copies (loads landed, stores completed)
   kProfArrivalWait = 18,  // combine, mailbox: ns producer 0 spent waiting for arrival words of peers' rows
+  kProfStoreCycles = 19,  // combine, bulk-copy reduce: cycles consumer warp 0 spent converting and storing finished chunks
 };
 
 enum MiscWord : int { kValidCount = 0, kDirtyRows = 1, kSendTotal = 2 };

@@ -41,7 +41,7 @@ COMBINE_INTERVALS = {1: ("push", "signal_wait", "reduce"), 2: ("push", "signal_w
                      3: ("push_and_reduce_until_first_pusher_done", "push_and_reduce", "retire")}
 COMBINE_PROTOCOLS = {1: "register", 2: "bulk", 3: "mailbox"}
 WORDS = {"rows": 8, "bytes": 9, "items": 10, "polls": 11, "first_publish": 12, "first_receive": 13, "status": 14,
-         "completion": 15, "mode": 16, "push_wait": 17, "arrival_wait": 18}
+         "completion": 15, "mode": 16, "push_wait": 17, "arrival_wait": 18, "store_cycles": 19}
 
 
 class OperationProfile:
@@ -95,6 +95,8 @@ def summarize(record, stamps):
     entry = dict(record)
     if kind == "combine":
         entry["cycles"] = {name: float(stamps[:, 4 + i].double().mean()) for i, name in enumerate(COMBINE_CYCLES)}
+        if stamps.shape[1] > WORDS["store_cycles"]:
+            entry["cycles"]["consumer_store_cycles"] = float(stamps[:, WORDS["store_cycles"]].double().mean())
     entry["phases"] = phases
     entry["elapsed_ns"] = max((p["last_ns"] for p in phases.values()), default=0)
     wide = stamps.shape[1] > WORDS["arrival_wait"]

@@ -114,6 +114,35 @@ def test_wide_topk_with_a_scattered_expert_map(world, topk):
             run_round(group, slot, xs, ids, [w for _, w in routes], owners)
 
 
+@pytest.mark.parametrize("rounding", ["two_step", "single"])
+@pytest.mark.parametrize("hidden,tokens", [(7168, 300), (264, 41), (64, 1)])
+def test_one_rank_group_streams_local_rows(hidden, tokens, rounding):
+    """A group of one rank takes the streaming combine: tokens without any active expert come out
+    as zeros, negative zeros come out as +0 like everywhere else, repeated operations keep the
+    epoch in step, and a short partial is an error."""
+    topk, experts = 4, 8
+    cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=tokens, timeout_seconds=2.0,
+                 combine_rounding=rounding)
+    emap = [0] * experts
+    with EmulatedGroup(1, emap, cfg) as group:
+        slot = group.create_slot()
+        for seed in range(3):
+            ids, ws = workloads.uniform_routing(tokens, experts, topk, seed=seed, rank=0)
+            x = workloads.gaussian_payload(tokens, hidden, seed=seed, rank=0)
+            x[0, : hidden // 2] = -0.0
+            if tokens > 2:
+                ids[1] = -1                                     # a token that goes nowhere
+                ws[2] = 0.0                                     # a token whose row is scaled to zero
+            run_round(group, slot, [x], [ids], [ws], emap, rounding=rounding, direct_partial=(seed != 1))
+        if tokens > 2:
+            dev = group.device
+            batch = group.dispatch(slot, [x.to(dev)], [ids.to(dev)], [ws.to(dev)])[0]
+            short = group.scale_rows(batch)[: tokens - 2].clone()
+            group.combine(slot, [short], [tokens])
+            torch.cuda.synchronize()
+            assert group.status()[0][0] != 0
+
+
 def test_intermediate_rounding_is_observable():
     """remote-sum -> bf16 -> + local -> bf16 differs from a single rounding on chosen values."""
     world, hidden = 3, 64
