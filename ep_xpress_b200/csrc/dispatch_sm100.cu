@@ -236,14 +236,23 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   debug_delay(c, 1);
 
   // ---- 2. publish my count row ----------------------------------------------
-  if (tid < W) {
+  // One warp per destination: the lanes fetch the tiles' counts together (one memory round
+  // trip for 32 tiles instead of one per tile) and scan them with shuffles.
+  for (int d = warp; d < W; d += kWarps) {
     int run = 0;
-    for (int tile = 0; tile < ntiles; ++tile) {
-      const int v = tile_cnt[static_cast<long long>(tile) * W + tid];
-      tile_base[tile * W + tid] = run;
-      run += v;
+    for (int first = 0; first < ntiles; first += 32) {
+      const int tile = first + lane;
+      const int v = tile < ntiles ? tile_cnt[static_cast<long long>(tile) * W + d] : 0;
+      int upto = v;
+#pragma unroll
+      for (int step = 1; step < 32; step <<= 1) {
+        const int below = __shfl_up_sync(0xffffffffu, upto, step);
+        if (lane >= step) upto += below;
+      }
+      if (tile < ntiles) tile_base[tile * W + d] = run + upto - v;
+      run += __shfl_sync(0xffffffffu, upto, 31);
     }
-    s_send[tid] = run;
+    if (lane == 0) s_send[d] = run;
   }
   __syncthreads();
   if (blockIdx.x == 0 && !lone) {
@@ -278,11 +287,20 @@ __device__ __forceinline__ void dispatch_body(const DispatchOp& op, int* tile_ba
   // Towards the end of the batch a mover takes one piece at a time: a full claim is tens of
   // microseconds of link time, which the last claimers would spend alone.
   const long long tail_items = static_cast<long long>(gridDim.x) * kMovers * kMoveStages;
+  // Every mover's FIRST claim is its own fixed share (mover g of the launch takes pieces
+  // g * claim ...): hundreds of movers hitting one counter at the same instant queue up for
+  // microseconds. The counter hands out what lies behind those shares.
+  const long long fixed_items = static_cast<long long>(gridDim.x) * kMovers * claim;
+  bool first_claim = true;
   auto claim_and_load = [&]() {
     unsigned base = 0, taken = claim;
-    if (lane == 0) {
-      if (claim > 1 && move_items - static_cast<long long>(ld_volatile_u32(&hdr->work_next)) < tail_items) taken = 1;
-      base = atomicAdd(&hdr->work_next, taken);
+    if (first_claim) {
+      base = (blockIdx.x * kMovers + warp) * claim;
+      first_claim = false;
+    } else if (lane == 0) {
+      const long long handed = fixed_items + static_cast<long long>(ld_volatile_u32(&hdr->work_next));
+      if (claim > 1 && move_items - handed < tail_items) taken = 1;
+      base = static_cast<unsigned>(fixed_items) + atomicAdd(&hdr->work_next, taken);
     }
     base = __shfl_sync(0xffffffffu, base, 0);
     taken = __shfl_sync(0xffffffffu, taken, 0);
