@@ -11,9 +11,10 @@ the CUDA-graph hooks an engine's MoE layer and graph runner call.
 from .dispatcher import DispatchOutput, EPDispatcher, close_contexts, prepare_graph_capture, prepare_graph_replay
 from .env import PRESETS, channel_policy_from_env, config_from_env
 from .guards import (contiguous_expert_map, receive_capacity_from_scheduler, select_active_channels,
-                     validate_expert_runner, validate_runner_config, validate_server_args)
+                     validate_expert_runner, validate_moe_layer, validate_runner_config, validate_server_args,
+                     validate_serving_args)
 
 __all__ = ["DispatchOutput", "EPDispatcher", "PRESETS", "channel_policy_from_env", "close_contexts", "config_from_env",
            "contiguous_expert_map", "prepare_graph_capture", "prepare_graph_replay",
-           "receive_capacity_from_scheduler", "select_active_channels", "validate_expert_runner", "validate_runner_config",
-           "validate_server_args"]
+           "receive_capacity_from_scheduler", "select_active_channels", "validate_expert_runner", "validate_moe_layer",
+           "validate_runner_config", "validate_server_args", "validate_serving_args"]

@@ -93,13 +93,24 @@ class EPDispatcher:
         self._workspaces[key] = self.context.create_workspace(capacity, tokens)
         return self._workspaces[key]
 
-    def dispatch(self, hidden_states, topk_ids, topk_weights, *, token_counts, is_decode, stream=None):
-        """``token_counts``: scheduled tokens of EVERY rank of the group (host integers)."""
+    def dispatch(self, hidden_states, topk_ids, topk_weights, *, token_counts=None, is_decode, stream=None,
+                 recv_capacity=None):
+        """``token_counts``: scheduled tokens of EVERY rank of the group (host integers), or
+        ``recv_capacity``: their sum where the scheduler already publishes it (a padded sum is fine:
+        it only has to bound the rows this rank can receive and be the same on every rank)."""
         if self._outstanding is not None:
             raise RuntimeError(f"layer {self.layer_id} already has an operation outstanding; combine it first")
         cfg = self.config
         tokens = hidden_states.shape[0]
-        capacity = receive_capacity_from_scheduler(token_counts, cfg.max_tokens_per_rank)
+        if (token_counts is None) == (recv_capacity is None):
+            raise ValueError("pass either token_counts or recv_capacity")
+        if recv_capacity is None:
+            capacity = receive_capacity_from_scheduler(token_counts, cfg.max_tokens_per_rank)
+        else:
+            capacity = int(recv_capacity)
+            world = getattr(self.context, "world_size", None)
+            if capacity < 0 or (world is not None and capacity > world * cfg.max_tokens_per_rank):
+                raise ValueError("recv_capacity must lie within [0, world_size * max_tokens_per_rank]")
         small_decode = is_decode and tokens <= max(cfg.decode_max_tokens, 0)
         channels = select_active_channels(tokens, self.context.effective_channels, is_decode=is_decode,
                                           **self.channel_policy)

@@ -39,7 +39,9 @@ _POLICY = {
 
 # Read by other parts of the library, not by this module: accepted here so that setting them does
 # not make the configuration fail ("EPX_NODE_ID": node label of the multi-node context).
-_FOREIGN = ("EPX_NODE_ID",)
+# "EPX_MAX_TOKENS", "EPX_CUDA_GRAPH", "EPX_GEMM_CTA_PAIRS": read by the SGLang binding (per-rank
+# token capacity, full decode graphs on/off, CTA pairs in the grouped GEMM).
+_FOREIGN = ("EPX_NODE_ID", "EPX_MAX_TOKENS", "EPX_CUDA_GRAPH", "EPX_GEMM_CTA_PAIRS")
 
 PRESETS = {
     # decode-heavy serving: small bounded batches, many retained per-layer workspaces

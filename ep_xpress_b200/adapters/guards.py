@@ -86,3 +86,59 @@ def validate_expert_runner(*, activation="silu", is_gated=True, gemm1_alpha=None
         raise ValueError("the grouped expert runner requires gated SiLU")
     if any(value is not None for value in (gemm1_alpha, gemm1_clamp_limit, swiglu_limit)):
         raise ValueError("the grouped expert runner does not support activation modifiers")
+
+
+_UNSUPPORTED_SERVER_FEATURES = (
+    "enable_eplb", "enable_waterfill", "enable_lora", "enable_two_batch_overlap", "enable_single_batch_overlap",
+    "enable_fused_moe_sum_all_reduce", "enable_torch_compile", "speculative_algorithm", "ep_num_redundant_experts",
+    "ep_join_mode", "elastic_ep_backend", "enable_memory_saver", "enable_pdmux",
+)
+
+
+def validate_serving_args(args, model_config=None):
+    """The same layout rules for a serving framework's resolved argument OBJECT (attribute access,
+    missing attributes take the framework's defaults), plus the features that would bypass or
+    re-order the dispatcher. Scope of the reference's guard (ep_xpress/adapters/sglang_config.py:6-45)
+    minus its model allow-list: any BF16 MoE with evenly split, unshared experts is served.
+    """
+    tp = getattr(args, "tp_size", 1)
+    if getattr(args, "nnodes", 1) != 1:
+        raise ValueError("the NVLink transport spans the GPUs of one node (nnodes must be 1)")
+    validate_server_args(tp_size=tp, dp_size=getattr(args, "dp_size", 1), ep_size=getattr(args, "ep_size", tp),
+                         pp_size=getattr(args, "pp_size", 1), moe_tp_size=getattr(args, "moe_tp_size", 1),
+                         moe_dp_size=getattr(args, "moe_dp_size", 1),
+                         enable_dp_attention=bool(getattr(args, "enable_dp_attention", False)))
+    if getattr(args, "dwdp_size", 1) != 1:
+        raise ValueError("dense-weight data parallelism is not supported with the EP dispatcher")
+    if getattr(args, "dtype", None) not in ("bfloat16", "bf16"):
+        raise ValueError("activations and expert weights must be BF16: pass the dtype explicitly")
+    if getattr(args, "quantization", None) or getattr(model_config, "quantization_config", None):
+        raise ValueError("quantised experts are not supported: the expert runner is BF16")
+    for name in _UNSUPPORTED_SERVER_FEATURES:
+        if getattr(args, name, None):
+            raise ValueError(f"{name} is not supported with the EP dispatcher")
+    if getattr(model_config, "n_shared_experts", 0) or getattr(model_config, "num_shared_experts", 0):
+        raise ValueError("shared experts are not supported: every expert is routed")
+
+
+def validate_moe_layer(config, *, world_size, bf16):
+    """Per-layer facts of a framework's MoE runner configuration object: BF16, no fused shared
+    experts, weighted output that is combined by the dispatcher, an even contiguous expert split
+    (ep_xpress/adapters/sglang_config.py:48-58)."""
+    if getattr(config, "params_dtype", bf16) != bf16:
+        raise ValueError("the EP dispatcher needs BF16 activations and expert weights")
+    if getattr(config, "num_fused_shared_experts", 0):
+        raise ValueError("fused shared experts are not supported")
+    validate_runner_config(reduce_results=False,
+                           apply_router_weight_on_input=bool(getattr(config, "apply_router_weight_on_input", False)),
+                           activation=getattr(config, "activation", "silu"))
+    if getattr(config, "no_combine", False):
+        raise ValueError("the expert runner must return combined-per-row output (no_combine is not supported)")
+    if config.num_experts != world_size * config.num_local_experts:
+        raise ValueError("experts must divide evenly into contiguous blocks per rank")
+    if getattr(config, "use_tp_all_gather_activation", False):
+        raise ValueError("TP activation all-gather cannot be combined with the EP dispatcher")
+    validate_expert_runner(activation=getattr(config, "activation", "silu"), is_gated=getattr(config, "is_gated", True),
+                           gemm1_alpha=getattr(config, "gemm1_alpha", None),
+                           gemm1_clamp_limit=getattr(config, "gemm1_clamp_limit", None),
+                           swiglu_limit=getattr(config, "swiglu_limit", None))
