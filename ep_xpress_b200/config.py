@@ -66,7 +66,7 @@ class Config:
     zero_padding: bool = True                 # keep activation rows above valid_count at zero
     cooperative_launch: bool = True           # driver-guaranteed co-residency of the transport CTAs
     debug_delay_ns: int = 0                   # debugging: random sleeps below this bound at kernel phase boundaries
-    combine_streaming: str = "auto"           # reduce while peers still push: "on"; "off"/"auto": push, then reduce
+    combine_streaming: str = "auto"           # "auto"/"on": mailbox protocol (reduce while peers still push); "off": push, signal, reduce
 
     @property
     def single_rounding(self) -> bool:

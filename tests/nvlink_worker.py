@@ -403,6 +403,49 @@ def run_subgroup(rank, world, args):
     dist.barrier()
 
 
+def run_multinode(comm, rank, world, args):
+    """The multi-node context on GPUs: the ranks of ONE box are labelled as two nodes, records move
+    with grouped NCCL point-to-point transfers on the borrowed communicator, and every plane is
+    compared with the oracle (the CPU-rank test of the same path: tests/test_multinode_gloo.py)."""
+    hidden, topk, tokens, experts = 256, 3, 21, world * 3
+    emap = [(e * 7) % world for e in range(experts)]
+    os.environ["EPX_NODE_ID"] = f"node{rank * 2 // world}"          # two node labels on one box
+    for rounding in ("auto", "two_step"):
+        cfg = Config(hidden_size=hidden, topk=topk, max_tokens_per_rank=32, transport="host_sm",
+                     internode_transport="gin", combine_rounding=rounding, max_pending_operations=2)
+        ep = Context(comm, emap, cfg)
+        assert type(ep).__name__ == "MultiNodeContext" and ep.device.type == "cuda"
+        assert ep.transport_info["nodes"] == 2 and rank in ep.transport_info["local_ranks"]
+        handles = []
+        for seed in (1, 2):
+            routes = [workloads.uniform_routing(max(tokens - 4 * r, 0), experts, topk, seed=seed, rank=r) for r in range(world)]
+            ids, ws = [i for i, _ in routes], [w for _, w in routes]
+            xs = [workloads.gaussian_payload(i.shape[0], hidden, seed=seed, rank=r) for r, i in enumerate(ids)]
+            plan = routing.plan_routes(ids, ws, emap, world, topk)
+            batch = ep.dispatch_async(xs[rank].cuda(), (ids[rank] if seed == 1 else ids[rank].to(torch.int32)).cuda(),
+                                      ws[rank].cuda(), tag=("layer", seed)).wait()
+            want = plan.received[rank]
+            valid = int(batch.valid_count.item())
+            assert batch.hidden.is_cuda and valid == want.rows
+            assert torch.equal(bits(batch.hidden[:valid]), bits(routing.dispatch_oracle(xs, plan)[rank]))
+            assert torch.equal(batch.local_ids[:valid].cpu(), want.local_ids)
+            assert torch.equal(batch.handle.inverse_map[:valid].cpu(), want.inverse)
+            assert (batch.local_ids[valid:] == -1).all() and (batch.hidden[valid:] == 0).all()
+            partial = routing.scale_expert_oracle(batch.hidden[:valid].cpu(), batch.local_ids[:valid].cpu(),
+                                                  batch.weights[:valid].cpu())
+            padded = torch.zeros_like(batch.hidden)
+            padded[:valid] = partial.cuda()
+            handles.append((batch.handle, padded, xs, plan, seed))
+        for handle, padded, xs, plan, seed in reversed(handles):
+            out = ep.combine_async(padded, handle, tag=("layer", seed)).wait()
+            rows = routing.dispatch_oracle(xs, plan)
+            partials = [routing.scale_expert_oracle(rows[r], plan.received[r].local_ids, plan.received[r].weights)
+                        for r in range(world)]
+            want_out = routing.combine_oracle(partials, plan, hidden, "two_step" if rounding == "two_step" else "single")
+            assert out.is_cuda and torch.equal(bits(out), bits(want_out[rank])), (rounding, seed)
+        ep.close()
+
+
 def run_errors(ep, rank, world, args):
     """A capacity that is too small poisons the group within the timeout; the GPU stays usable."""
     hidden, topk, tokens = args.hidden, 4, args.tokens
@@ -474,7 +517,7 @@ CASES = {"streams": run_streams, "stagger": run_stagger, "headline": run_headlin
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--case", choices=sorted(CASES) + ["hostce", "topk", "subgroup"], required=True)
+    parser.add_argument("--case", choices=sorted(CASES) + ["hostce", "multinode", "topk", "subgroup"], required=True)
     parser.add_argument("--hidden", type=int, default=256)
     parser.add_argument("--tokens", type=int, default=24)
     parser.add_argument("--replays", type=int, default=1000)
@@ -485,9 +528,11 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     comm = get_nccl_comm_handle(dist.group.WORLD)
-    if args.case in ("topk", "subgroup"):
+    if args.case in ("topk", "subgroup", "multinode"):
         if args.case == "topk":
             run_topk(comm, rank, world, args)
+        elif args.case == "multinode":
+            run_multinode(comm, rank, world, args)
         else:
             run_subgroup(rank, world, args)
         dist.destroy_process_group()

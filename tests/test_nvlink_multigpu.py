@@ -118,3 +118,10 @@ def test_topk_3_and_33_with_a_scattered_expert_map():
 @pytest.mark.skipif(gpu_count() < 3, reason="needs at least three CUDA devices")
 def test_noncontiguous_subgroup_and_handle_reacquisition():
     launch("subgroup", min(gpu_count(), 4))
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.skipif(gpu_count() < 2, reason="needs at least two CUDA devices")
+def test_multinode_context_over_nccl_point_to_point():
+    launch("multinode", min(gpu_count(), 4))
