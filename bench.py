@@ -364,10 +364,14 @@ def run(args):
             raise SystemExit("the sample ring recorded fewer operations than steps were timed")
         dispatch_us = gather_max([ns / 1e3 for ns in samples["dispatch"]["elapsed_ns"][:args.steps]], world)
         combine_us = gather_max([ns / 1e3 for ns in samples["combine"]["elapsed_ns"][:args.steps]], world)
+        expert_us, between_us = [], []
         phase_timing = "library sample ring: earliest CTA start to latest CTA end of every replayed kernel"
     else:
         dispatch_us = gather_max([m[0].elapsed_time(m[1]) * 1e3 for m in timing], world)
         combine_us = gather_max([m[2].elapsed_time(m[3]) * 1e3 for m in timing], world)
+        expert_us = gather_max([m[1].elapsed_time(m[2]) * 1e3 for m in timing], world)
+        # device time between the end of one step's combine and the start of the next dispatch
+        between_us = gather_max([a[3].elapsed_time(b[0]) * 1e3 for a, b in zip(timing, timing[1:])] or [0.0], world)
         phase_timing = "CUDA events around every phase"
     both_us = [d + c for d, c in zip(dispatch_us, combine_us)]
     ms_per_step = total_ms / args.steps
@@ -448,6 +452,8 @@ def run(args):
                          "inputs rotate over 4 batches; the rows of a step come from a peer's memory or were "
                          "written by the previous kernel, a small batch fits the 126 MB L2 by nature"},
         "dispatch_us_p50": statistics.median(dispatch_us), "combine_us_p50": statistics.median(combine_us),
+        "expert_us_p50": statistics.median(expert_us) if expert_us else None,
+        "between_steps_us_p50": statistics.median(between_us) if between_us else None,
         "dispatch_combine_us_p50": statistics.median(both_us),
         "dispatch_combine_us_p95": ordered[min(len(ordered) - 1, int(0.95 * len(ordered)))],
         "checked": checked is not None, "verified": checked, "status": status,
