@@ -1032,7 +1032,8 @@ combine_kernel(const __grid_constant__ CombineArgs args) {
 // error reporting are those of the general kernel; profiled operations use the general kernel.
 constexpr int kLoneThreads = 256;
 constexpr int kLoneUnroll = 8;
-constexpr int kLoneMaxCtas = 148 * 8;
+constexpr int kLoneSms = 148;
+constexpr int kLoneMaxCtas = kLoneSms * 8;
 
 __global__ void __launch_bounds__(kLoneThreads) combine_lone_kernel(const __grid_constant__ CombineArgs args) {
   const CombineOp& op = args.op[blockIdx.y];
@@ -1062,7 +1063,9 @@ __global__ void __launch_bounds__(kLoneThreads) combine_lone_kernel(const __grid
     report_error(c, kCapacityExceeded, kPhaseCombine, 7, static_cast<unsigned>(op.partial_rows));
 
   const int warps = kLoneThreads / 32;
-  for (long long t = static_cast<long long>(blockIdx.x) * warps + (tid >> 5); t < op.tokens;
+  // Warp w of CTA c takes tokens w * grid + c, ...: every CTA (hence every SM) ends up with the
+  // same number of rows to within one, also when the grid was rounded up to whole waves.
+  for (long long t = static_cast<long long>(tid >> 5) * gridDim.x + blockIdx.x; t < op.tokens;
        t += static_cast<long long>(gridDim.x) * warps) {
     const int row = (mask_arr[t] & 1ull) ? send_rows[t * fan] : -1;
     const bool usable = row >= 0 && row < op.partial_rows;       // warp-uniform
@@ -1171,10 +1174,11 @@ cudaError_t launch_combine(const CombineArgs& args, int ranks, int ctas_per_rank
   CombineVariant variant;
   const long long row_bytes = static_cast<long long>(hidden) * 2;
   if (world == 1 && ranks == 1 && vec16 && args.op[0].profile == nullptr) {
-    // One rank: a streaming pass over local memory, eight tokens per CTA and pass.
+    // One rank: a streaming pass over local memory, one token per warp and pass.
     const int warps = kLoneThreads / 32, tokens = args.op[0].tokens;
     int ctas = (tokens + warps - 1) / warps;
     if (ctas < 1) ctas = 1;
+    if (ctas > kLoneSms) ctas = (ctas + kLoneSms - 1) / kLoneSms * kLoneSms;   // whole waves over the SMs
     if (ctas > kLoneMaxCtas) ctas = kLoneMaxCtas;
     return cudaLaunchKernel(reinterpret_cast<const void*>(combine_lone_kernel), dim3(ctas, 1, 1),
                             dim3(kLoneThreads, 1, 1), params, 0, stream);
