@@ -678,6 +678,9 @@ __device__ __forceinline__ bool mailbox_push(const PushArgs& p, const RankCtx& c
     if (wait_begin != 0ull) prof.count(kProfPushWait, global_timer_ns() - wait_begin);
     fence_proxy_async();               // the copies wrote through the async proxy; the words below are ordinary stores
     if (!__all_sync(0xffffffffu, ok)) break;
+    // A round that only met holes of the interleaved order completed no row: nothing to order,
+    // nothing to publish (all pieces of a row travel in one round).
+    if (!__any_sync(0xffffffffu, word != nullptr)) continue;
     if (hand == nullptr) {
       __threadfence_system();
       if (word != nullptr) {

@@ -194,9 +194,15 @@ class TransportCore:
         """CTAs per rank of a combine. Under the mailbox protocol 7/16 of them (at most 64) only
         push - fifteen received rows per round trip each - and the others reduce four (token, row
         segment) items at a time; small batches get enough CTAs for one round trip to move
-        everything, and never fewer than two (one pushes, one reduces)."""
+        everything (one round per pusher also for the tiniest batch), and never fewer than two (one
+        pushes, one reduces)."""
         budget = self.max_ctas if budget is None else max(1, min(budget, self.max_ctas))
-        wanted = max(2, -(-max(capacity, 1) // 6), max(tokens, 1))
+        # The pushers walk the received rows interleaved over the peers in blocks of eight, holes
+        # included: even one row per peer is (world - 1) * 8 work items, fifteen per pusher round.
+        peers = max(getattr(self, "world", 1) - 1, 0)
+        pushers = -(-peers * 8 // 15)
+        floor = max(2, -(-pushers * 16 // 7))
+        wanted = max(floor, -(-max(capacity, 1) // 6), max(tokens, 1))
         return max(1, min(budget, wanted))
 
     def dispatch(self, slot: Slot, xs, ids, weights, capacities, *, identity=0, ctas=None, stream=None,

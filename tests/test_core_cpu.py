@@ -68,6 +68,13 @@ def test_launch_width_follows_items_per_cta():
     assert core.pick_combine_ctas(128, 1024) == 148 and core.pick_combine_ctas(1, 8) == 2
     assert core.pick_combine_ctas(16, 16) == 16 and core.pick_combine_ctas(4096, 32768, budget=100) == 100
     assert core.pick_combine_ctas(1, 1) == 2 and core.pick_combine_ctas(8, 64) == 11
+    # with peers, the tiniest batch still gets one pusher per fifteen interleaved work items
+    core.world = 8
+    assert core.pick_combine_ctas(1, 8) == 10 and core.pick_combine_ctas(8, 64) == 11
+    core.world = 4
+    assert core.pick_combine_ctas(1, 4) == 5
+    core.world = 2
+    assert core.pick_combine_ctas(1, 2) == 3
 
 
 def test_load_refuses_a_binary_built_from_other_sources(monkeypatch):
