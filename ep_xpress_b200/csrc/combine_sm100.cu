@@ -206,7 +206,8 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 constexpr int kGroupWarps = 4;                    // consumer warps of one pipeline
 constexpr int kGroupThreads = kGroupWarps * 32;
 constexpr int kMaxGroups = 4;
-constexpr int kBulkThreads = kThreads + 32 * kMaxGroups;   // sequential protocol: 4 pipelines = 20 warps
+constexpr int kGroupProducers = 2;                // producer warps of one pipeline: they take its items alternately
+constexpr int kBulkThreads = kThreads + 32 * kMaxGroups * kGroupProducers;   // 4 pipelines of 4 + 2 warps = 24 warps
 constexpr size_t kBulkSmemBytes = 192 * 1024;              // ... sharing 192 KB of stage rings
 constexpr int kMaxGroupStages = 3;
 constexpr int kChunksPerThread = 4;
@@ -317,8 +318,10 @@ struct BulkReduceArgs {
 };
 
 // Barriers and item slots are indexed [group][stage]. Returns false when a bounded wait gave up.
-// Called by the first kGroups * (kGroupWarps + 1) warps of the CTA: consumers first, then one
-// producer warp per group. kMailbox: the peers are still pushing while this runs, so before a
+// Called by the first kGroups * (kGroupWarps + kGroupProducers) warps of the CTA: consumers first,
+// then the producer warps, kGroupProducers per group. The producers of a group take its items
+// alternately (item k fills stage k % stages whoever issues it), because a producer's per-item
+// chain - arrival words, look-ups, barrier, copies - is longer than the consumers' arithmetic. kMailbox: the peers are still pushing while this runs, so before a
 // producer copies a token's rows, lane j waits (bounded) for the arrival word behind the staging
 // row of remote contributor j to carry this combine's epoch, and the CTAs take items round-robin
 // so that each of them owns tokens from every part of the batch.
@@ -330,7 +333,8 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   constexpr size_t kGroupSmemBytes = kReduceSmem / kGroups;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool producer = warp >= kConsumerWarps;
-  const int group = producer ? warp - kConsumerWarps : warp / kGroupWarps;
+  const int group = producer ? (warp - kConsumerWarps) / kGroupProducers : warp / kGroupWarps;
+  const int turn = producer ? (warp - kConsumerWarps) % kGroupProducers : 0;   // which items of the pipeline this producer takes
   const int seg_max = ring_segment_bytes(a.fan, kGroupSmemBytes);
   const int rsegs = static_cast<int>((a.row_bytes + seg_max - 1) / seg_max);
   const int rseg_bytes = static_cast<int>(align_up((a.row_bytes + rsegs - 1) / rsegs, 512));
@@ -378,7 +382,8 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
         if (kMailbox) {
           const unsigned long long mk = __shfl_sync(0xffffffffu, mask_now, 4 * r + (lane >> 3));
           const int k = base + 4 * r + (lane >> 3), j = lane & 7;
-          if (k < mine && j < __popcll(mk) && rows_now[r] >= 0 && nth_set_bit(mk, j) != a.self) {
+          if (k < mine && k % kGroupProducers == turn && j < __popcll(mk) && rows_now[r] >= 0 &&
+              nth_set_bit(mk, j) != a.self) {
             const long long tk = item_of(k) / rsegs;
             early = ld_acquire_sys_u32(reinterpret_cast<const unsigned*>(a.staging + (tk * a.fan + j) * a.stride + a.row_bytes));
           }
@@ -391,9 +396,10 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           const int row = __shfl_sync(0xffffffffu, rows_now[r], q * 8 + (lane & 7));
           const unsigned seen = __shfl_sync(0xffffffffu, early, q * 8 + (lane & 7));
           if (base + i >= mine || !ok) continue;                 // warp-uniform
+          if ((base + i) % kGroupProducers != turn) continue;    // the pipeline's other producer fills that stage
+          use = static_cast<unsigned>(base + i);                 // stages are used in item order
           const int stage = use % stages;
           const unsigned parity = ((use / stages) & 1u) ^ 1u;
-          ++use;
           const long long t0 = clock64();
           if (!__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
             ok = false;
@@ -461,7 +467,8 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
 #pragma unroll
       for (int r = 0; r < 8; ++r) rows_now[r] = rows_next[r];
     }
-    if (ok) {                                              // end marker
+    use = static_cast<unsigned>(mine);
+    if (ok && mine % kGroupProducers == turn) {            // end marker, by the producer whose turn it would be
       const int stage = use % stages;
       const unsigned parity = ((use / stages) & 1u) ^ 1u;
       if (__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
@@ -526,7 +533,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       worked += clock64() - t1;
     }
   }
-  if (kProfile && a.profile != nullptr && lane == 0 && (warp == 0 || warp == kConsumerWarps)) {   // group 0
+  if (kProfile && a.profile != nullptr && lane == 0 && (warp == 0 || warp == kConsumerWarps)) {   // group 0 (its first producer)
     unsigned long long* slot = a.profile + static_cast<size_t>(blockIdx.x) * kProfileStamps + (warp == 0 ? 4 : 6);
     slot[0] = static_cast<unsigned long long>(waited);
     slot[1] = static_cast<unsigned long long>(worked);
