@@ -194,9 +194,9 @@ __device__ __forceinline__ int nth_set_bit(unsigned long long mask, int n) {
 
 // ---- reduce phase, bulk-copy variant -------------------------------------------------------
 // (rows 16-byte aligned, at most kPeerBatch contributors per token)
-// The reducing warps of a CTA form independent pipelines. Each has one producer warp, four
-// consumer warps and a private ring of shared-memory stages. The producer walks its share of
-// the CTA's (token, row segment) items; lane j issues ONE bulk copy (TMA) of contributor j's
+// The reducing warps of a CTA form independent pipelines. Each has two producer warps, four
+// consumer warps and a private ring of shared-memory stages. The producers walk the pipeline's
+// share of the CTA's (token, row segment) items alternately; lane j issues ONE bulk copy (TMA) of contributor j's
 // segment into the stage and all copies of an item complete on the stage's "full" mbarrier.
 // The consumers add the staged chunks in ascending rank order, store the result and release
 // the stage through its "empty" mbarrier. Data in flight lives in shared memory, so the phase
