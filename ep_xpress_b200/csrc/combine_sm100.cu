@@ -340,6 +340,12 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
   const int rseg_bytes = static_cast<int>(align_up((a.row_bytes + rsegs - 1) / rsegs, 512));
   const int items = a.tokens * rsegs;
   const int stages = ring_stages(a.fan, seg_max, kGroupSmemBytes);
+  // A wait on a stage's "empty" barrier tells two consecutive phases apart, no more. A producer
+  // that takes every kGroupProducers-th item passed the wait of its previous item, i.e. knows
+  // that the consumers are at most `stages` + kGroupProducers - 1 items behind: that is within
+  // one phase of every stage as long as the ring has at least kGroupProducers stages. A shorter
+  // ring (not reachable with the segment sizes above) is filled by the first producer alone.
+  const int producers = stages >= kGroupProducers ? kGroupProducers : 1;
   const size_t stage_bytes = static_cast<size_t>(a.fan) * seg_max;
   char* const ring = smem + static_cast<size_t>(group) * kGroupSmemBytes;
   unsigned long long* const full = full_all + group * kMaxGroupStages;
@@ -382,7 +388,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
         if (kMailbox) {
           const unsigned long long mk = __shfl_sync(0xffffffffu, mask_now, 4 * r + (lane >> 3));
           const int k = base + 4 * r + (lane >> 3), j = lane & 7;
-          if (k < mine && k % kGroupProducers == turn && j < __popcll(mk) && rows_now[r] >= 0 &&
+          if (k < mine && k % producers == turn && j < __popcll(mk) && rows_now[r] >= 0 &&
               nth_set_bit(mk, j) != a.self) {
             const long long tk = item_of(k) / rsegs;
             early = ld_acquire_sys_u32(reinterpret_cast<const unsigned*>(a.staging + (tk * a.fan + j) * a.stride + a.row_bytes));
@@ -396,7 +402,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
           const int row = __shfl_sync(0xffffffffu, rows_now[r], q * 8 + (lane & 7));
           const unsigned seen = __shfl_sync(0xffffffffu, early, q * 8 + (lane & 7));
           if (base + i >= mine || !ok) continue;                 // warp-uniform
-          if ((base + i) % kGroupProducers != turn) continue;    // the pipeline's other producer fills that stage
+          if ((base + i) % producers != turn) continue;          // the pipeline's other producer fills that stage
           use = static_cast<unsigned>(base + i);                 // stages are used in item order
           const int stage = use % stages;
           const unsigned parity = ((use / stages) & 1u) ^ 1u;
@@ -468,7 +474,7 @@ __device__ __forceinline__ bool bulk_reduce(const BulkReduceArgs& a, char* smem,
       for (int r = 0; r < 8; ++r) rows_now[r] = rows_next[r];
     }
     use = static_cast<unsigned>(mine);
-    if (ok && mine % kGroupProducers == turn) {            // end marker, by the producer whose turn it would be
+    if (ok && mine % producers == turn) {                  // end marker, by the producer whose turn it would be
       const int stage = use % stages;
       const unsigned parity = ((use / stages) & 1u) ^ 1u;
       if (__all_sync(0xffffffffu, mbarrier_wait_bounded(empty + stage, parity, a.timeout_ns))) {
