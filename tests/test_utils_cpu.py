@@ -206,3 +206,40 @@ def test_identity_layer_oracle_matches_the_group_wide_oracles(world, rounding):
     for rank in range(world):
         got = routing.identity_layer_oracle(xs[rank], ids[rank], ws[rank], owners, rank, world, rounding)
         assert torch.equal(got.view(torch.int16), want[rank].view(torch.int16))
+
+
+def test_identity_layer_oracle_property():
+    """Random shapes, placements, inactive slots and zero weights: the per-rank shortcut and the
+    group-wide oracles agree bit for bit (hypothesis drives the cases)."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=40, deadline=None)
+    @given(world=st.integers(1, 5), experts_per_rank=st.integers(1, 3), topk=st.integers(1, 4),
+           tokens=st.integers(0, 9), seed=st.integers(0, 10_000), rounding=st.sampled_from(["two_step", "single"]))
+    def check(world, experts_per_rank, topk, tokens, seed, rounding):
+        experts = world * experts_per_rank
+        topk = min(topk, experts)
+        generator = torch.Generator().manual_seed(seed)
+        owners = torch.randint(0, world, (experts,), generator=generator).tolist()
+        xs, ids, ws = [], [], []
+        for rank in range(world):
+            n = max(tokens - rank, 0)
+            scores = torch.rand((n, experts), generator=generator)
+            chosen = scores.topk(topk, dim=1).indices.to(torch.int64)
+            chosen[torch.rand((n, topk), generator=generator) < 0.15] = -1
+            weights = torch.rand((n, topk), generator=generator)
+            weights[torch.rand((n, topk), generator=generator) < 0.1] = 0.0
+            xs.append(torch.randn((n, 16), generator=generator).to(torch.bfloat16))
+            ids.append(chosen)
+            ws.append(weights)
+        plan = routing.plan_routes(ids, ws, owners, world, topk)
+        rows = routing.dispatch_oracle(xs, plan)
+        partials = [routing.scale_expert_oracle(rows[r], plan.received[r].local_ids, plan.received[r].weights)
+                    for r in range(world)]
+        want = routing.combine_oracle(partials, plan, 16, rounding)
+        for rank in range(world):
+            got = routing.identity_layer_oracle(xs[rank], ids[rank], ws[rank], owners, rank, world, rounding)
+            assert torch.equal(got.view(torch.int16), want[rank].view(torch.int16))
+
+    check()
